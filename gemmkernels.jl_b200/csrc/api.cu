@@ -1,0 +1,251 @@
+// C ABI of the library (include/gemmkernels_b200.h): handle, dispatch, error reporting.
+#include <cstring>
+#include <new>
+
+#include "common.h"
+#include "simt_gemm.cuh"
+#include "tc_plan.h"
+
+namespace gk {
+
+static thread_local char g_error[512] = "";
+
+gk_status set_error(gk_status s, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return s;
+}
+void clear_error() { g_error[0] = 0; }
+
+// ------------------------------------------------------------------------------------------------
+// descriptor validation shared by every path
+// ------------------------------------------------------------------------------------------------
+static gk_status validate_desc(const gk_gemm_desc* d, const gk_epilogue_desc* epi) {
+  if (!d) return set_error(GK_ERR_INVALID_ARGUMENT, "descriptor is NULL");
+  if (d->struct_size != sizeof(gk_gemm_desc))
+    return set_error(GK_ERR_INVALID_ARGUMENT, "gk_gemm_desc.struct_size is %u, this library expects %zu",
+                     d->struct_size, sizeof(gk_gemm_desc));
+  if (epi && epi->struct_size != sizeof(gk_epilogue_desc))
+    return set_error(GK_ERR_INVALID_ARGUMENT, "gk_epilogue_desc.struct_size is %u, this library expects %zu",
+                     epi->struct_size, sizeof(gk_epilogue_desc));
+  if (d->m < 0 || d->n < 0 || d->k < 0)
+    return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: negative extent (%lld, %lld, %lld)",
+                     (long long)d->m, (long long)d->n, (long long)d->k);
+  const int64_t a_rows = d->trans_a ? d->k : d->m;
+  const int64_t b_rows = d->trans_b ? d->n : d->k;
+  if (d->layout_a == GK_LAYOUT_DENSE && d->lda < (a_rows > 0 ? a_rows : 1))
+    return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: lda = %lld < %lld stored rows of A",
+                     (long long)d->lda, (long long)a_rows);
+  if (d->layout_b == GK_LAYOUT_DENSE && d->ldb < (b_rows > 0 ? b_rows : 1))
+    return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: ldb = %lld < %lld stored rows of B",
+                     (long long)d->ldb, (long long)b_rows);
+  if (d->ldd < (d->m > 0 ? d->m : 1))
+    return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: ldd = %lld < M = %lld",
+                     (long long)d->ldd, (long long)d->m);
+  if (d->layout_c == GK_LAYOUT_DENSE && d->beta != 0.0 && d->ldc < (d->m > 0 ? d->m : 1))
+    return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: ldc = %lld < M = %lld",
+                     (long long)d->ldc, (long long)d->m);
+  if (dtype_size(d->dtype_a) == 0 || dtype_size(d->dtype_b) == 0 || dtype_size(d->dtype_c) == 0 ||
+      dtype_size(d->dtype_d) == 0)
+    return set_error(GK_ERR_UNSUPPORTED, "unknown element type in descriptor");
+  if (d->number < GK_REAL || d->number > GK_DUAL)
+    return set_error(GK_ERR_INVALID_CONFIG, "unknown number system %d", d->number);
+  if (epi) {
+    if (epi->bias_axis < GK_BIAS_NONE || epi->bias_axis > GK_BIAS_COL)
+      return set_error(GK_ERR_UNSUPPORTED, "bias axis %d is not none/row/column", epi->bias_axis);
+    if (epi->activation < GK_ACT_NONE || epi->activation > GK_ACT_GELU)
+      return set_error(GK_ERR_UNSUPPORTED, "activation %d is not one of none/ReLU/GELU", epi->activation);
+  }
+  return GK_OK;
+}
+
+// Which kernel family serves this descriptor: 1 tcgen05, 3 generic SIMT.
+static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+  const bool tc_types = (d.compute == GK_F16 || d.compute == GK_BF16 || d.compute == GK_TF32);
+  if (d.op == GK_OP_TCGEN05 || (d.op == GK_OP_AUTO && tc_types)) {
+    if (tc_eligible(d, a, b, why)) return 1;
+    if (d.number != GK_REAL) return -1;        // no SIMT complex/dual kernel
+    if (d.compute == GK_TF32) return -1;       // an FP32 SIMT result is not a TF32 result: refuse
+    return 3;                                  // FP16/BF16 inputs, FP32 accumulation in SIMT
+  }
+  if (d.number != GK_REAL) { if (why) *why = "complex and dual products need the TCGen05Operator"; return -1; }
+  return 3;
+}
+
+// ------------------------------------------------------------------------------------------------
+// generic SIMT dispatch
+// ------------------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, typename TAcc>
+static gk_status launch_simt_typed(const SimtParams& p, bool tropical, cudaStream_t stream) {
+  dim3 grid(static_cast<unsigned>((p.M + kSimtTile - 1) / kSimtTile),
+            static_cast<unsigned>((p.N + kSimtTile - 1) / kSimtTile));
+  if (grid.y > 65535u) return set_error(GK_ERR_INVALID_CONFIG, "N too large for the generic kernel");
+  if (tropical)
+    simt_gemm_kernel<TIn, TOut, TAcc, true><<<grid, kSimtThreads, 0, stream>>>(p);
+  else
+    simt_gemm_kernel<TIn, TOut, TAcc, false><<<grid, kSimtThreads, 0, stream>>>(p);
+  GK_CUDA_CHECK(cudaGetLastError());
+  return GK_OK;
+}
+
+static gk_status launch_simt(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
+                             const void* b, const void* c, void* dd, cudaStream_t stream) {
+  if (d.dtype_a != d.dtype_b)
+    return set_error(GK_ERR_UNSUPPORTED, "A (%s) and B (%s) must have the same element type",
+                     dtype_name(d.dtype_a), dtype_name(d.dtype_b));
+  if (d.dtype_c != d.dtype_d)
+    return set_error(GK_ERR_UNSUPPORTED, "C (%s) and D (%s) must have the same element type",
+                     dtype_name(d.dtype_c), dtype_name(d.dtype_d));
+  if (d.m == 0 || d.n == 0) return GK_OK;
+  SimtParams p{};
+  p.A = a; p.B = b; p.C = c; p.D = dd;
+  p.M = d.m; p.N = d.n; p.K = d.k;
+  p.a_sm = d.trans_a ? d.lda : 1; p.a_sk = d.trans_a ? 1 : d.lda;
+  p.b_sk = d.trans_b ? d.ldb : 1; p.b_sn = d.trans_b ? 1 : d.ldb;
+  p.ldc = d.ldc; p.ldd = d.ldd;
+  p.alpha = d.alpha; p.beta = d.beta;
+  p.has_c = (d.layout_c != GK_LAYOUT_ZERO && c != nullptr && d.beta != 0.0) ? 1 : 0;
+  p.a_zero = (d.layout_a == GK_LAYOUT_ZERO || d.layout_b == GK_LAYOUT_ZERO || d.alpha == 0.0 || d.k == 0) ? 1 : 0;
+  if (d.layout_a == GK_LAYOUT_DIAGONAL)
+    return set_error(GK_ERR_UNSUPPORTED, "Diagonal layout is not handled by the generic kernel");
+  if (epi) { p.bias = epi->bias; p.bias_axis = epi->bias_axis; p.act = epi->activation; }
+  const bool trop = d.op == GK_OP_FPU_TROPICAL;
+  const int ti = d.dtype_a, to = d.dtype_d;
+  if (ti == GK_F16 && to == GK_F32) return launch_simt_typed<__half, float, float>(p, trop, stream);
+  if (ti == GK_F16 && to == GK_F16) return launch_simt_typed<__half, __half, float>(p, trop, stream);
+  if (ti == GK_BF16 && to == GK_F32) return launch_simt_typed<__nv_bfloat16, float, float>(p, trop, stream);
+  if (ti == GK_BF16 && to == GK_BF16) return launch_simt_typed<__nv_bfloat16, __nv_bfloat16, float>(p, trop, stream);
+  if (ti == GK_F32 && to == GK_F32) return launch_simt_typed<float, float, float>(p, trop, stream);
+  if (ti == GK_F32 && to == GK_F64) return launch_simt_typed<float, double, double>(p, trop, stream);
+  if (ti == GK_F64 && to == GK_F64) return launch_simt_typed<double, double, double>(p, trop, stream);
+  if (ti == GK_I16 && to == GK_I16) return launch_simt_typed<int16_t, int16_t, int16_t>(p, trop, stream);
+  if (ti == GK_I32 && to == GK_I32) return launch_simt_typed<int32_t, int32_t, int32_t>(p, trop, stream);
+  if (ti == GK_I64 && to == GK_I64) return launch_simt_typed<int64_t, int64_t, int64_t>(p, trop, stream);
+  return set_error(GK_ERR_UNSUPPORTED, "no kernel for element types A/B %s, C/D %s", dtype_name(ti), dtype_name(to));
+}
+
+}  // namespace gk
+
+using namespace gk;
+
+extern "C" {
+
+int32_t gk_version(void) { return GK_VERSION_MAJOR * 1000 + GK_VERSION_MINOR; }
+
+const char* gk_last_error_message(void) { return g_error; }
+
+gk_status gk_create(gk_handle* out) {
+  clear_error();
+  if (!out) return set_error(GK_ERR_INVALID_ARGUMENT, "out is NULL");
+  *out = nullptr;
+  int dev = 0;
+  GK_CUDA_CHECK(cudaGetDevice(&dev));
+  cudaDeviceProp prop{};
+  GK_CUDA_CHECK(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10)
+    return set_error(GK_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                     prop.major, prop.minor);
+  gk_handle h = new (std::nothrow) gk_handle_s();
+  if (!h) return set_error(GK_ERR_CUDA, "out of host memory");
+  h->device = dev;
+  h->sm_count = prop.multiProcessorCount;
+  h->cc_major = prop.major; h->cc_minor = prop.minor;
+  h->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    delete h;
+    return set_error(GK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  h->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaHostAlloc(reinterpret_cast<void**>(&h->status_host), sizeof(int32_t), cudaHostAllocMapped);
+  if (e != cudaSuccess) { delete h; return set_error(GK_ERR_CUDA, "cudaHostAlloc failed: %s", cudaGetErrorString(e)); }
+  *h->status_host = 0;
+  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&h->status_dev), h->status_host, 0);
+  if (e != cudaSuccess) {
+    cudaFreeHost(h->status_host); delete h;
+    return set_error(GK_ERR_CUDA, "cudaHostGetDevicePointer failed: %s", cudaGetErrorString(e));
+  }
+  *out = h;
+  return GK_OK;
+}
+
+gk_status gk_destroy(gk_handle h) {
+  clear_error();
+  if (!h) return GK_OK;
+  for (int i = 0; i < 4; ++i)
+    if (h->stage_dev[i]) cudaFree(h->stage_dev[i]);
+  if (h->status_host) cudaFreeHost(h->status_host);
+  delete h;
+  return GK_OK;
+}
+
+gk_status gk_poll_status(gk_handle h, int32_t* raw_code) {
+  clear_error();
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  const int32_t code = *reinterpret_cast<volatile int32_t*>(h->status_host);
+  if (raw_code) *raw_code = code;
+  if (code == 0) return GK_OK;
+  *reinterpret_cast<volatile int32_t*>(h->status_host) = 0;
+  return set_error(GK_ERR_TIMEOUT, "a device-side wait gave up (code %d: %s)", code,
+                   code == 101 ? "TMA producer" : code == 102 ? "MMA issuer"
+                   : code == 103 ? "epilogue" : code == 104 ? "drain" : "unknown");
+}
+
+gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
+                        gk_gemm_plan* plan) {
+  clear_error();
+  if (!h || !plan) return set_error(GK_ERR_INVALID_ARGUMENT, "handle or plan is NULL");
+  gk_status s = validate_desc(desc, epi);
+  if (s != GK_OK) return s;
+  std::memset(plan, 0, sizeof(*plan));
+  std::string why;
+  const int fam = choose_family(*desc, nullptr, nullptr, &why);
+  if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
+  plan->kernel = fam;
+  if (fam == 1) {
+    TcLaunch L;
+    s = tc_plan(h, *desc, epi, nullptr, nullptr, nullptr, nullptr, &L);
+    if (s != GK_OK) return s;
+    plan->grid = L.grid; plan->block = kTcThreads; plan->cluster = L.cg;
+    plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
+    plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn; plan->tile_k = L.params.bk;
+    plan->stages = L.params.stages;
+  } else {
+    plan->grid = static_cast<int32_t>(((desc->m + kSimtTile - 1) / kSimtTile) * ((desc->n + kSimtTile - 1) / kSimtTile));
+    plan->block = kSimtThreads; plan->cluster = 1;
+    plan->tile_m = kSimtTile; plan->tile_n = kSimtTile; plan->tile_k = kSimtK; plan->stages = 1;
+  }
+  return GK_OK;
+}
+
+gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
+                  const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
+                  gk_stream stream) {
+  clear_error();
+  (void)workspace;
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  gk_status s = validate_desc(desc, epi);
+  if (s != GK_OK) return s;
+  if (!d && desc->m > 0 && desc->n > 0) return set_error(GK_ERR_INVALID_ARGUMENT, "D is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::string why;
+  int fam = choose_family(*desc, a, b, &why);
+  if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
+  if (desc->m == 0 || desc->n == 0) return GK_OK;
+  if (fam == 1 && (desc->k == 0 || desc->alpha == 0.0)) fam = 3;  // nothing to multiply
+  if (fam == 1) {
+    TcLaunch L;
+    s = tc_plan(h, *desc, epi, a, b, c, d, &L);
+    if (s != GK_OK) return s;
+    s = tc_encode_maps(h, *desc, a, b, &L);
+    if (s != GK_OK) return s;
+    return tc_launch(L, st);
+  }
+  return launch_simt(*desc, epi, a, b, c, d, st);
+}
+
+}  // extern "C"

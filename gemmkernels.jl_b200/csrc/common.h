@@ -1,0 +1,71 @@
+// Host-side shared declarations of the library: handle, error reporting, small helpers.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
+#include <string>
+
+#include "../../include/gemmkernels_b200.h"
+
+namespace gk {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+gk_status set_error(gk_status s, const char* fmt, ...);
+void clear_error();
+
+inline int dtype_size(int32_t dt) {
+  switch (dt) {
+    case GK_F16: case GK_BF16: case GK_I16: return 2;
+    case GK_F32: case GK_I32: case GK_TF32: return 4;
+    case GK_F64: case GK_I64: return 8;
+    default: return 0;
+  }
+}
+
+inline const char* dtype_name(int32_t dt) {
+  switch (dt) {
+    case GK_F16: return "Float16";
+    case GK_BF16: return "BFloat16";
+    case GK_F32: return "Float32";
+    case GK_F64: return "Float64";
+    case GK_I16: return "Int16";
+    case GK_I32: return "Int32";
+    case GK_I64: return "Int64";
+    case GK_TF32: return "TF32";
+    default: return "?";
+  }
+}
+
+#define GK_CUDA_CHECK(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return gk::set_error(GK_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                  \
+                           cudaGetErrorString(_e), __FILE__, __LINE__);                  \
+  } while (0)
+
+}  // namespace gk
+
+struct gk_handle_s {
+  int device = 0;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int cc_major = 0, cc_minor = 0;
+  int32_t* status_host = nullptr;  // pinned, mapped: device-side waits report here
+  int32_t* status_dev = nullptr;   // the same word as the device sees it
+  gk::EncodeTiledFn encode_tiled = nullptr;
+  std::mutex mu;                   // guards the caches below
+  int max_clusters[2][2][2] = {};  // tc kernel [planes-1][tf32][unused] -> co-resident CTA pairs
+  bool attr_set[2][2][2] = {};     // tc kernel [cg-1][planes-1][tf32]: smem attribute set
+  // staging buffers of gk_gemm_host (grown on demand, freed by gk_destroy)
+  void* stage_dev[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t stage_bytes[4] = {0, 0, 0, 0};
+};

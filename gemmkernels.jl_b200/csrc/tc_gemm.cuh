@@ -1,0 +1,390 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D = act( alpha * sum_terms(+/- A_plane * B_plane) + beta * C + bias )
+//
+// One kernel covers the real product (one term), the planar complex product (four terms, two
+// accumulator planes) and the dual-number product (three terms).  Operands reach shared memory by
+// TMA with the 128-byte swizzle and are consumed by tcgen05.mma straight from there; accumulators
+// live in tensor memory, double-buffered so the epilogue of one tile overlaps the main loop of the
+// next.  With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of
+// A and its own half of B's columns (no multicast), and the pair leader issues the MMAs for both.
+//
+// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = TMEM allocator,
+// warp 3 = idle, warps 4..7 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+//
+// Every barrier wait is bounded (ptx.cuh: mbar_wait).  When a wait gives up, the CTA raises a
+// shared abort flag, all roles leave their loops, in-flight copies and MMAs are drained with
+// bounded waits, TMEM is released, and an error code is left in *status for the host.
+#pragma once
+#include "ptx.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace gk {
+
+constexpr int kTcThreads = 256;
+constexpr int kTcTileM = 128;              // rows per CTA (TMEM lanes)
+constexpr int kTcKBytes = 128;             // bytes of K per k-block row (= swizzle span)
+constexpr int kTcMmaPerKBlock = 4;         // each MMA consumes 32 bytes of K
+constexpr uint64_t kTcWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+
+enum TcDtype : int32_t { TC_F16 = 0, TC_BF16 = 1, TC_F32 = 2 };
+enum TcAct : int32_t { TC_ACT_NONE = 0, TC_ACT_RELU = 1, TC_ACT_GELU = 2 };
+enum TcBias : int32_t { TC_BIAS_NONE = 0, TC_BIAS_ROW = 1, TC_BIAS_COL = 2 };
+
+// status word values (0 = ok)
+enum TcStatus : int32_t {
+  TC_ST_OK = 0,
+  TC_ST_TIMEOUT_PRODUCER = 101,
+  TC_ST_TIMEOUT_MMA = 102,
+  TC_ST_TIMEOUT_EPILOGUE = 103,
+  TC_ST_TIMEOUT_DRAIN = 104,
+};
+
+struct TcTerm {
+  uint8_t a_plane, b_plane, acc_plane, negate_a;
+  uint8_t first;  // first term that writes its accumulator plane: overwrites at k == 0
+  uint8_t pad[3];
+};
+
+struct TcParams {
+  CUtensorMap tm_a;  // dims {contiguous, strided, plane}
+  CUtensorMap tm_b;
+  int32_t M, N, K;
+  int32_t tiles_m, tiles_n;  // cluster tiles: (128*CG) x bn
+  int32_t k_blocks;
+  int32_t raster_group;      // cluster tiles along M walked before stepping along N
+  int32_t bn;                // columns per cluster tile (multiple of 32; per-CTA B rows = bn/CG)
+  int32_t bk;                // K elements per k-block (128 bytes)
+  int32_t stages;
+  int32_t a_mn_major, b_mn_major;
+  int32_t a_boxes, b_boxes;  // TMA boxes per plane per CTA per k-block
+  int32_t a_box_bytes, b_box_bytes;
+  int32_t a_plane_bytes, b_plane_bytes;  // shared memory per plane per stage per CTA
+  int32_t a_planes, b_planes;
+  int32_t n_terms;
+  TcTerm terms[4];
+  uint32_t idesc, idesc_neg;  // instruction descriptors (second one negates A)
+  uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
+  uint32_t tmem_cols;         // power of two >= 2 * acc_planes * bn
+  // epilogue
+  const void* C;
+  void* D;
+  int64_t ldc, ldd;           // elements between columns (of one plane / of interleaved pairs)
+  int64_t c_plane, d_plane;   // elements between planes; 0 = interleaved (re, im) pairs
+  int32_t dtype_c, dtype_d;
+  float alpha, beta;
+  const float* bias;
+  int32_t bias_axis, act;
+  int32_t* status;
+};
+
+// The status word may live in host-mapped memory: plain stores, first error wins.
+__device__ __forceinline__ void tc_report(int32_t* status, int32_t code) {
+  volatile int32_t* s = status;
+  if (s != nullptr && *s == TC_ST_OK) {
+    *s = code;
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ float tc_load_elem(const void* p, int64_t idx, int32_t dt) {
+  if (dt == TC_F32) return static_cast<const float*>(p)[idx];
+  if (dt == TC_F16) return __half2float(static_cast<const __half*>(p)[idx]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+}
+
+__device__ __forceinline__ void tc_store_elem(void* p, int64_t idx, int32_t dt, float v) {
+  if (dt == TC_F32)
+    static_cast<float*>(p)[idx] = v;
+  else if (dt == TC_F16)
+    static_cast<__half*>(p)[idx] = __float2half_rn(v);
+  else
+    static_cast<__nv_bfloat16*>(p)[idx] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float tc_activation(float v, int32_t act) {
+  if (act == TC_ACT_RELU) return fmaxf(v, 0.0f);
+  if (act == TC_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+// Cluster tile index -> (tile_m, tile_n): walk `raster_group` tiles down M, then step along N,
+// so that the tiles in flight at any time share A rows and B columns in L2.
+__device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm, int& tn) {
+  const int g = p.raster_group;
+  const int band = g * p.tiles_n;
+  const int band_id = t / band;
+  const int first_m = band_id * g;
+  const int rows = min(g, p.tiles_m - first_m);
+  const int r = t - band_id * band;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+template <int CG, int PLANES, bool TF32>
+__global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle atoms are 1024 bytes and the pattern is a function of the address.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (CG == 2) ? cluster_cta_rank() : 0u;
+  const bool leader = (rank == 0);
+
+  const uint32_t stage_bytes = p.a_planes * p.a_plane_bytes + p.b_planes * p.b_plane_bytes;
+  const uint32_t ctrl = smem_base + p.stages * stage_bytes;  // control block after the stages
+  // control block layout (8-byte slots): full[stages], empty[stages], tmem_full[2], tmem_empty[2],
+  // drain, then two 32-bit words: tmem base, abort flag.
+  const uint32_t bar_full = ctrl;
+  const uint32_t bar_empty = ctrl + 8u * p.stages;
+  const uint32_t bar_tfull = ctrl + 16u * p.stages;
+  const uint32_t bar_tempty = bar_tfull + 16u;
+  const uint32_t bar_drain = bar_tempty + 16u;
+  const uint32_t tmem_slot = bar_drain + 8u;
+  uint8_t* ctrl_gen = smem_gen + p.stages * stage_bytes;
+  volatile uint32_t* tmem_slot_gen =
+      reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * p.stages + 40);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * p.stages + 44);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(bar_full + 8u * s, 1);
+      mbar_init(bar_empty + 8u * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8u * a, 1);
+      mbar_init(bar_tempty + 8u * a, 4 * CG);  // one arrival per epilogue warp per CTA
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&p.tm_a);
+    prefetch_tensormap(&p.tm_b);
+  }
+  if (warp == 2) {
+    tmem_alloc<CG>(tmem_slot, p.tmem_cols);
+    tmem_relinquish<CG>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // peer barriers are initialised before any remote use
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int cluster_id = blockIdx.x / CG;
+  const int num_clusters = gridDim.x / CG;
+  const int bn_cta = p.bn / CG;
+  const uint32_t acc_cols = PLANES * p.bn;  // TMEM columns per accumulator stage
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t full0_leader = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t issued = 0;  // k-blocks issued so far by this CTA
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int tm, tn;
+        tc_tile_coords(p, t, tm, tn);
+        const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
+        const int n_cta = tn * p.bn + static_cast<int>(rank) * bn_cta;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs)) {
+            tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = bar_full + 8u * s;
+          const uint32_t full_signal = (CG == 2) ? full0_leader + 8u * s : full_local;
+          if (leader) mbar_arrive_expect_tx(full_local, stage_bytes * CG);
+          const int k0 = kb * p.bk;
+          uint32_t dst = smem_base + s * stage_bytes;
+          for (int pl = 0; pl < p.a_planes; ++pl) {
+            for (int i = 0; i < p.a_boxes; ++i) {
+              int c0, c1;
+              if (p.a_mn_major) { c0 = m_cta + i * p.bk; c1 = k0; } else { c0 = k0; c1 = m_cta; }
+              if constexpr (CG == 2) tma_load_3d_pair(dst, &p.tm_a, full_signal, c0, c1, pl);
+              else tma_load_3d(dst, &p.tm_a, full_signal, c0, c1, pl);
+              dst += p.a_box_bytes;
+            }
+          }
+          for (int pl = 0; pl < p.b_planes; ++pl) {
+            for (int i = 0; i < p.b_boxes; ++i) {
+              int c0, c1;
+              if (p.b_mn_major) { c0 = n_cta + i * p.bk; c1 = k0; } else { c0 = k0; c1 = n_cta; }
+              if constexpr (CG == 2) tma_load_3d_pair(dst, &p.tm_b, full_signal, c0, c1, pl);
+              else tma_load_3d(dst, &p.tm_b, full_signal, c0, c1, pl);
+              dst += p.b_box_bytes;
+            }
+          }
+          ++issued;
+          if (++s == p.stages) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok && leader) {
+        // Let this CTA's copies in flight land before shared memory is given back: the full
+        // barrier of every stage that was armed completes when its bytes arrive.
+        const uint32_t n_back = issued < static_cast<uint32_t>(p.stages) ? issued : p.stages;
+        for (uint32_t b = 0; b < n_back; ++b) {
+          const uint32_t idx = issued - 1 - b;
+          const uint32_t st = idx % p.stages;
+          const uint32_t par = (idx / p.stages) & 1u;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(bar_full + 8u * st, par)) {
+            if (global_timer_ns() - t0 > 2000000ull) break;  // 2 ms per stage at most
+          }
+        }
+      }
+      if (!ok && !leader) {
+        // The peer's copies signal the leader's barriers; give them a bounded time to land.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && leader) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t acc_it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
+        const uint32_t as = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs)) {
+          tc_report(p.status, TC_ST_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_base = tmem_base + as * acc_cols;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs)) {
+            tc_report(p.status, TC_ST_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_smem = smem_base + s * stage_bytes;
+          const uint32_t b_smem = a_smem + p.a_planes * p.a_plane_bytes;
+#pragma unroll
+          for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
+            for (int ti = 0; ti < p.n_terms; ++ti) {
+              const TcTerm tr = p.terms[ti];
+              const uint64_t da = make_smem_desc(
+                  a_smem + tr.a_plane * p.a_plane_bytes + ks * p.a_kadv, p.a_lbo, p.a_sbo);
+              const uint64_t db = make_smem_desc(
+                  b_smem + tr.b_plane * p.b_plane_bytes + ks * p.b_kadv, p.b_lbo, p.b_sbo);
+              const uint32_t acc = (kb > 0 || ks > 0 || !tr.first) ? 1u : 0u;
+              umma<CG, TF32>(d_base + tr.acc_plane * p.bn, da, db,
+                             tr.negate_a ? p.idesc_neg : p.idesc, acc);
+            }
+          }
+          umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
+          if (++s == p.stages) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit<CG>(bar_tfull + 8u * as);  // accumulator complete
+      }
+      // Drain: nothing below may free TMEM or shared memory while an MMA is still running.
+      umma_commit_local<CG>(bar_drain);
+      {
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(bar_drain, 0)) {
+          if (global_timer_ns() - t0 > kTcWaitLimitNs) {
+            tc_report(p.status, TC_ST_TIMEOUT_DRAIN);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    const uint32_t tempty_leader = (CG == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
+      int tm, tn;
+      tc_tile_coords(p, t, tm, tn);
+      const int m = (tm * CG + static_cast<int>(rank)) * kTcTileM + q * 32 + lane;
+      const int n0 = tn * p.bn;
+      const uint32_t as = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      // all-or-nothing per warp: the TMEM loads below are warp-collective
+      const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * acc_cols;
+      const bool m_ok = m < p.M;
+      float bias_row = 0.0f;
+      if (p.bias_axis == TC_BIAS_ROW && m_ok) bias_row = p.bias[m];
+      for (int c = 0; c < p.bn; c += 32) {
+        uint32_t v[PLANES][32];
+#pragma unroll
+        for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_row + pl * p.bn + c, v[pl]);
+        tmem_ld_wait();
+        if (m_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + c + j;
+            if (n < p.N) {
+              float bias = bias_row;
+              if (p.bias_axis == TC_BIAS_COL) bias = p.bias[n];
+              float out[PLANES];
+#pragma unroll
+              for (int pl = 0; pl < PLANES; ++pl) {
+                float x = p.alpha * __uint_as_float(v[pl][j]);
+                if (p.beta != 0.0f) {
+                  const int64_t ci = (PLANES == 2 && p.c_plane == 0)
+                                         ? 2 * (m + n * p.ldc) + pl
+                                         : pl * p.c_plane + m + n * p.ldc;
+                  x += p.beta * tc_load_elem(p.C, ci, p.dtype_c);
+                }
+                if (pl == 0) x += bias;
+                out[pl] = tc_activation(x, p.act);
+              }
+              if (PLANES == 2 && p.d_plane == 0 && p.dtype_d == TC_F32) {
+                reinterpret_cast<float2*>(p.D)[m + n * p.ldd] = make_float2(out[0], out[PLANES - 1]);
+              } else {
+#pragma unroll
+                for (int pl = 0; pl < PLANES; ++pl) {
+                  const int64_t di = (PLANES == 2 && p.d_plane == 0)
+                                         ? 2 * (m + n * p.ldd) + pl
+                                         : pl * p.d_plane + m + n * p.ldd;
+                  tc_store_elem(p.D, di, p.dtype_d, out[pl]);
+                }
+              }
+            }
+          }
+        }
+      }
+      // Accumulator stage can be overwritten once every warp of the pair has read it.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * as);
+        else mbar_arrive(bar_tempty + 8u * as);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer may still read this CTA's smem / barriers
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, p.tmem_cols);
+  }
+}
+
+}  // namespace gk

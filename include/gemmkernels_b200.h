@@ -1,0 +1,170 @@
+/*
+ * gemmkernels_b200 — C ABI of the Blackwell (sm_100a) GEMM engine that sits behind the
+ * GemmKernels.jl API.  Plain pointers and sizes only; every pointer named "device" is a CUDA
+ * device pointer owned by the caller (never freed or retained past the call).  Work is enqueued
+ * asynchronously on the caller's stream in the caller's current context; no call synchronises
+ * unless its comment says so.  All functions return a gk_status; gk_last_error_message() gives
+ * the text of the last failure on the calling thread.
+ *
+ * Reference interface replaced (paths inside the GemmKernels.jl repository):
+ *   gk_gemm            the kernel launch in GemmKernels.matmul, src/matmul.jl:38-43, together with
+ *                      the device code it launches (src/kernel.jl:10-574, src/operator.jl,
+ *                      src/layout.jl, src/epilogue.jl:14-73, src/transform.jl:19-30)
+ *   gk_gemm_query      the launch-geometry and limit checks of src/matmul.jl:24-41
+ *   gk_contract        the tensor-contraction driver benchmarks/tensor-contractions/run.jl:88-131
+ *   gk_create/destroy  no counterpart (CUDA.jl keeps the context); holds per-device caches
+ */
+#ifndef GEMMKERNELS_B200_H
+#define GEMMKERNELS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GK_API __attribute__((visibility("default")))
+#else
+#define GK_API
+#endif
+
+#define GK_VERSION_MAJOR 0
+#define GK_VERSION_MINOR 1
+
+typedef struct gk_handle_s* gk_handle;
+typedef void* gk_stream; /* a CUstream / cudaStream_t; NULL = the legacy default stream */
+
+typedef enum gk_status {
+  GK_OK = 0,
+  GK_ERR_INVALID_CONFIG = 1,     /* maps to GemmKernels.ConfigError (src/config.jl:78-82)        */
+  GK_ERR_UNSUPPORTED = 2,        /* a Transform/Epilogue/dtype outside the enumerated set         */
+  GK_ERR_DIMENSION_MISMATCH = 3, /* maps to DimensionMismatch (src/matmul.jl:75-77)               */
+  GK_ERR_CUDA = 4,               /* a CUDA runtime / driver call failed                           */
+  GK_ERR_TIMEOUT = 5,            /* a bounded device-side wait gave up; the context stays usable  */
+  GK_ERR_INVALID_ARGUMENT = 6
+} gk_status;
+
+typedef enum gk_dtype {
+  GK_F16 = 0,
+  GK_BF16 = 1,
+  GK_F32 = 2,
+  GK_F64 = 3,
+  GK_I16 = 4,
+  GK_I32 = 5,
+  GK_I64 = 6,
+  GK_TF32 = 7 /* compute type only: FP32 storage read by the tensor cores as TF32 */
+} gk_dtype;
+
+/* Operator.* of src/operator.jl.  TCGEN05 replaces the WMMA operators (operator.jl:163-372);
+ * FPU is FPUOp (operator.jl:35-153), FPU_TROPICAL is TropicalFPUOp (max-plus). */
+typedef enum gk_operator {
+  GK_OP_AUTO = 0,
+  GK_OP_TCGEN05 = 1,
+  GK_OP_FPU = 2,
+  GK_OP_FPU_TROPICAL = 3
+} gk_operator;
+
+/* Number system of the product: real, complex (WMMAComplexOp, operator.jl:251-314) or dual
+ * numbers (WMMADualOp, operator.jl:320-372).  Complex and dual operands have two planes. */
+typedef enum gk_number { GK_REAL = 0, GK_COMPLEX = 1, GK_DUAL = 2 } gk_number;
+
+/* Per-operand layout kind.  DENSE covers ColMajor/RowMajor/UnsafeAligned* (layout.jl:111-270);
+ * ZERO is Layout.Zero (layout.jl:82-89): the operand is not read; DIAGONAL is Layout.Diagonal
+ * (layout.jl:225-236): A is a length-M vector holding the diagonal of a square matrix. */
+typedef enum gk_layout_kind { GK_LAYOUT_DENSE = 0, GK_LAYOUT_ZERO = 1, GK_LAYOUT_DIAGONAL = 2 } gk_layout_kind;
+
+typedef enum gk_activation { GK_ACT_NONE = 0, GK_ACT_RELU = 1, GK_ACT_GELU = 2 } gk_activation;
+
+/* Bias axis.  COL is the reference's Epilogue.Bias (epilogue.jl:44-52: one value per column of D,
+ * length N); ROW is one value per row of D (length M). */
+typedef enum gk_bias_axis { GK_BIAS_NONE = 0, GK_BIAS_ROW = 1, GK_BIAS_COL = 2 } gk_bias_axis;
+
+/* CTASwizzle.* of src/cta-swizzle.jl:26-160, reinterpreted as raster orders of the persistent
+ * tile scheduler. */
+typedef enum gk_raster {
+  GK_RASTER_AUTO = 0,
+  GK_RASTER_IDENTITY = 1,      /* column-major walk over tiles                       */
+  GK_RASTER_HORIZONTAL = 2,    /* HorizontallyTiled{T}: bands of T tiles along N     */
+  GK_RASTER_VERTICAL = 3,      /* VerticallyTiled{T}: bands of T tiles along M       */
+  GK_RASTER_LEBESGUE = 4       /* LebesgueCurve: Z-order                             */
+} gk_raster;
+
+/*
+ * D = act( alpha * op(A) * op(B) + beta * C + bias ),  op(X) = X or X^T.
+ * All matrices are column-major (Julia order): element (i, j) of a stored matrix X is at
+ * X[i + j * ldx].  trans_a = 0: A is stored M x K; trans_a = 1: A is stored K x M (the reference's
+ * RowMajor global layout).  Likewise trans_b with K x N / N x K.  C and D are M x N and may alias.
+ * For GK_COMPLEX / GK_DUAL, plane_x is the element distance between the two planes of operand x
+ * (real/imaginary, or value/derivative); plane_x = 0 means interleaved pairs, in which case ldx
+ * counts pairs.  Interleaved A/B need a scratch buffer: see gk_gemm_workspace_size.
+ */
+typedef struct gk_gemm_desc {
+  uint32_t struct_size; /* sizeof(gk_gemm_desc), for ABI evolution */
+  int32_t number;       /* gk_number */
+  int64_t m, n, k;
+  int32_t trans_a, trans_b;
+  int32_t dtype_a, dtype_b, dtype_c, dtype_d; /* gk_dtype of the stored elements */
+  int32_t compute;      /* gk_dtype the multiply runs in: F16/BF16/TF32 (TCGEN05), others (FPU) */
+  int32_t op;           /* gk_operator */
+  int64_t lda, ldb, ldc, ldd;
+  int64_t plane_a, plane_b, plane_c, plane_d;
+  int32_t layout_a, layout_b, layout_c; /* gk_layout_kind */
+  int32_t raster;       /* gk_raster */
+  double alpha, beta;
+  /* Tuning overrides; 0 = use the built-in table. */
+  int32_t tile_n;       /* 32..256, multiple of 32 (per CTA pair when cta_group = 2) */
+  int32_t cta_group;    /* 1 or 2 */
+  int32_t stages;       /* shared-memory pipeline depth */
+  int32_t raster_group; /* T of the tiled rasters */
+  int32_t max_ctas;     /* cap on the persistent grid */
+  int32_t reserved[3];
+} gk_gemm_desc;
+
+typedef struct gk_epilogue_desc {
+  uint32_t struct_size;
+  int32_t bias_axis;   /* gk_bias_axis */
+  const float* bias;   /* device, FP32, length M (ROW) or N (COL) */
+  int32_t activation;  /* gk_activation, applied last (the reference's shared_to_global_d hook) */
+  int32_t reserved[3];
+} gk_epilogue_desc;
+
+typedef struct gk_gemm_plan {
+  int32_t kernel;       /* 1 = tcgen05, 2 = FPU (SIMT FFMA), 3 = generic SIMT, 4 = diagonal scale */
+  int32_t grid, block, cluster;
+  int32_t smem_bytes, tmem_columns;
+  int32_t tile_m, tile_n, tile_k, stages;
+  int64_t workspace_bytes;
+} gk_gemm_plan;
+
+/* Version of the loaded library: major * 1000 + minor. */
+GK_API int32_t gk_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). Never NULL. */
+GK_API const char* gk_last_error_message(void);
+
+/* Creates the per-device state (SM count, driver entry points, a host-visible status word that
+ * device-side waits report into).  Uses the current device.  Allocates; call once, not per GEMM. */
+GK_API gk_status gk_create(gk_handle* out);
+GK_API gk_status gk_destroy(gk_handle h);
+
+/* Reads and clears the device-side status word without synchronising: GK_OK, or GK_ERR_TIMEOUT if
+ * a kernel launched through this handle abandoned a wait since the last call. */
+GK_API gk_status gk_poll_status(gk_handle h, int32_t* raw_code);
+
+/* Fills *plan with what gk_gemm would launch for this descriptor; launches nothing. */
+GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
+                        gk_gemm_plan* plan);
+
+/* Enqueues one GEMM on `stream`.  a, b, c, d are device pointers (c may be NULL when beta == 0 or
+ * layout_c is ZERO; c == d is allowed).  epi may be NULL.  workspace is a device buffer of at
+ * least plan.workspace_bytes bytes (NULL when that is 0). */
+GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
+                  const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
+                  gk_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMMKERNELS_B200_H */
