@@ -226,7 +226,6 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
                   gk_stream stream) {
   clear_error();
-  (void)workspace;
   if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
   gk_status s = validate_desc(desc, epi);
   if (s != GK_OK) return s;
@@ -243,6 +242,10 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     if (s != GK_OK) return s;
     s = tc_encode_maps(h, *desc, a, b, &L);
     if (s != GK_OK) return s;
+    if (L.params.debug & 8) {
+      if (!workspace) return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace");
+      L.params.dbg_out = static_cast<long long*>(workspace);
+    }
     return tc_launch(L, st);
   }
   return launch_simt(*desc, epi, a, b, c, d, st);

@@ -93,12 +93,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  uint64_t t0 = 0;
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 31u) == 0u) {
+    if ((++it & 15u) == 0u) {  // each try_wait already suspends for a while in hardware
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > limit_ns) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
@@ -292,19 +294,22 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor for 128-byte swizzled operands (the only mode used here).
+// Shared-memory matrix descriptor, split in two 32-bit halves so that the issuing thread only
+// adds to the low half while it walks stages and k-steps.
 //   K-major  operand: rows of 128 B (one k-block), 8-row groups `sbo` bytes apart.
-//   MN-major operand: 128-B runs of the M/N index, 8 consecutive k rows per 1024-B atom,
-//                     atoms `sbo` bytes apart along K and `lbo` bytes apart along M/N.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // SWIZZLE_128B
-  return d;
+//   MN-major operand: 128-B runs of the M/N index, a group of consecutive k rows per swizzle
+//                     atom, atoms `sbo` bytes apart along K and `lbo` bytes apart along M/N.
+// `swizzle_type` is the descriptor's layout field: 2 = 128-byte swizzle with 16-byte units,
+// 1 = 128-byte swizzle with 32-byte units (the only mode for MN-major 32-bit operands).
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t sbo_bytes, uint32_t swizzle_type) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) /* sm_100 descriptor version */ |
+         (swizzle_type << 29);
+}
+__device__ __forceinline__ uint64_t smem_desc(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
 }  // namespace gk

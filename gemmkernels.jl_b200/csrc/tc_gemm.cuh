@@ -9,8 +9,9 @@
 // next.  With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of
 // A and its own half of B's columns (no multicast), and the pair leader issues the MMAs for both.
 //
-// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warp 2 = TMEM allocator,
-// warp 3 = idle, warps 4..7 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Warp roles (256 threads): warp 0 = TMA producer for A, warp 1 = MMA issuer, warp 2 = TMEM
+// allocator, warp 3 = TMA producer for B, warps 4..7 = epilogue (warp w reads TMEM lanes
+// 32*(w%4)..+31).
 //
 // Every barrier wait is bounded (ptx.cuh: mbar_wait).  When a wait gives up, the CTA raises a
 // shared abort flag, all roles leave their loops, in-flight copies and MMAs are drained with
@@ -66,6 +67,7 @@ struct TcParams {
   TcTerm terms[4];
   uint32_t idesc, idesc_neg;  // instruction descriptors (second one negates A)
   uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
+  uint32_t a_swz, b_swz;      // descriptor swizzle field per operand (ptx.cuh: smem_desc_hi)
   uint32_t tmem_cols;         // power of two >= 2 * acc_planes * bn
   // epilogue
   const void* C;
@@ -77,6 +79,9 @@ struct TcParams {
   const float* bias;
   int32_t bias_axis, act;
   int32_t* status;
+  int32_t debug;  // measurement aids, 0 in production: 1 = no TMA (barriers only), 2 = no MMA,
+                  // 8 = per-role cycle counters written to dbg_out[blockIdx.x * 16 + i]
+  long long* dbg_out;
 };
 
 // The status word may live in host-mapped memory: plain stores, first error wins.
@@ -180,122 +185,184 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
   const int bn_cta = p.bn / CG;
   const uint32_t acc_cols = PLANES * p.bn;  // TMEM columns per accumulator stage
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      const uint32_t full0_leader = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
+  if (warp == 0 || warp == 3) {
+    // ------------------------------------------------------------------ TMA producers
+    // Warp 0 loads A, warp 3 loads B: issuing a copy costs its thread on the order of 100
+    // cycles, and splitting the operands keeps each producer loop well under one k-block of MMA.
+    // One lane per TMA box: every lane runs the same short instruction stream with its own
+    // destination and coordinates, so the cost per k-block does not grow with the box count.
+    // (Measured on B200: issuing from one elected lane of a converged warp with warp-uniform
+    // operands cost ~3x more cycles per copy than this form.)
+    {
+      const bool is_a = warp == 0;
+      const int n_boxes = is_a ? p.a_planes * p.a_boxes : p.b_planes * p.b_boxes;
+      const bool active = lane < n_boxes;
+      const int bi = lane;
+      const int per_plane = is_a ? p.a_boxes : p.b_boxes;
+      const int pl = active ? bi / per_plane : 0;
+      const int bx = active ? bi % per_plane : 0;
+      const bool mn_major = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
+      const uint32_t dst_off =
+          is_a ? pl * p.a_plane_bytes + bx * p.a_box_bytes
+               : p.a_planes * p.a_plane_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes;
+      const void* tmap = is_a ? static_cast<const void*>(&p.tm_a) : static_cast<const void*>(&p.tm_b);
+      const int mn_add = mn_major ? bx * p.bk : 0;
+      const uint32_t full0_signal = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
+      const uint32_t tx_bytes = stage_bytes * CG;
       int s = 0;
       uint32_t ph = 0;
       uint32_t issued = 0;  // k-blocks issued so far by this CTA
       bool ok = true;
+      const bool prof = (p.debug & 8) != 0;
+      long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
         tc_tile_coords(p, t, tm, tn);
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
         const int n_cta = tn * p.bn + static_cast<int>(rank) * bn_cta;
+        const int mn = (is_a ? m_cta : n_cta) + mn_add;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs)) {
-            tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
+          if (prof) pt0 = clock64();
+          const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
+          if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
             ok = false;
             break;
           }
-          const uint32_t full_local = bar_full + 8u * s;
-          const uint32_t full_signal = (CG == 2) ? full0_leader + 8u * s : full_local;
-          if (leader) mbar_arrive_expect_tx(full_local, stage_bytes * CG);
-          const int k0 = kb * p.bk;
-          uint32_t dst = smem_base + s * stage_bytes;
-          for (int pl = 0; pl < p.a_planes; ++pl) {
-            for (int i = 0; i < p.a_boxes; ++i) {
-              int c0, c1;
-              if (p.a_mn_major) { c0 = m_cta + i * p.bk; c1 = k0; } else { c0 = k0; c1 = m_cta; }
-              if constexpr (CG == 2) tma_load_3d_pair(dst, &p.tm_a, full_signal, c0, c1, pl);
-              else tma_load_3d(dst, &p.tm_a, full_signal, c0, c1, pl);
-              dst += p.a_box_bytes;
-            }
-          }
-          for (int pl = 0; pl < p.b_planes; ++pl) {
-            for (int i = 0; i < p.b_boxes; ++i) {
-              int c0, c1;
-              if (p.b_mn_major) { c0 = n_cta + i * p.bk; c1 = k0; } else { c0 = k0; c1 = n_cta; }
-              if constexpr (CG == 2) tma_load_3d_pair(dst, &p.tm_b, full_signal, c0, c1, pl);
-              else tma_load_3d(dst, &p.tm_b, full_signal, c0, c1, pl);
-              dst += p.b_box_bytes;
+          if (p.debug & 1) {
+            if (lane == 0 && leader && is_a) mbar_arrive(bar_full + 8u * s);
+          } else {
+            // Bytes may be counted on the barrier before they are expected: the phase cannot
+            // complete until the A producer's arrival below.
+            if (lane == 0 && leader && is_a) mbar_arrive_expect_tx(bar_full + 8u * s, tx_bytes);
+            __syncwarp();
+            if (active) {
+              const int k0 = kb * p.bk;
+              const int c0 = mn_major ? mn : k0;
+              const int c1 = mn_major ? k0 : mn;
+              const uint32_t dst = smem_base + s * stage_bytes + dst_off;
+              if constexpr (CG == 2) tma_load_3d_pair(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
+              else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
             }
           }
           ++issued;
           if (++s == p.stages) { s = 0; ph ^= 1u; }
+          if (prof) pi += clock64() - pt1;
         }
       }
-      if (!ok && leader) {
-        // Let this CTA's copies in flight land before shared memory is given back: the full
-        // barrier of every stage that was armed completes when its bytes arrive.
-        const uint32_t n_back = issued < static_cast<uint32_t>(p.stages) ? issued : p.stages;
-        for (uint32_t b = 0; b < n_back; ++b) {
-          const uint32_t idx = issued - 1 - b;
-          const uint32_t st = idx % p.stages;
-          const uint32_t par = (idx / p.stages) & 1u;
-          const uint64_t t0 = global_timer_ns();
-          while (!mbar_try_wait(bar_full + 8u * st, par)) {
-            if (global_timer_ns() - t0 > 2000000ull) break;  // 2 ms per stage at most
+      if (prof && lane == 0) {
+        p.dbg_out[blockIdx.x * 16 + (is_a ? 0 : 9)] = pw;
+        p.dbg_out[blockIdx.x * 16 + (is_a ? 1 : 10)] = pi;
+      }
+      if (!ok && lane == 0) {
+        if (leader) {
+          // Let this CTA's copies in flight land before shared memory is given back: the full
+          // barrier of every stage that was armed completes when its bytes arrive.
+          const uint32_t n_back = issued < static_cast<uint32_t>(p.stages) ? issued : p.stages;
+          for (uint32_t b = 0; b < n_back; ++b) {
+            const uint32_t idx = issued - 1 - b;
+            const uint32_t st = idx % p.stages;
+            const uint32_t par = (idx / p.stages) & 1u;
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait(bar_full + 8u * st, par)) {
+              if (global_timer_ns() - t0 > 2000000ull) break;  // 2 ms per stage at most
+            }
           }
+        } else {
+          // The peer's copies signal the leader's barriers; give them a bounded time to land.
+          const uint64_t t0 = global_timer_ns();
+          while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
         }
-      }
-      if (!ok && !leader) {
-        // The peer's copies signal the leader's barriers; give them a bounded time to land.
-        const uint64_t t0 = global_timer_ns();
-        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && leader) {
+    // Same discipline as the producer: the warp stays converged, descriptors are computed from
+    // warp-uniform values (tcgen05.mma takes them from the uniform datapath), and only the
+    // instruction itself is predicated on the elected lane.
+    if (leader) {
+      constexpr int kMaxTerms = (PLANES == 1) ? 1 : 4;
+      const bool elected = elect_one();
+      const uint32_t hi_a = smem_desc_hi(p.a_sbo, p.a_swz);
+      const uint32_t hi_b = smem_desc_hi(p.b_sbo, p.b_swz);
+      uint32_t t_a[kMaxTerms], t_b[kMaxTerms], t_d[kMaxTerms], t_id[kMaxTerms], t_keep[kMaxTerms];
+#pragma unroll
+      for (int ti = 0; ti < kMaxTerms; ++ti) {
+        const TcTerm tr = p.terms[ti < p.n_terms ? ti : 0];
+        t_a[ti] = smem_desc_lo(tr.a_plane * p.a_plane_bytes, p.a_lbo);
+        t_b[ti] = smem_desc_lo(p.a_planes * p.a_plane_bytes + tr.b_plane * p.b_plane_bytes, p.b_lbo);
+        t_d[ti] = tr.acc_plane * p.bn;
+        t_id[ti] = tr.negate_a ? p.idesc_neg : p.idesc;
+        t_keep[ti] = tr.first ? 0u : 1u;
+      }
+      const uint32_t base16 = (smem_base & 0x3FFFFu) >> 4;
+      const uint32_t stage16 = stage_bytes >> 4;
+      const uint32_t a_k16 = p.a_kadv >> 4, b_k16 = p.b_kadv >> 4;
+      const int n_terms = (p.debug & 2) ? 0 : p.n_terms;
       int s = 0;
+      uint32_t s16 = base16;
       uint32_t ph = 0;
       uint32_t acc_it = 0;
       bool ok = true;
+      const bool prof = (p.debug & 8) != 0;
+      long long mw = 0, mi = 0, mt = 0, t0 = 0, t1 = 0;
+      const long long k_start = clock64();
+      const uint64_t g_start = global_timer_ns();
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
         const uint32_t as = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
-        if (!mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs)) {
-          tc_report(p.status, TC_ST_TIMEOUT_MMA);
+        if (prof) t0 = clock64();
+        const bool tgot = mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs);
+        if (prof) mt += clock64() - t0;
+        if (!__all_sync(0xffffffffu, tgot)) {
+          if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_MMA);
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_base = tmem_base + as * acc_cols;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs)) {
-            tc_report(p.status, TC_ST_TIMEOUT_MMA);
+          if (prof) t0 = clock64();
+          const bool fgot = mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs);
+          if (prof) { t1 = clock64(); mw += t1 - t0; }
+          if (!__all_sync(0xffffffffu, fgot)) {
+            if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_MMA);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_smem = smem_base + s * stage_bytes;
-          const uint32_t b_smem = a_smem + p.a_planes * p.a_plane_bytes;
 #pragma unroll
           for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
-            for (int ti = 0; ti < p.n_terms; ++ti) {
-              const TcTerm tr = p.terms[ti];
-              const uint64_t da = make_smem_desc(
-                  a_smem + tr.a_plane * p.a_plane_bytes + ks * p.a_kadv, p.a_lbo, p.a_sbo);
-              const uint64_t db = make_smem_desc(
-                  b_smem + tr.b_plane * p.b_plane_bytes + ks * p.b_kadv, p.b_lbo, p.b_sbo);
-              const uint32_t acc = (kb > 0 || ks > 0 || !tr.first) ? 1u : 0u;
-              umma<CG, TF32>(d_base + tr.acc_plane * p.bn, da, db,
-                             tr.negate_a ? p.idesc_neg : p.idesc, acc);
+#pragma unroll
+            for (int ti = 0; ti < kMaxTerms; ++ti) {
+              if (ti < n_terms) {
+                const uint64_t da = smem_desc(s16 + t_a[ti] + ks * a_k16, hi_a);
+                const uint64_t db = smem_desc(s16 + t_b[ti] + ks * b_k16, hi_b);
+                const uint32_t acc = (kb | ks) ? 1u : t_keep[ti];
+                if (elected) umma<CG, TF32>(d_base + t_d[ti], da, db, t_id[ti], acc);
+              }
             }
           }
-          umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
-          if (++s == p.stages) { s = 0; ph ^= 1u; }
+          if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
+          ++s; s16 += stage16;
+          if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }
+          if (prof) mi += clock64() - t1;
         }
-        if (ok) umma_commit<CG>(bar_tfull + 8u * as);  // accumulator complete
+        if (ok && elected) umma_commit<CG>(bar_tfull + 8u * as);  // accumulator complete
+      }
+      if (prof && lane == 0) {
+        long long* o = p.dbg_out + blockIdx.x * 16;
+        o[2] = mw; o[3] = mi; o[4] = mt; o[5] = clock64() - k_start;
+        o[6] = static_cast<long long>(global_timer_ns() - g_start);
       }
       // Drain: nothing below may free TMEM or shared memory while an MMA is still running.
-      umma_commit_local<CG>(bar_drain);
-      {
-        const uint64_t t0 = global_timer_ns();
+      // The commit must come from the thread that issued the MMAs.
+      if (elected) {
+        umma_commit_local<CG>(bar_drain);
+        const uint64_t d0 = global_timer_ns();
         while (!mbar_try_wait(bar_drain, 0)) {
-          if (global_timer_ns() - t0 > kTcWaitLimitNs) {
+          if (global_timer_ns() - d0 > kTcWaitLimitNs) {
             tc_report(p.status, TC_ST_TIMEOUT_DRAIN);
             break;
           }
@@ -308,6 +375,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     const uint32_t tempty_leader = (CG == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
     uint32_t acc_it = 0;
     bool ok = true;
+    const bool fast_store = PLANES == 1 && p.dtype_d == TC_F32 && p.beta == 0.0f &&
+                            p.bias_axis != TC_BIAS_COL && p.act != TC_ACT_GELU;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;
       tc_tile_coords(p, t, tm, tn);
@@ -316,7 +385,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       // all-or-nothing per warp: the TMEM loads below are warp-collective
+      const long long e0 = (p.debug & 8) ? clock64() : 0;
       const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);
+      const long long e1 = (p.debug & 8) ? clock64() : 0;
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_EPILOGUE);
         ok = false;
@@ -332,36 +403,56 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
 #pragma unroll
         for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_row + pl * p.bn + c, v[pl]);
         tmem_ld_wait();
-        if (m_ok) {
+        const int ncols = p.N - (n0 + c);  // columns of this chunk inside the matrix (may be <= 0)
+        if (!m_ok || ncols <= 0) continue;
+        if (fast_store) {
+          // FP32 output, no C, no per-column bias: one FMA (+ max) and one coalesced store per
+          // column; a warp writes 32 consecutive rows = 128 bytes of a column of D.
+          float* dp = static_cast<float*>(p.D) + m + static_cast<int64_t>(n0 + c) * p.ldd;
+          if (ncols >= 32) {
+            if (p.act == TC_ACT_RELU) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = n0 + c + j;
-            if (n < p.N) {
+              for (int j = 0; j < 32; ++j)
+                dp[j * p.ldd] = fmaxf(fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row), 0.0f);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                dp[j * p.ldd] = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < ncols) {
+                const float x = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
+                dp[j * p.ldd] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
+              }
+            }
+          }
+        } else {
+          const bool c_pairs = PLANES == 2 && p.c_plane == 0;
+          const bool d_pairs = PLANES == 2 && p.d_plane == 0;
+          int64_t ci = m + static_cast<int64_t>(n0 + c) * p.ldc;  // element (m, n) of one plane
+          int64_t di = m + static_cast<int64_t>(n0 + c) * p.ldd;
+#pragma unroll
+          for (int j = 0; j < 32; ++j, ci += p.ldc, di += p.ldd) {
+            if (j < ncols) {
               float bias = bias_row;
-              if (p.bias_axis == TC_BIAS_COL) bias = p.bias[n];
+              if (p.bias_axis == TC_BIAS_COL) bias = p.bias[n0 + c + j];
               float out[PLANES];
 #pragma unroll
               for (int pl = 0; pl < PLANES; ++pl) {
                 float x = p.alpha * __uint_as_float(v[pl][j]);
-                if (p.beta != 0.0f) {
-                  const int64_t ci = (PLANES == 2 && p.c_plane == 0)
-                                         ? 2 * (m + n * p.ldc) + pl
-                                         : pl * p.c_plane + m + n * p.ldc;
-                  x += p.beta * tc_load_elem(p.C, ci, p.dtype_c);
-                }
+                if (p.beta != 0.0f)
+                  x += p.beta * tc_load_elem(p.C, c_pairs ? 2 * ci + pl : pl * p.c_plane + ci, p.dtype_c);
                 if (pl == 0) x += bias;
                 out[pl] = tc_activation(x, p.act);
               }
-              if (PLANES == 2 && p.d_plane == 0 && p.dtype_d == TC_F32) {
-                reinterpret_cast<float2*>(p.D)[m + n * p.ldd] = make_float2(out[0], out[PLANES - 1]);
+              if (d_pairs && p.dtype_d == TC_F32) {
+                reinterpret_cast<float2*>(p.D)[di] = make_float2(out[0], out[PLANES - 1]);
               } else {
 #pragma unroll
-                for (int pl = 0; pl < PLANES; ++pl) {
-                  const int64_t di = (PLANES == 2 && p.d_plane == 0)
-                                         ? 2 * (m + n * p.ldd) + pl
-                                         : pl * p.d_plane + m + n * p.ldd;
-                  tc_store_elem(p.D, di, p.dtype_d, out[pl]);
-                }
+                for (int pl = 0; pl < PLANES; ++pl)
+                  tc_store_elem(p.D, d_pairs ? 2 * di + pl : pl * p.d_plane + di, p.dtype_d, out[pl]);
               }
             }
           }
@@ -373,6 +464,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       if (lane == 0) {
         if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * as);
         else mbar_arrive(bar_tempty + 8u * as);
+      }
+      if ((p.debug & 8) && warp == 4 && lane == 0) {
+        p.dbg_out[blockIdx.x * 16 + 7] += e1 - e0;
+        p.dbg_out[blockIdx.x * 16 + 8] += clock64() - e1;
       }
     }
   }

@@ -46,7 +46,8 @@ bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::strin
 
 static gk_status encode_operand(gk_handle h, CUtensorMap* tm, const void* base, int32_t dt,
                                 int64_t contiguous_extent, int64_t strided_extent, int64_t ld,
-                                int planes, int64_t plane_stride, int box_contig, int box_strided) {
+                                int planes, int64_t plane_stride, int box_contig, int box_strided,
+                                bool atom32) {
   const int es = dtype_size(dt);
   CUtensorMapDataType tdt = dt == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                             : dt == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -59,7 +60,8 @@ static gk_status encode_operand(gk_handle h, CUtensorMap* tm, const void* base, 
   cuuint32_t box[3] = {static_cast<cuuint32_t>(box_contig), static_cast<cuuint32_t>(box_strided), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = h->encode_tiled(tm, tdt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(GK_ERR_INVALID_CONFIG,
@@ -154,21 +156,27 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
   const int mn_box_bytes = p.bk * p.bk * es;  // MN-major box: 128 B of M/N by one k-block
   p.a_plane_bytes = kTcTileM * kTcKBytes;
   p.b_plane_bytes = bn_cta * kTcKBytes;
+  // MN-major operands: 16-bit types use the plain 128-byte swizzle (atoms of 8 k rows, 1024 B);
+  // 32-bit types must use the 128-byte swizzle with 32-byte units (atoms of 4 k rows, 512 B).
+  // Either way one MMA consumes 32 / es rows of K, i.e. 2048 B (16-bit) or 1024 B (32-bit).
+  const uint32_t mn_sbo = es == 4 ? 512 : 1024;
+  const uint32_t mn_swz = es == 4 ? 1 : 2;
+  const uint32_t mn_kadv = (32 / es) * 128;
   if (p.a_mn_major) {
     p.a_boxes = kTcTileM / p.bk; p.a_box_bytes = mn_box_bytes;
-    p.a_lbo = mn_box_bytes; p.a_sbo = 1024; p.a_kadv = (32 / es / 8) * 1024;
+    p.a_lbo = mn_box_bytes; p.a_sbo = mn_sbo; p.a_kadv = mn_kadv; p.a_swz = mn_swz;
   } else {
     p.a_boxes = 1; p.a_box_bytes = p.a_plane_bytes;
-    p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = 32;
+    p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = 32; p.a_swz = 2;
   }
   if (p.b_mn_major) {
     if (bn_cta % p.bk)
       return set_error(GK_ERR_INVALID_CONFIG, "tile_n = %d too small for a transposed B of this type", bn);
     p.b_boxes = bn_cta / p.bk; p.b_box_bytes = mn_box_bytes;
-    p.b_lbo = mn_box_bytes; p.b_sbo = 1024; p.b_kadv = (32 / es / 8) * 1024;
+    p.b_lbo = mn_box_bytes; p.b_sbo = mn_sbo; p.b_kadv = mn_kadv; p.b_swz = mn_swz;
   } else {
     p.b_boxes = 1; p.b_box_bytes = p.b_plane_bytes;
-    p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32;
+    p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32; p.b_swz = 2;
   }
 
   // terms of the product
@@ -242,6 +250,8 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
     p.act = epi->activation;
   }
   p.status = h->status_dev;
+  p.debug = d.reserved[0];
+  p.dbg_out = nullptr;
 
   out->cg = cg;
   out->planes = planes;
@@ -308,14 +318,14 @@ gk_status tc_encode_maps(gk_handle h, const gk_gemm_desc& d, const void* a, cons
   const int bn_cta = p.bn / L->cg;
   gk_status s;
   if (p.a_mn_major)
-    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.m, d.k, d.lda, planes, d.plane_a, p.bk, p.bk);
+    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.m, d.k, d.lda, planes, d.plane_a, p.bk, p.bk, p.a_swz == 1);
   else
-    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.k, d.m, d.lda, planes, d.plane_a, p.bk, kTcTileM);
+    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.k, d.m, d.lda, planes, d.plane_a, p.bk, kTcTileM, false);
   if (s != GK_OK) return s;
   if (p.b_mn_major)
-    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.n, d.k, d.ldb, planes, d.plane_b, p.bk, p.bk);
+    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.n, d.k, d.ldb, planes, d.plane_b, p.bk, p.bk, p.b_swz == 1);
   else
-    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.k, d.n, d.ldb, planes, d.plane_b, p.bk, bn_cta);
+    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.k, d.n, d.ldb, planes, d.plane_b, p.bk, bn_cta, false);
   return s;
 }
 
