@@ -63,12 +63,22 @@ static gk_status validate_desc(const gk_gemm_desc* d, const gk_epilogue_desc* ep
 
 // Which kernel family serves this descriptor: 1 tcgen05, 3 generic SIMT.
 static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+  // Nothing to multiply (Layout.Zero operands, alpha == 0, K == 0): D = act(beta * C + bias),
+  // which the generic kernel does without touching A or B.
+  const bool no_product = d.layout_a == GK_LAYOUT_ZERO || d.layout_b == GK_LAYOUT_ZERO ||
+                          d.alpha == 0.0 || d.k == 0;
+  if (no_product && d.number == GK_REAL) return 3;
   const bool tc_types = (d.compute == GK_F16 || d.compute == GK_BF16 || d.compute == GK_TF32);
   if (d.op == GK_OP_TCGEN05 || (d.op == GK_OP_AUTO && tc_types)) {
     if (tc_eligible(d, a, b, why)) return 1;
     if (d.number != GK_REAL) return -1;        // no SIMT complex/dual kernel
     if (d.compute == GK_TF32) return -1;       // an FP32 SIMT result is not a TF32 result: refuse
-    return 3;                                  // FP16/BF16 inputs, FP32 accumulation in SIMT
+    // Only a TMA obstacle (alignment, leading dimension) may reroute a tensor-core request, and
+    // only for 16-bit inputs, whose FP32-accumulated SIMT product meets the same tolerance.
+    const bool f16 = d.dtype_a == GK_F16 && d.dtype_b == GK_F16 && d.compute == GK_F16;
+    const bool bf16 = d.dtype_a == GK_BF16 && d.dtype_b == GK_BF16 && d.compute == GK_BF16;
+    if (!(f16 || bf16) || d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE) return -1;
+    return 3;
   }
   if (d.number != GK_REAL) { if (why) *why = "complex and dual products need the TCGen05Operator"; return -1; }
   return 3;

@@ -79,7 +79,8 @@ struct TcParams {
   const float* bias;
   int32_t bias_axis, act;
   int32_t* status;
-  int32_t debug;  // measurement aids, 0 in production: 1 = no TMA (barriers only), 2 = no MMA,
+  int32_t debug;  // measurement/test aids, 0 in production: 1 = no TMA (barriers only),
+                  // 2 = no MMA, 4 = producers issue nothing (lets the bounded waits run out),
                   // 8 = per-role cycle counters written to dbg_out[blockIdx.x * 16 + i]
   long long* dbg_out;
 };
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       bool ok = true;
       const bool prof = (p.debug & 8) != 0;
       long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
         int tm, tn;
         tc_tile_coords(p, t, tm, tn);
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;

@@ -96,6 +96,8 @@ static int stage_bytes_for(int cg, int bn, int a_planes, int b_planes) {
 // Picks (cta_group, tile_n): fewest "tile-time" units over the persistent grid, where a larger
 // tile is worth more per unit time (operand reuse) but quantises worse on small problems.
 static void choose_tile(const gk_gemm_desc& d, int sm_count, int planes, int* cg_out, int* bn_out) {
+  // a transposed (N-contiguous) B is loaded in boxes of 128 bytes of N per CTA
+  const int n_unit = d.trans_b ? kTcKBytes / dtype_size(d.dtype_b) : 8;
   struct Cand { int cg, bn; double eff; };
   static const Cand cands[] = {{2, 256, 1.00}, {1, 256, 0.92}, {2, 128, 0.80},
                                {1, 128, 0.74}, {1, 64, 0.50},  {1, 32, 0.30}};
@@ -103,6 +105,7 @@ static void choose_tile(const gk_gemm_desc& d, int sm_count, int planes, int* cg
   int bcg = 1, bbn = 128;
   for (const Cand& c : cands) {
     if (planes * c.bn > 256) continue;  // two accumulator stages must fit 512 TMEM columns
+    if ((c.bn / c.cg) % n_unit) continue;
     if (d.cta_group && c.cg != d.cta_group) continue;
     if (d.tile_n && c.bn != d.tile_n) continue;
     const int64_t tm = (d.m + 128 * c.cg - 1) / (128 * c.cg);

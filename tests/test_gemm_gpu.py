@@ -1,0 +1,369 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes) by the host mirror of the
+GemmKernels.jl API, against the CPU oracle on the same seeded inputs.
+
+Tolerances: normwise relative error <= 1e-3 for the FP16/BF16/TF32 -> FP32 tensor-core paths and
+<= 1e-5 for the FP32 FPU path (against a float64 product), plus the reference's own rules where its
+test matrix is replayed: elementwise rtol = sqrt(eps(T)) (configs/configs.jl:123-130) and normwise
+sqrt(eps(T)) (test/blas.jl:36,65).  Integer results must be bit-exact.
+"""
+import ctypes as C
+import importlib.util
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import gemmkernels_b200 as GK
+from gemmkernels_b200 import _lib as L
+from gemmkernels_b200 import Epilogue, Kernel, Layout, Operator, Transform
+from oracle import gemm_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_TENSOR = 1e-3
+TOL_FPU = 1e-5
+GOLDEN_DIR = Path(__file__).parent / "golden"
+
+
+def _golden_cases():
+    spec = importlib.util.spec_from_file_location("make_golden", GOLDEN_DIR / "make_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.cases()
+
+
+@pytest.fixture(scope="module")
+def golden():
+    return _golden_cases(), np.load(GOLDEN_DIR / "golden_small.npz")
+
+
+def dev(x, eltype=None):
+    return GK.to_cuarray(np.asarray(x), eltype)
+
+
+def planar(x, eltype=None):
+    """numpy (2, r, c) planes -> device (r, c, 2) column-major planes (Layout.Split*)."""
+    t = torch.from_numpy(np.ascontiguousarray(np.asarray(x).transpose(0, 2, 1)))   # [2, c, r]
+    if eltype is not None:
+        t = t.to(eltype.torch_dtype())
+    return t.cuda().permute(2, 1, 0)
+
+
+def run_matmul(a, b, c, d, *, M, N, K, op, la, lb, lc, ld, alpha=1.0, beta=1.0, epilogue=None, act=None,
+               kernel=Kernel.matmul_singlestage, **conf_kw):
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=op, global_a_layout=la, global_b_layout=lb,
+                         global_c_layout=lc, global_d_layout=ld, is_a_col_major=la.col_major,
+                         is_b_col_major=lb.col_major, **conf_kw)
+    kw = {}
+    if alpha != 1.0:
+        kw["transform_shared_to_regs_a"] = Transform.Elementwise(Transform.Scale(alpha))
+    if beta != 1.0:
+        kw["transform_shared_to_regs_c"] = Transform.Elementwise(Transform.Scale(beta))
+    if act is not None:
+        kw["transform_shared_to_global_d"] = Transform.Elementwise(act)
+    GK.matmul(conf, a, b, c, d, epilogue=epilogue, kernel=kernel, **kw)
+    torch.cuda.synchronize()
+    GK.poll_status()
+    return conf
+
+
+# ------------------------------------------------------------------------------------------------
+# committed golden fixtures
+# ------------------------------------------------------------------------------------------------
+def test_golden_fp16_nn(golden):
+    cases, want = golden
+    A, B = cases["fp16_nn"]["A"], cases["fp16_nn"]["B"]
+    M, K = A.shape; N = B.shape[1]
+    d = GK.cuarray(GK.Float32, M, N)
+    run_matmul(dev(A), dev(B), None, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+               la=Layout.ColMajor[GK.Float16], lb=Layout.ColMajor[GK.Float16],
+               lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32], block_shape=(128, 128, 64))
+    assert O.normwise_error(GK.to_numpy(d), want["fp16_nn/D"]) <= TOL_TENSOR
+
+
+def test_golden_fp16_tt_alpha_beta(golden):
+    cases, want = golden
+    cs = cases["fp16_tt_alpha_beta"]
+    At, Bt, Cm = cs["A"], cs["B"], cs["C"]
+    K, M = At.shape; N = Bt.shape[0]
+    c = dev(Cm); d = GK.cuarray(GK.Float32, M, N)
+    run_matmul(dev(At), dev(Bt), c, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+               la=Layout.RowMajor[GK.Float16], lb=Layout.RowMajor[GK.Float16],
+               lc=Layout.ColMajor[GK.Float32], ld=Layout.ColMajor[GK.Float32], alpha=2.0, beta=3.0,
+               block_shape=(128, 128, 64))
+    assert O.normwise_error(GK.to_numpy(d), want["fp16_tt_alpha_beta/D"]) <= TOL_TENSOR
+
+
+@pytest.mark.parametrize("case,axis,act", [("fp32_tn_bias_relu", "row", Transform.ReLU()),
+                                           ("fp32_tn_colbias_gelu", "col", Transform.GELU())])
+def test_golden_fp32_fpu_bias_activation(golden, case, axis, act):
+    cases, want = golden
+    cs = cases[case]
+    At, B, bias = cs["A"], cs["B"], cs["bias"]
+    K, M = At.shape; N = B.shape[1]
+    d = GK.cuarray(GK.Float32, M, N)
+    run_matmul(dev(At), dev(B), None, d, M=M, N=N, K=K, op=Operator.FPUOp[8, 8, 1, 4, 8, 1, GK.Float32, GK.Float32],
+               la=Layout.RowMajor[GK.Float32], lb=Layout.ColMajor[GK.Float32],
+               lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32],
+               epilogue=Epilogue.Bias(dev(bias), axis=axis), act=act, block_shape=(128, 128, 32))
+    assert O.normwise_error(GK.to_numpy(d), want[f"{case}/D"]) <= TOL_FPU
+
+
+@pytest.mark.parametrize("case,opcls", [("complex_planar", Operator.WMMAComplexOp), ("dual_planar", Operator.WMMADualOp)])
+def test_golden_planar_complex_and_dual(golden, case, opcls):
+    cases, want = golden
+    A, B = cases[case]["A"], cases[case]["B"]          # (2, M, K), (2, K, N)
+    M, K = A.shape[1:]; N = B.shape[2]
+    d = GK.cuarray(GK.Float32, M, N, 2)
+    run_matmul(planar(A), planar(B), None, d, M=M, N=N, K=K, op=opcls[16, 16, 16, GK.Float16, GK.Float32],
+               la=Layout.SplitColMajor[GK.Float16], lb=Layout.SplitColMajor[GK.Float16],
+               lc=Layout.Zero[GK.Float32], ld=Layout.SplitColMajor[GK.Float32], block_shape=(64, 64, 32))
+    got = GK.to_numpy(d).transpose(2, 0, 1)
+    assert O.normwise_error(got, want[f"{case}/D"]) <= TOL_TENSOR
+
+
+def test_golden_bf16(golden):
+    cases, want = golden
+    A, B = cases["bf16_nn"]["A"], cases["bf16_nn"]["B"]
+    M, K = A.shape; N = B.shape[1]
+    d = GK.cuarray(GK.Float32, M, N)
+    run_matmul(dev(A, GK.BFloat16), dev(B, GK.BFloat16), None, d, M=M, N=N, K=K,
+               op=Operator.TCGen05Operator[GK.BFloat16, GK.Float32],
+               la=Layout.ColMajor[GK.BFloat16], lb=Layout.ColMajor[GK.BFloat16],
+               lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32], block_shape=(128, 128, 64))
+    assert O.normwise_error(GK.to_numpy(d), want["bf16_nn/D"]) <= TOL_TENSOR
+
+
+def test_golden_int32_is_bit_exact(golden):
+    cases, want = golden
+    cs = cases["int32_wrap"]
+    A, B, Cm = cs["A"], cs["B"], cs["C"]
+    M, K = A.shape; N = B.shape[1]
+    c = dev(Cm); d = GK.cuarray(GK.Int32, M, N)
+    run_matmul(dev(A), dev(B), c, d, M=M, N=N, K=K, op=Operator.FPUOp[8, 16, 2, 4, 8, 1, GK.Int32, GK.Int32],
+               la=Layout.ColMajor[GK.Int32], lb=Layout.ColMajor[GK.Int32], lc=Layout.ColMajor[GK.Int32],
+               ld=Layout.ColMajor[GK.Int32], alpha=2, beta=3, block_shape=(64, 64, 32))
+    assert np.array_equal(GK.to_numpy(d), want["int32_wrap/D"])
+
+
+def test_golden_tropical(golden):
+    cases, want = golden
+    cs = cases["tropical"]
+    A, B, Cm = cs["A"], cs["B"], cs["C"]
+    M, K = A.shape; N = B.shape[1]
+    c = dev(Cm); d = GK.cuarray(GK.Float32, M, N)
+    run_matmul(dev(A), dev(B), c, d, M=M, N=N, K=K,
+               op=Operator.TropicalFPUOp[8, 16, 2, 4, 8, 1, GK.Float32, GK.Float32],
+               la=Layout.ColMajor[GK.Float32], lb=Layout.ColMajor[GK.Float32], lc=Layout.ColMajor[GK.Float32],
+               ld=Layout.ColMajor[GK.Float32], block_shape=(64, 64, 32))
+    assert np.array_equal(GK.to_numpy(d), want["tropical/D"])
+
+
+# ------------------------------------------------------------------------------------------------
+# replay of test/blas.jl: matmatmul! with all transposes, unaligned sizes, random alpha/beta
+# ------------------------------------------------------------------------------------------------
+BLAS_TYPES = [("Float16", "Float32", True, 128), ("Float16", "Float16", True, 256), ("Float32", "Float32", False, 128)]
+
+
+@pytest.mark.parametrize("ab,cd,wmma,min_dim", BLAS_TYPES)
+@pytest.mark.parametrize("ta,tb", [("N", "N"), ("N", "T"), ("T", "N"), ("T", "T")])
+def test_blas_matmatmul(ab, cd, wmma, min_dim, ta, tb):
+    rng = np.random.default_rng(hash((ab, cd, ta, tb)) % 2 ** 32)
+    AB, CD = getattr(GK, ab), getattr(GK, cd)
+    sizes = [(10, 10, 10), (min_dim, min_dim, min_dim), (1000, 1000, 1000), (10, min_dim, 1000), (1000, 10, min_dim),
+             (min_dim, 1000, 10)]
+    for (M, N, K) in sizes:
+        alpha, beta = float(rng.random()), float(rng.random())
+        A = (rng.random((K, M) if ta == "T" else (M, K)) / math.sqrt(K)).astype(AB.np_dtype)
+        B = (rng.random((N, K) if tb == "T" else (K, N)) / math.sqrt(K)).astype(AB.np_dtype)
+        Cm = rng.random((M, N)).astype(CD.np_dtype)
+        c = dev(Cm)
+        out = GK.matmatmul_(c, ta, tb, dev(A), dev(B), alpha, beta, wmma=wmma)
+        torch.cuda.synchronize(); GK.poll_status()
+        assert out is c
+        want = O.gemm(A, B, Cm, alpha, beta, ta == "T", tb == "T")
+        got = GK.to_numpy(c)
+        assert O.isapprox_normwise(want, got, cd if cd == "Float16" else ab), (M, N, K, O.normwise_error(got, want))
+        assert O.normwise_error(got, want) <= (TOL_FPU if ab == "Float32" else (2e-3 if cd == "Float16" else TOL_TENSOR))
+
+
+def test_mul_with_transposed_views():
+    rng = np.random.default_rng(5)
+    A = rng.random((256, 384)).astype(np.float16); Bt = rng.random((128, 384)).astype(np.float16)
+    c = GK.cuarray(GK.Float32, 256, 128)
+    GK.mul_(c, dev(A), dev(Bt).T)          # C = A * Bt'
+    torch.cuda.synchronize()
+    assert O.normwise_error(GK.to_numpy(c), O.gemm(A, Bt, trans_b=True)) <= TOL_TENSOR
+
+
+# ------------------------------------------------------------------------------------------------
+# benchmark configurations at full size
+# ------------------------------------------------------------------------------------------------
+def test_config1_fp16_2048_against_cpu_product():
+    """Configuration 1: A, B Float16 ~ U[0,1), 2048^3, alpha = 1, beta = 0, checked against the CPU
+    product of the Float32-promoted inputs."""
+    A, B = O.inputs_fp16_uniform01(1, 2048, 2048, 2048)
+    c = GK.cuarray(GK.Float32, 2048, 2048); c.zero_()
+    GK.mul_(c, dev(A), dev(B))
+    torch.cuda.synchronize(); GK.poll_status()
+    want = O.gemm(A, B)
+    got = GK.to_numpy(c)
+    assert O.normwise_error(got, want) <= TOL_TENSOR
+    assert O.isapprox_elementwise(want, got, "Float16")
+
+
+def test_metric_shape_8192_sampled_rows_and_linearity():
+    """8192^3 FP16 -> FP32 (the headline shape).  A full CPU product would take minutes, so the
+    result is checked on 48 sampled rows against the oracle, and through linearity:
+    (A1 + A2) B = A1 B + A2 B holds exactly in exact arithmetic and to rounding here."""
+    n = 8192
+    A, B = O.inputs_fp16_uniform01(0, n, n, n)
+    a, b = dev(A), dev(B)
+    c = GK.cuarray(GK.Float32, n, n)
+    GK.mul_(c, a, b)
+    torch.cuda.synchronize(); GK.poll_status()
+    rows = np.random.default_rng(0).choice(n, 48, replace=False)
+    want = A[rows].astype(np.float32) @ B.astype(np.float32)
+    got = c[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert O.normwise_error(got, want) <= TOL_TENSOR
+    # 2*A is exact in Float16 here (values in [0, 1)), so every product and partial sum doubles
+    # exactly: the result must be 2*C bit for bit.
+    c2 = GK.cuarray(GK.Float32, n, n)
+    GK.mul_(c2, dev((A * np.float16(2)).astype(np.float16)), b)
+    torch.cuda.synchronize()
+    assert torch.equal(c2, c * 2)
+    # additivity: split A exactly into a coarse part and a remainder, A = A1 + A2
+    A1 = (A.view(np.uint16) & np.uint16(0xFFE0)).view(np.float16)
+    A2 = (A.astype(np.float32) - A1.astype(np.float32)).astype(np.float16)
+    assert np.array_equal(A1.astype(np.float32) + A2.astype(np.float32), A.astype(np.float32))
+    c3 = GK.cuarray(GK.Float32, n, n)
+    GK.mul_(c2, dev(A1), b)
+    GK.mul_(c3, dev(A2), b)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert ((c2 + c3) - c).norm().item() / c.norm().item() <= 1e-4   # FP32 accumulation noise over K = 8192
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("cg,bn", [(1, 128), (2, 256), (1, 256), (2, 128)])
+def test_tile_shapes_and_transposes_exact(ta, tb, cg, bn):
+    """Small-integer inputs make the FP16 -> FP32 product exact, so any layout / descriptor slip
+    shows as a hard mismatch rather than as noise."""
+    rng = np.random.default_rng(cg * 1000 + bn + ta * 2 + tb)
+    M, N, K = 640, 520, 392
+    A = rng.integers(-2, 3, (K, M) if ta else (M, K)).astype(np.float16)
+    B = rng.integers(-2, 3, (N, K) if tb else (K, N)).astype(np.float16)
+    d = GK.cuarray(GK.Float32, M, N)
+    la = (Layout.RowMajor if ta else Layout.ColMajor)[GK.Float16]
+    lb = (Layout.RowMajor if tb else Layout.ColMajor)[GK.Float16]
+    run_matmul(dev(A), dev(B), None, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+               la=la, lb=lb, lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32],
+               block_shape=(128, 128, 64), cta_group=cg, tile_n=bn)
+    assert np.array_equal(GK.to_numpy(d), O.gemm(A, B, trans_a=bool(ta), trans_b=bool(tb)))
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_tf32(ta, tb):
+    rng = np.random.default_rng(9 + ta * 2 + tb)
+    M, N, K = 384, 256, 520
+    A = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    d = GK.cuarray(GK.Float32, M, N)
+    la = (Layout.RowMajor if ta else Layout.ColMajor)[GK.Float32]
+    lb = (Layout.RowMajor if tb else Layout.ColMajor)[GK.Float32]
+    run_matmul(dev(A), dev(B), None, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[Operator.TF32, GK.Float32],
+               la=la, lb=lb, lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32], block_shape=(128, 128, 32))
+    got = GK.to_numpy(d)
+    assert O.normwise_error(got, O.gemm64(A, B, trans_a=bool(ta), trans_b=bool(tb))) <= TOL_TENSOR
+    # and it is what TF32 inputs give: tighter against the truncated-input product
+    assert O.normwise_error(got, O.gemm64(O.tf32_truncate(A), O.tf32_truncate(B), trans_a=bool(ta), trans_b=bool(tb))) <= 2e-5
+
+
+def test_config3_planar_complex_4096_sampled():
+    """Configuration 3 at full size (4096^3 planar complex FP16 -> Complex{F32}): sampled rows."""
+    n = 4096
+    A, B = O.inputs_planar_fp16(3, n, n, n)
+    d = GK.cuarray(GK.Float32, n, n, 2)
+    run_matmul(planar(A), planar(B), None, d, M=n, N=n, K=n, op=Operator.WMMAComplexOp[16, 16, 16, GK.Float16, GK.Float32],
+               la=Layout.SplitColMajor[GK.Float16], lb=Layout.SplitColMajor[GK.Float16],
+               lc=Layout.Zero[GK.Float32], ld=Layout.SplitColMajor[GK.Float32], block_shape=(64, 64, 32))
+    rows = np.random.default_rng(1).choice(n, 32, replace=False)
+    re, im = O.complex_gemm(A[0][rows], A[1][rows], B[0], B[1])
+    got = d[torch.from_numpy(rows).cuda()].cpu().numpy()      # (32, n, 2)
+    assert O.normwise_error(got[..., 0], re) <= TOL_TENSOR and O.normwise_error(got[..., 1], im) <= TOL_TENSOR
+
+
+# ------------------------------------------------------------------------------------------------
+# edge cases and error behaviour
+# ------------------------------------------------------------------------------------------------
+def test_beta_with_aliased_c_and_d_and_fp16_output():
+    rng = np.random.default_rng(21)
+    M, N, K = 256, 136, 72
+    A = rng.random((M, K)).astype(np.float16); B = rng.random((K, N)).astype(np.float16)
+    Cm = rng.random((M, N)).astype(np.float16)
+    c = dev(Cm)
+    GK.matmatmul_(c, "N", "N", dev(A), dev(B), 2.0, 3.0, wmma=True)
+    torch.cuda.synchronize()
+    want = O.gemm(A, B, Cm, 2.0, 3.0)
+    assert O.isapprox_elementwise(want, GK.to_numpy(c), "Float16")
+
+
+def test_leading_dimension_larger_than_rows():
+    rng = np.random.default_rng(22)
+    M, N, K, ld = 200, 96, 64, 264
+    big = torch.zeros(K, ld, dtype=torch.float16, device="cuda").T      # (ld, K) column-major
+    A = rng.random((M, K)).astype(np.float16)
+    big[:M] = torch.from_numpy(A).cuda()
+    a = big[:M]                                                        # view with ld = 264
+    assert a.stride(1) == ld
+    B = rng.random((K, N)).astype(np.float16)
+    c = GK.cuarray(GK.Float32, M, N)
+    GK.mul_(c, a, dev(B))
+    torch.cuda.synchronize()
+    assert O.normwise_error(GK.to_numpy(c), O.gemm(A, B)) <= TOL_TENSOR
+
+
+def test_alpha_zero_and_k_zero_reduce_to_beta_c():
+    rng = np.random.default_rng(23)
+    Cm = rng.random((64, 48)).astype(np.float32)
+    A = rng.random((64, 32)).astype(np.float16); B = rng.random((32, 48)).astype(np.float16)
+    c = dev(Cm)
+    GK.matmatmul_(c, "N", "N", dev(A), dev(B), 0.0, 0.5, wmma=True)
+    torch.cuda.synchronize()
+    assert np.allclose(GK.to_numpy(c), 0.5 * Cm, rtol=1e-6)
+
+
+def test_unsupported_combinations_raise_config_error():
+    a = GK.cuarray(GK.Float64, 128, 128); d = GK.cuarray(GK.Float64, 128, 128)
+    conf = GK.get_config(gemm_shape=(128, 128, 128), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=Layout.ColMajor[GK.Float64], global_c_layout=Layout.ColMajor[GK.Float64],
+                         block_shape=(128, 128, 64))
+    with pytest.raises(GK.ConfigError):
+        GK.matmul(conf, a, a, d, d)
+    with pytest.raises(GK.DimensionMismatch):
+        GK.matmatmul_(GK.cuarray(GK.Float32, 64, 64), "N", "N", GK.cuarray(GK.Float16, 64, 32),
+                      GK.cuarray(GK.Float16, 48, 64), 1.0, 0.0)
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A wait that nothing will ever satisfy (the producers are told to issue no copies) must run
+    out, leave an error status for the host, and leave the context usable."""
+    n = 256
+    a = torch.ones(n, n, dtype=torch.float16, device="cuda").T
+    d = GK.cuarray(GK.Float32, n, n)
+    desc = L.GemmDesc(number=0, m=n, n=n, k=n, dtype_a=L.GK_F16, dtype_b=L.GK_F16, dtype_c=L.GK_F32, dtype_d=L.GK_F32,
+                      compute=L.GK_F16, op=L.GK_OP_TCGEN05, lda=n, ldb=n, ldc=n, ldd=n, alpha=1.0, cta_group=1, tile_n=128)
+    desc.reserved[0] = 4          # measurement/test aid: producers skip their copies
+    h = GK.handle()
+    st = L.lib.gk_gemm(h, C.byref(desc), a.data_ptr(), a.data_ptr(), None, d.data_ptr(), None, None,
+                       C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == L.GK_OK
+    torch.cuda.synchronize()
+    with pytest.raises(GK.DeviceTimeout):
+        GK.poll_status()
+    GK.poll_status()               # status is cleared by the read
+    c = GK.cuarray(GK.Float32, n, n)
+    GK.mul_(c, a, a)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert torch.all(c == n)
