@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200: `python bench.py --gpus N --steps K --warmup W`.
+
+Workload (config.workload): the shape the headline metric is quoted on — C = A*B with A, B
+Float16 ~ U[0,1) 8192 x 8192 column-major, C Float32, alpha = 1, beta = 0 (synthetic, seeded).
+One step = one such GEMM per GPU through the C ABI.  With N > 1 (one process per GPU under
+torchrun) the path is sharded by column blocks of B and C: rank r owns its own 8192 columns, A is
+broadcast once with NCCL before the timed region and stays resident, and no collective runs inside
+a step (weak scaling: the problem is M = K = 8192, N = 8192 * ranks).
+
+Prints one JSON line: device-timed throughput (`value`), the same metric measured end to end from
+host buffers (`e2e`), the tensor-core roofline of the kernel (`roofline`) and, at N = 1, the CPU
+baseline (`cpu_baseline`, numpy/OpenBLAS sgemm on the Float32-promoted inputs — the reference's
+own CPU check is LinearAlgebra.mul!, i.e. OpenBLAS sgemm).
+
+`--impl reference` times that CPU product alone (rank 0 only) for the same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "gemmkernels.jl_b200"))
+
+import numpy as np  # noqa: E402
+
+METRIC = "GEMM TFLOP/s (FP16->FP32, 8192^3)"
+N_DIM = 8192
+FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
+# DRAM traffic of one launch, from the ncu capture summarised in profiles/ (dram read + write).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.503e9   # 1.248 GB read + 0.255 GB written
+
+
+def measured_peaks():
+    """Measured denominators written by the driver; fallback figures when the file is absent."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return {"tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": f"c0: C=A*B, A,B Float16 U[0,1) {N_DIM}x{N_DIM} col-major, C Float32, alpha=1 beta=0"
+                        + (f"; column blocks of B,C over {n_gpus} ranks, A broadcast once (NCCL), resident" if n_gpus > 1 else ""),
+            "m": N_DIM, "n_per_gpu": N_DIM, "k": N_DIM, "operator": "TCGen05Operator{Float16,Float32}",
+            "l2": "inputs and output (512 MiB per GPU) are larger than L2; no flush between steps"}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU check (OpenBLAS sgemm on promoted inputs), bounded sample
+# ------------------------------------------------------------------------------------------------
+def cpu_sgemm_sample(cols: int, reps: int, warmup: int):
+    """Times D[:, :cols] = A * B[:, :cols] in float32 with every host thread BLAS will use.
+    Returns (seconds per rep, flops per rep, threads)."""
+    from oracle import gemm_oracle as O
+    A, B = O.inputs_fp16_uniform01(0, N_DIM, cols, N_DIM)
+    a32, b32 = A.astype(np.float32), B.astype(np.float32)
+    threads = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info
+        blas = [p for p in threadpool_info() if p.get("user_api") == "blas"]
+        if blas:
+            threads = int(blas[0]["num_threads"])
+    except Exception:
+        pass
+    for _ in range(warmup):
+        O.gemm(a32, b32)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.gemm(a32, b32)
+    dt = (time.perf_counter() - t0) / max(reps, 1)
+    return dt, 2.0 * N_DIM * cols * N_DIM, threads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    cols = 1024   # one eighth of the columns per step: a bounded sample of the same product
+    dt, flops, threads = cpu_sgemm_sample(cols, args.steps, min(args.warmup, 1))
+    tf = flops / dt / 1e12
+    line = {"impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                             "sample": f"{N_DIM}x{cols}x{N_DIM} slice (first {cols} columns of D) of the 8192^3 product per step, "
+                                       "numpy/OpenBLAS sgemm on Float32-promoted inputs"},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks during the timed region (read-only NVML sampling)
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, device_index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                break
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# the GPU arm
+# ------------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import gemmkernels_b200 as GK
+    from gemmkernels_b200 import _lib as L
+    from oracle import gemm_oracle as O   # input generators and the CPU baseline leg only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 needs one process per GPU: launch with torch.distributed.run --nproc-per-node N")
+        args.gpus = world
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    n = N_DIM
+    # Inputs: A is generated on rank 0 and broadcast (the one exchange of the sharded path);
+    # every rank draws its own column block of B.
+    A_host, _ = O.inputs_fp16_uniform01(0, n, 8, n)
+    B_host = np.random.default_rng(2000 + rank).random((n, n), dtype=np.float32).astype(np.float16)
+    a_pin = torch.from_numpy(np.ascontiguousarray(A_host.T)).pin_memory().T      # column-major, pinned
+    b_pin = torch.from_numpy(np.ascontiguousarray(B_host.T)).pin_memory().T
+    d_pin = torch.empty(n, n, dtype=torch.float32).pin_memory().T
+    a = GK.cuarray(GK.Float16, n, n)
+    b = GK.cuarray(GK.Float16, n, n); b.copy_(b_pin, non_blocking=True)
+    d = GK.cuarray(GK.Float32, n, n)
+    bcast_ms = None
+    if rank == 0:
+        a.copy_(a_pin, non_blocking=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(a.T, src=0)      # a.T is the contiguous view of the column-major storage
+        e1.record(); torch.cuda.synchronize()
+        bcast_ms = e0.elapsed_time(e1)
+
+    # the call a user makes: GemmKernels.matmul with a Config (TCGen05Operator, aligned layouts)
+    conf = GK.get_config(gemm_shape=(n, n, n), operator=GK.Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float16],
+                         global_c_layout=GK.Layout.Zero[GK.Float32],
+                         global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
+    plan = GK.query(conf, a, b, None, d)
+
+    def step():
+        GK.matmul(conf, a, b, None, d, kernel=GK.Kernel.matmul_pipelined)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = max_over_ranks(e0.elapsed_time(e1))
+    GK.poll_status()
+    ms_per_step = total_ms / args.steps
+    value = world * FLOPS_PER_GEMM / (ms_per_step * 1e-3) / 1e12
+
+    # correctness spot check of the timed result (one row against the oracle's product)
+    row = np.asarray(A_host[7:8].astype(np.float32) @ B_host.astype(np.float32)) if rank == 0 else None
+    if rank == 0:
+        got = d[7:8].cpu().numpy()
+        err = O.normwise_error(got, row)
+        if not err <= 1e-3:
+            raise SystemExit(f"bench result is wrong: normwise error {err}")
+
+    # end to end: same GEMM from pinned host buffers through gk_gemm_host (H2D of A and B, D2H of D
+    # inside the timed region, every step)
+    for _ in range(2):
+        GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
+    barrier()
+    e2e_steps = min(args.steps, 100)   # ~10 ms per step over PCIe: bounded so the default run stays short
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
+    if rank == 0:
+        err = O.normwise_error(d_pin[7:8].numpy(), row)
+        if not err <= 1e-3:
+            raise SystemExit(f"end-to-end result is wrong: normwise error {err}")
+    e2e_value = world * FLOPS_PER_GEMM / (e2e_ms * 1e-3) / 1e12
+    h2d = a_pin.numel() * 2 + b_pin.numel() * 2
+    d2h = d_pin.numel() * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier(); dist.destroy_process_group()
+        return 0
+
+    peaks = measured_peaks()
+    achieved = FLOPS_PER_GEMM / (ms_per_step * 1e-3) / 1e12     # per launch, one GPU
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst; sustained {peaks['tflops_sustained']}",
+                     "frac_of_nominal_dense_2250": achieved / 2250.0},
+        "kernel": {"family": int(plan.kernel), "grid": int(plan.grid), "cluster": int(plan.cluster),
+                   "tile": [int(plan.tile_m), int(plan.tile_n), int(plan.tile_k)], "stages": int(plan.stages),
+                   "smem_bytes": int(plan.smem_bytes), "tmem_columns": int(plan.tmem_columns)},
+    }
+    if bcast_ms is not None:
+        line["a_broadcast_ms"] = bcast_ms
+    if world == 1 and not args.no_cpu_baseline:
+        cols = 2048
+        dt, flops, threads = cpu_sgemm_sample(cols, 3, 1)
+        line["cpu_baseline"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": f"{n}x{cols}x{n} slice of the 8192^3 product, 3 timed runs after 1 warm-up, "
+                                          "numpy/OpenBLAS sgemm on Float32-promoted inputs"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

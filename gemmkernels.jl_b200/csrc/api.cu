@@ -186,7 +186,7 @@ gk_status gk_create(gk_handle* out) {
 gk_status gk_destroy(gk_handle h) {
   clear_error();
   if (!h) return GK_OK;
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < 5; ++i)
     if (h->stage_dev[i]) cudaFree(h->stage_dev[i]);
   if (h->status_host) cudaFreeHost(h->status_host);
   delete h;
@@ -259,6 +259,65 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     return tc_launch(L, st);
   }
   return launch_simt(*desc, epi, a, b, c, d, st);
+}
+
+// Bytes an operand occupies, from its first to its last addressed element.
+static size_t operand_bytes(int64_t ld, int64_t cols, int64_t plane, int number, int dtype) {
+  const size_t es = static_cast<size_t>(dtype_size(dtype));
+  if (cols <= 0) return 0;
+  if (number == GK_REAL) return static_cast<size_t>(ld) * cols * es;
+  if (plane == 0) return 2 * static_cast<size_t>(ld) * cols * es;  // interleaved pairs
+  return (static_cast<size_t>(plane) + static_cast<size_t>(ld) * cols) * es;
+}
+
+static gk_status stage_reserve(gk_handle h, int slot, size_t bytes) {
+  if (bytes <= h->stage_bytes[slot]) return GK_OK;
+  if (h->stage_dev[slot]) { cudaFree(h->stage_dev[slot]); h->stage_dev[slot] = nullptr; h->stage_bytes[slot] = 0; }
+  GK_CUDA_CHECK(cudaMalloc(&h->stage_dev[slot], bytes));
+  h->stage_bytes[slot] = bytes;
+  return GK_OK;
+}
+
+gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host, const void* b_host,
+                       const void* c_host, void* d_host, const gk_epilogue_desc* epi,
+                       gk_stream stream) {
+  clear_error();
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  gk_status s = validate_desc(desc, epi);
+  if (s != GK_OK) return s;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const gk_gemm_desc& d = *desc;
+  const bool read_ab = d.layout_a == GK_LAYOUT_DENSE && d.layout_b == GK_LAYOUT_DENSE;
+  const bool read_c = c_host != nullptr && d.layout_c == GK_LAYOUT_DENSE && d.beta != 0.0;
+  const size_t a_bytes = read_ab ? operand_bytes(d.lda, d.trans_a ? d.m : d.k, d.plane_a, d.number, d.dtype_a) : 0;
+  const size_t b_bytes = read_ab ? operand_bytes(d.ldb, d.trans_b ? d.k : d.n, d.plane_b, d.number, d.dtype_b) : 0;
+  const size_t c_bytes = read_c ? operand_bytes(d.ldc, d.n, d.plane_c, d.number, d.dtype_c) : 0;
+  const size_t d_bytes = operand_bytes(d.ldd, d.n, d.plane_d, d.number, d.dtype_d);
+  size_t bias_bytes = 0;
+  if (epi && epi->bias_axis != GK_BIAS_NONE)
+    bias_bytes = sizeof(float) * static_cast<size_t>(epi->bias_axis == GK_BIAS_ROW ? d.m : d.n);
+  std::lock_guard<std::mutex> lock(h->host_mu);  // the staging buffers are shared per handle
+  const size_t need[5] = {a_bytes, b_bytes, c_bytes, d_bytes, bias_bytes};
+  for (int i = 0; i < 5; ++i)
+    if (need[i] && (s = stage_reserve(h, i, need[i])) != GK_OK) return s;
+  if (a_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[0], a_host, a_bytes, cudaMemcpyHostToDevice, st));
+  if (b_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[1], b_host, b_bytes, cudaMemcpyHostToDevice, st));
+  if (c_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[2], c_host, c_bytes, cudaMemcpyHostToDevice, st));
+  gk_epilogue_desc epi_dev;
+  const gk_epilogue_desc* epi_use = epi;
+  if (bias_bytes) {
+    GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[4], epi->bias, bias_bytes, cudaMemcpyHostToDevice, st));
+    epi_dev = *epi;
+    epi_dev.bias = static_cast<const float*>(h->stage_dev[4]);
+    epi_use = &epi_dev;
+  }
+  s = gk_gemm(h, desc, h->stage_dev[0], h->stage_dev[1], read_c ? h->stage_dev[2] : nullptr, h->stage_dev[3],
+              epi_use, nullptr, stream);
+  if (s != GK_OK) return s;
+  if (d_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(d_host, h->stage_dev[3], d_bytes, cudaMemcpyDeviceToHost, st));
+  GK_CUDA_CHECK(cudaStreamSynchronize(st));
+  int32_t code = 0;
+  return gk_poll_status(h, &code);
 }
 
 }  // extern "C"

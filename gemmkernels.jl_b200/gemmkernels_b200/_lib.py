@@ -26,7 +26,7 @@ GK_RASTER_AUTO, GK_RASTER_IDENTITY, GK_RASTER_HORIZONTAL, GK_RASTER_VERTICAL, GK
 
 EXPORTS = (
     "gk_version", "gk_last_error_message", "gk_create", "gk_destroy", "gk_poll_status",
-    "gk_gemm_query", "gk_gemm",
+    "gk_gemm_query", "gk_gemm", "gk_gemm_host",
 )
 
 
@@ -94,6 +94,9 @@ def _load() -> C.CDLL:
     lib.gk_gemm.restype = C.c_int
     lib.gk_gemm.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                             C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p, C.c_void_p]
+    lib.gk_gemm_host.restype = C.c_int
+    lib.gk_gemm_host.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
+                                 C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p]
     return lib
 
 

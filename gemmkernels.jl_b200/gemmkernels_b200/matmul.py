@@ -259,6 +259,24 @@ def matmul(conf: Config, a, b, c, d, *,
     return None
 
 
+def matmul_host(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, stream=None,
+                device_index=None, **transforms):
+    """`matmul` for matrices in host memory (column-major CPU tensors, ideally pinned): copies the
+    operands to the device, runs the GEMM and copies D back into `d`; returns when `d` is complete.
+    Julia counterpart: calling the shim's `matmul` with `Array`s instead of `CuArray`s."""
+    import torch
+    hooks = {k.replace("transform_", ""): v for k, v in transforms.items()}
+    epilogue = epilogue or Epilogue.Default()
+    desc, epi, (pa, pb, pc, pd) = lower(conf, a, b, c, d, hooks, epilogue, kernel)
+    dev = device_index if device_index is not None else torch.cuda.current_device()
+    s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        st = L.lib.gk_gemm_host(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), C.c_void_p(s))
+    if st != L.GK_OK:
+        _raise(st)
+    return None
+
+
 def query(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, **hooks) -> L.GemmPlan:
     """What `matmul` would launch for these arguments (kernel family, grid, shared memory, TMEM
     columns); launches nothing.  This is where the reference checked its shared-memory and thread

@@ -11,7 +11,6 @@
  *                      the device code it launches (src/kernel.jl:10-574, src/operator.jl,
  *                      src/layout.jl, src/epilogue.jl:14-73, src/transform.jl:19-30)
  *   gk_gemm_query      the launch-geometry and limit checks of src/matmul.jl:24-41
- *   gk_contract        the tensor-contraction driver benchmarks/tensor-contractions/run.jl:88-131
  *   gk_create/destroy  no counterpart (CUDA.jl keeps the context); holds per-device caches
  */
 #ifndef GEMMKERNELS_B200_H
@@ -98,7 +97,7 @@ typedef enum gk_raster {
  * RowMajor global layout).  Likewise trans_b with K x N / N x K.  C and D are M x N and may alias.
  * For GK_COMPLEX / GK_DUAL, plane_x is the element distance between the two planes of operand x
  * (real/imaginary, or value/derivative); plane_x = 0 means interleaved pairs, in which case ldx
- * counts pairs.  Interleaved A/B need a scratch buffer: see gk_gemm_workspace_size.
+ * counts pairs.
  */
 typedef struct gk_gemm_desc {
   uint32_t struct_size; /* sizeof(gk_gemm_desc), for ABI evolution */
@@ -163,6 +162,16 @@ GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_e
 GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
                   gk_stream stream);
+
+/* The same GEMM for callers whose matrices live in host memory (Julia `Array`s rather than
+ * `CuArray`s; the reference has no such method — CUDA.jl users would `CuArray(A)` first, which is
+ * what this call does internally): copies a, b (and c, and the bias named by epi) to device
+ * staging buffers kept in the handle, runs gk_gemm, copies D back to d_host and returns once
+ * d_host is complete (it synchronises `stream`).  Pinned host memory makes the copies faster but
+ * is not required.  Calls on one handle are serialised. */
+GK_API gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host,
+                              const void* b_host, const void* c_host, void* d_host,
+                              const gk_epilogue_desc* epi, gk_stream stream);
 
 #ifdef __cplusplus
 }
