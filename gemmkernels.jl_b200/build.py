@@ -19,7 +19,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libgemmkernels_b200.so"
 
-SOURCES = ["api.cu", "tc_plan.cu"]
+SOURCES = ["api.cu", "tc_plan.cu", "contract.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,8 +1,11 @@
 // C ABI of the library (include/gemmkernels_b200.h): handle, dispatch, error reporting.
+#include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <new>
 
 #include "common.h"
+#include "fpu_gemm.cuh"
 #include "simt_gemm.cuh"
 #include "tc_plan.h"
 
@@ -61,7 +64,54 @@ static gk_status validate_desc(const gk_gemm_desc* d, const gk_epilogue_desc* ep
   return GK_OK;
 }
 
-// Which kernel family serves this descriptor: 1 tcgen05, 3 generic SIMT.
+// FP32 FFMA fast path: the reference's UnsafeAligned* conditions (tile-multiple sizes, 16-byte
+// aligned columns), all four matrices Float32.
+static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, const void* c, const void* dd,
+                         const gk_epilogue_desc* epi) {
+  if (d.op == GK_OP_FPU_TROPICAL || d.op == GK_OP_TCGEN05 || d.number != GK_REAL) return false;
+  if (d.dtype_a != GK_F32 || d.dtype_b != GK_F32 || d.dtype_d != GK_F32) return false;
+  if (d.compute != GK_F32) return false;
+  if (d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE) return false;
+  const bool has_c = d.layout_c == GK_LAYOUT_DENSE && d.beta != 0.0;
+  if (has_c && (d.dtype_c != GK_F32 || d.ldc % 4)) return false;
+  if (d.m < kFpuBM || d.n < kFpuBN || d.k < kFpuBK) return false;
+  if (d.m % kFpuBM || d.n % kFpuBN || d.k % kFpuBK) return false;
+  if (d.m > INT32_MAX / 2 || d.n > INT32_MAX / 2 || d.k > INT32_MAX / 2) return false;
+  if (d.lda % 4 || d.ldb % 4 || d.ldd % 4) return false;
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(a) || misaligned(b) || misaligned(dd) || (has_c && misaligned(c))) return false;
+  if (epi && epi->bias_axis != GK_BIAS_NONE && misaligned(epi->bias)) return false;
+  return true;
+}
+
+static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
+                            const void* b, const void* c, void* dd, cudaStream_t stream) {
+  FpuParams p{};
+  p.A = static_cast<const float*>(a); p.B = static_cast<const float*>(b);
+  p.C = static_cast<const float*>(c); p.D = static_cast<float*>(dd);
+  p.M = static_cast<int>(d.m); p.N = static_cast<int>(d.n); p.K = static_cast<int>(d.k);
+  p.lda = d.lda; p.ldb = d.ldb; p.ldc = d.ldc; p.ldd = d.ldd;
+  p.alpha = static_cast<float>(d.alpha);
+  p.beta = (d.layout_c == GK_LAYOUT_DENSE && c) ? static_cast<float>(d.beta) : 0.0f;
+  if (epi) { p.bias = epi->bias; p.bias_axis = epi->bias_axis; p.act = epi->activation; }
+  p.tiles_m = p.M / kFpuBM; p.tiles_n = p.N / kFpuBN;
+  // 2 CTAs per SM run together: make the set of tiles in flight roughly square
+  int group = d.raster_group > 0 ? d.raster_group
+                                 : static_cast<int>(std::lround(std::sqrt(2.0 * h->sm_count)));
+  if (d.raster == GK_RASTER_IDENTITY) group = p.tiles_m;
+  p.raster_group = std::max(1, std::min(group, p.tiles_m));
+  const dim3 grid(static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n));
+  const bool ak = d.trans_a != 0;   // stored K x M: K is the contiguous index of A
+  const bool bk = d.trans_b == 0;   // stored K x N: K is the contiguous index of B
+  if (ak && bk) fpu_gemm_kernel<true, true><<<grid, kFpuThreads, 0, stream>>>(p);
+  else if (ak && !bk) fpu_gemm_kernel<true, false><<<grid, kFpuThreads, 0, stream>>>(p);
+  else if (!ak && bk) fpu_gemm_kernel<false, true><<<grid, kFpuThreads, 0, stream>>>(p);
+  else fpu_gemm_kernel<false, false><<<grid, kFpuThreads, 0, stream>>>(p);
+  GK_CUDA_CHECK(cudaGetLastError());
+  return GK_OK;
+}
+
+// Which kernel family serves this descriptor: 1 tcgen05, 2 FP32 FFMA, 3 generic SIMT.
 static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
   // Nothing to multiply (Layout.Zero operands, alpha == 0, K == 0): D = act(beta * C + bias),
   // which the generic kernel does without touching A or B.
@@ -171,9 +221,9 @@ gk_status gk_create(gk_handle* out) {
     return set_error(GK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   }
   h->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
-  e = cudaHostAlloc(reinterpret_cast<void**>(&h->status_host), sizeof(int32_t), cudaHostAllocMapped);
+  e = cudaHostAlloc(reinterpret_cast<void**>(&h->status_host), 16 * sizeof(int32_t), cudaHostAllocMapped);
   if (e != cudaSuccess) { delete h; return set_error(GK_ERR_CUDA, "cudaHostAlloc failed: %s", cudaGetErrorString(e)); }
-  *h->status_host = 0;
+  for (int i = 0; i < 16; ++i) h->status_host[i] = 0;
   e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&h->status_dev), h->status_host, 0);
   if (e != cudaSuccess) {
     cudaFreeHost(h->status_host); delete h;
@@ -205,6 +255,13 @@ gk_status gk_poll_status(gk_handle h, int32_t* raw_code) {
                    : code == 103 ? "epilogue" : code == 104 ? "drain" : "unknown");
 }
 
+gk_status gk_debug_marks(gk_handle h, int32_t* out16) {
+  clear_error();
+  if (!h || !out16) return set_error(GK_ERR_INVALID_ARGUMENT, "handle or output is NULL");
+  for (int i = 0; i < 16; ++i) out16[i] = reinterpret_cast<volatile int32_t*>(h->status_host)[i];
+  return GK_OK;
+}
+
 gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
                         gk_gemm_plan* plan) {
   clear_error();
@@ -218,12 +275,20 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
   plan->kernel = fam;
   if (fam == 1) {
     TcLaunch L;
-    s = tc_plan(h, *desc, epi, nullptr, nullptr, nullptr, nullptr, &L);
+    TcProblem pr;
+    tc_problem_from_gemm(*desc, epi, nullptr, nullptr, nullptr, nullptr, &pr);
+    s = tc_plan(h, pr, false, &L);
     if (s != GK_OK) return s;
     plan->grid = L.grid; plan->block = kTcThreads; plan->cluster = L.cg;
     plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
+  } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {
+    plan->kernel = 2;
+    plan->grid = static_cast<int32_t>((desc->m / kFpuBM) * (desc->n / kFpuBN));
+    plan->block = kFpuThreads; plan->cluster = 1;
+    plan->smem_bytes = 2 * 2 * kFpuBK * (kFpuBM + kFpuPad) * 4;
+    plan->tile_m = kFpuBM; plan->tile_n = kFpuBN; plan->tile_k = kFpuBK; plan->stages = 2;
   } else {
     plan->grid = static_cast<int32_t>(((desc->m + kSimtTile - 1) / kSimtTile) * ((desc->n + kSimtTile - 1) / kSimtTile));
     plan->block = kSimtThreads; plan->cluster = 1;
@@ -248,9 +313,9 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
   if (fam == 1 && (desc->k == 0 || desc->alpha == 0.0)) fam = 3;  // nothing to multiply
   if (fam == 1) {
     TcLaunch L;
-    s = tc_plan(h, *desc, epi, a, b, c, d, &L);
-    if (s != GK_OK) return s;
-    s = tc_encode_maps(h, *desc, a, b, &L);
+    TcProblem pr;
+    tc_problem_from_gemm(*desc, epi, a, b, c, d, &pr);
+    s = tc_plan(h, pr, true, &L);
     if (s != GK_OK) return s;
     if (L.params.debug & 8) {
       if (!workspace) return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace");
@@ -258,6 +323,8 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     }
     return tc_launch(L, st);
   }
+  if (desc->k > 0 && desc->alpha != 0.0 && fpu_eligible(*desc, a, b, c, d, epi))
+    return launch_fpu(h, *desc, epi, a, b, c, d, st);
   return launch_simt(*desc, epi, a, b, c, d, st);
 }
 

@@ -64,8 +64,8 @@ struct gk_handle_s {
   gk::EncodeTiledFn encode_tiled = nullptr;
   std::mutex mu;                   // guards the caches below
   std::mutex host_mu;              // serialises gk_gemm_host calls (shared staging buffers)
-  int max_clusters[2][2][2] = {};  // tc kernel [planes-1][tf32][unused] -> co-resident CTA pairs
-  bool attr_set[2][2][2] = {};     // tc kernel [cg-1][planes-1][tf32]: smem attribute set
+  int max_clusters[2][4] = {};     // tc kernel [planes-1][tf32 + 2*rank5] -> co-resident CTA pairs
+  bool attr_set[2][2][4] = {};     // tc kernel [cg-1][planes-1][tf32 + 2*rank5]: smem attribute set
   // staging buffers of gk_gemm_host (grown on demand, freed by gk_destroy)
   void* stage_dev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, D, bias
   size_t stage_bytes[5] = {0, 0, 0, 0, 0};

@@ -1,0 +1,168 @@
+// FP32 GEMM on the CUDA cores (FPUOperator): results that must not go through the tensor cores.
+//
+//   D = act( alpha * op(A) * op(B) + beta * C + bias ),  all FP32, FP32 FMA accumulation in K order.
+//
+// 128 x 128 x 16 CTA tile, 256 threads, an 8 x 8 register tile per thread (two 4-wide strips along
+// M and along N), operands staged in shared memory as As[k][m] / Bs[k][n] so the inner loop is four
+// 16-byte shared loads per 64 FMAs.  Global loads are 16-byte vectors prefetched into registers one
+// k-tile ahead; an operand whose contiguous index is K (a transposed A, an untransposed B) is
+// transposed on its way into shared memory.  Two shared-memory buffers, one barrier per k-tile.
+//
+// Takes tile-multiple sizes and 16-byte aligned rows only (the reference's UnsafeAligned* layouts,
+// src/layout.jl:192-270); everything else goes to the generic kernel in simt_gemm.cuh.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gk {
+
+constexpr int kFpuBM = 128, kFpuBN = 128, kFpuBK = 16, kFpuThreads = 256, kFpuPad = 4;
+
+struct FpuParams {
+  const float* A;
+  const float* B;
+  const float* C;
+  float* D;
+  int M, N, K;
+  int64_t lda, ldb, ldc, ldd;
+  float alpha, beta;
+  const float* bias;
+  int bias_axis;  // 0 none, 1 per row, 2 per column
+  int act;        // 0 none, 1 relu, 2 gelu
+  int tiles_m, tiles_n;
+  int raster_group;
+};
+
+// Global -> registers for one operand tile: 2 float4 per thread.
+//   MN-contiguous: element (x, k) at base[x + k*ld]  (x = m or n): rows of 128 floats per k
+//   K-contiguous : element (x, k) at base[k + x*ld]               : rows of 16 floats per x
+template <bool KMAJOR>
+__device__ __forceinline__ void fpu_load_tile(const float* __restrict__ base, int64_t ld, int x0, int k0,
+                                              float4 (&r)[2]) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + i * kFpuThreads;
+    if constexpr (KMAJOR) {
+      const int x = idx >> 2, k4 = idx & 3;
+      r[i] = __ldg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(x0 + x) * ld + k0 + k4 * 4));
+    } else {
+      const int k = idx >> 5, x4 = idx & 31;
+      r[i] = __ldg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(k0 + k) * ld + x0 + x4 * 4));
+    }
+  }
+}
+
+template <bool KMAJOR>
+__device__ __forceinline__ void fpu_store_tile(float (*s)[kFpuBM + kFpuPad], const float4 (&r)[2], float scale) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + i * kFpuThreads;
+    float4 v = r[i];
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    if constexpr (KMAJOR) {
+      const int x = idx >> 2, k4 = idx & 3;
+      s[k4 * 4 + 0][x] = v.x; s[k4 * 4 + 1][x] = v.y; s[k4 * 4 + 2][x] = v.z; s[k4 * 4 + 3][x] = v.w;
+    } else {
+      const int k = idx >> 5, x4 = idx & 31;
+      *reinterpret_cast<float4*>(&s[k][x4 * 4]) = v;
+    }
+  }
+}
+
+__device__ __forceinline__ float fpu_act(float v, int act) {
+  if (act == 1) return fmaxf(v, 0.0f);
+  if (act == 2) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParams p) {
+  __shared__ __align__(16) float As[2][kFpuBK][kFpuBM + kFpuPad];
+  __shared__ __align__(16) float Bs[2][kFpuBK][kFpuBN + kFpuPad];
+
+  // tile raster: bands of `raster_group` tiles down M, then along N (same walk as the tcgen05 path)
+  int tm, tn;
+  {
+    const int t = blockIdx.x, g = p.raster_group;
+    const int band = g * p.tiles_n, band_id = t / band, first_m = band_id * g;
+    const int rows = min(g, p.tiles_m - first_m), r = t - band_id * band;
+    tm = first_m + r % rows;
+    tn = r / rows;
+  }
+  const int m0 = tm * kFpuBM, n0 = tn * kFpuBN;
+  const int tx = threadIdx.x & 15;  // strip along M
+  const int ty = threadIdx.x >> 4;  // strip along N
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+  float4 ra[2], rb[2];
+  const int kt_count = p.K / kFpuBK;
+  fpu_load_tile<A_KMAJOR>(p.A, p.lda, m0, 0, ra);
+  fpu_load_tile<B_KMAJOR>(p.B, p.ldb, n0, 0, rb);
+  // alpha scales A on its way in, as the reference's shared_to_regs_a transform does
+  fpu_store_tile<A_KMAJOR>(As[0], ra, p.alpha);
+  fpu_store_tile<B_KMAJOR>(Bs[0], rb, 1.0f);
+  __syncthreads();
+
+  for (int kt = 0; kt < kt_count; ++kt) {
+    const int cur = kt & 1;
+    const bool more = kt + 1 < kt_count;
+    if (more) {
+      fpu_load_tile<A_KMAJOR>(p.A, p.lda, m0, (kt + 1) * kFpuBK, ra);
+      fpu_load_tile<B_KMAJOR>(p.B, p.ldb, n0, (kt + 1) * kFpuBK, rb);
+    }
+#pragma unroll
+    for (int k = 0; k < kFpuBK; ++k) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[cur][k][tx * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[cur][k][64 + tx * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[cur][k][ty * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[cur][k][64 + ty * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (more) {
+      fpu_store_tile<A_KMAJOR>(As[cur ^ 1], ra, p.alpha);
+      fpu_store_tile<B_KMAJOR>(Bs[cur ^ 1], rb, 1.0f);
+    }
+    __syncthreads();
+  }
+
+  // epilogue: each thread owns rows m0 + {tx*4..+3, 64 + tx*4..+3} and columns n0 + {ty*4..+3, 64 + ..}
+#pragma unroll
+  for (int jh = 0; jh < 2; ++jh)
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = jh * 4 + jj;
+      const int n = n0 + jh * 64 + ty * 4 + jj;
+      const float bias_n = p.bias_axis == 2 ? __ldg(p.bias + n) : 0.0f;
+#pragma unroll
+      for (int ih = 0; ih < 2; ++ih) {
+        const int m = m0 + ih * 64 + tx * 4;
+        float4 v = make_float4(acc[ih * 4 + 0][j], acc[ih * 4 + 1][j], acc[ih * 4 + 2][j], acc[ih * 4 + 3][j]);
+        if (p.beta != 0.0f) {
+          const float4 c = *reinterpret_cast<const float4*>(p.C + m + static_cast<int64_t>(n) * p.ldc);
+          v.x = fmaf(p.beta, c.x, v.x); v.y = fmaf(p.beta, c.y, v.y);
+          v.z = fmaf(p.beta, c.z, v.z); v.w = fmaf(p.beta, c.w, v.w);
+        }
+        if (p.bias_axis == 1) {
+          const float4 bm = __ldg(reinterpret_cast<const float4*>(p.bias + m));
+          v.x += bm.x; v.y += bm.y; v.z += bm.z; v.w += bm.w;
+        } else {
+          v.x += bias_n; v.y += bias_n; v.z += bias_n; v.w += bias_n;
+        }
+        v.x = fpu_act(v.x, p.act); v.y = fpu_act(v.y, p.act);
+        v.z = fpu_act(v.z, p.act); v.w = fpu_act(v.w, p.act);
+        *reinterpret_cast<float4*>(p.D + m + static_cast<int64_t>(n) * p.ldd) = v;
+      }
+    }
+}
+
+}  // namespace gk

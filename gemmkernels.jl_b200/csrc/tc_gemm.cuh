@@ -60,6 +60,7 @@ struct TcParams {
   int32_t stages;
   int32_t a_mn_major, b_mn_major;
   int32_t a_boxes, b_boxes;  // TMA boxes per plane per CTA per k-block
+  int32_t a_box_mn, b_box_mn;  // M/N elements per box of an MN-major operand (one swizzle span)
   int32_t a_box_bytes, b_box_bytes;
   int32_t a_plane_bytes, b_plane_bytes;  // shared memory per plane per stage per CTA
   int32_t a_planes, b_planes;
@@ -69,10 +70,23 @@ struct TcParams {
   uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
   uint32_t a_swz, b_swz;      // descriptor swizzle field per operand (ptx.cuh: smem_desc_hi)
   uint32_t tmem_cols;         // power of two >= 2 * acc_planes * bn
-  // epilogue
+  // Tensor contractions split an index of the product in two modes: index = in + div * out.
+  // For a plain matrix the divisor is INT32_MAX (out == 0).  RANK5 kernels use these in the
+  // producers (5-D tensor maps: {in, out} of the contiguous index, {in, out} of the other, plane).
+  int32_t a_mn_div, a_k_div, b_mn_div, b_k_div;
+  // RANK5 only.  A tensor map lists its modes in order of increasing stride (what the TMA unit
+  // expects), so each box is one contiguous run times ONE other mode; a k-block (or a tile's rows)
+  // that spans two modes is fetched as `sub` boxes.  perm packs, 3 bits each, the tensor-map
+  // position of the coordinates (mn_in, mn_out, k_in, k_out).
+  int32_t a_sub, a_sub_step, a_sub_bytes, a_perm;
+  int32_t b_sub, b_sub_step, b_sub_bytes, b_perm;
+  // epilogue: element (m, n) of D is at d_sm0*(m % m_div) + d_sm1*(m / m_div)
+  //                                   + d_sn0*(n % n_div) + d_sn1*(n / n_div); same for C.
   const void* C;
   void* D;
-  int64_t ldc, ldd;           // elements between columns (of one plane / of interleaved pairs)
+  int32_t m_div, n_div;       // n_div is a multiple of 32 or >= N
+  int64_t c_sm0, c_sm1, c_sn0, c_sn1;
+  int64_t d_sm0, d_sm1, d_sn0, d_sn1;
   int64_t c_plane, d_plane;   // elements between planes; 0 = interleaved (re, im) pairs
   int32_t dtype_c, dtype_d;
   float alpha, beta;
@@ -81,7 +95,8 @@ struct TcParams {
   int32_t* status;
   int32_t debug;  // measurement/test aids, 0 in production: 1 = no TMA (barriers only),
                   // 2 = no MMA, 4 = producers issue nothing (lets the bounded waits run out),
-                  // 8 = per-role cycle counters written to dbg_out[blockIdx.x * 16 + i]
+                  // 8 = per-role cycle counters written to dbg_out[blockIdx.x * 16 + i],
+                  // 16 = CTA 0 leaves progress marks in the host-visible diagnostic words
   long long* dbg_out;
 };
 
@@ -90,6 +105,15 @@ __device__ __forceinline__ void tc_report(int32_t* status, int32_t code) {
   volatile int32_t* s = status;
   if (s != nullptr && *s == TC_ST_OK) {
     *s = code;
+    __threadfence_system();
+  }
+}
+
+// Progress mark (debug bit 16): word `slot` (1..15) of the host-visible diagnostic area.
+__device__ __forceinline__ void tc_mark(const int32_t* status, int debug, int slot, int32_t value) {
+  if ((debug & 16) && status != nullptr && blockIdx.x == 0) {
+    volatile int32_t* s = const_cast<int32_t*>(status);
+    s[slot] = value;
     __threadfence_system();
   }
 }
@@ -128,7 +152,7 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm
   tn = r / rows;
 }
 
-template <int CG, int PLANES, bool TF32>
+template <int CG, int PLANES, bool TF32, bool RANK5>
 __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes and the pattern is a function of the address.
@@ -179,6 +203,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
   if constexpr (CG == 2) cluster_sync_all();  // peer barriers are initialised before any remote use
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  if (threadIdx.x == 0) tc_mark(p.status, p.debug, 1, 1);   // set-up done, TMEM allocated
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int cluster_id = blockIdx.x / CG;
@@ -196,18 +221,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     // operands cost ~3x more cycles per copy than this form.)
     {
       const bool is_a = warp == 0;
-      const int n_boxes = is_a ? p.a_planes * p.a_boxes : p.b_planes * p.b_boxes;
+      const int subs = RANK5 ? (is_a ? p.a_sub : p.b_sub) : 1;
+      const int per_plane = (is_a ? p.a_boxes : p.b_boxes) * subs;
+      const int n_boxes = (is_a ? p.a_planes : p.b_planes) * per_plane;
       const bool active = lane < n_boxes;
-      const int bi = lane;
-      const int per_plane = is_a ? p.a_boxes : p.b_boxes;
-      const int pl = active ? bi / per_plane : 0;
-      const int bx = active ? bi % per_plane : 0;
+      const int pl = active ? lane / per_plane : 0;
+      const int bx = active ? (lane % per_plane) / subs : 0;   // which swizzle-span chunk
+      const int sb = active ? (lane % per_plane) % subs : 0;   // which sub-box of it (RANK5)
       const bool mn_major = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
+      const int sub_step = RANK5 ? (is_a ? p.a_sub_step : p.b_sub_step) : 0;
       const uint32_t dst_off =
-          is_a ? pl * p.a_plane_bytes + bx * p.a_box_bytes
-               : p.a_planes * p.a_plane_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes;
+          (is_a ? pl * p.a_plane_bytes + bx * p.a_box_bytes
+                : p.a_planes * p.a_plane_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes) +
+          (RANK5 ? sb * (is_a ? p.a_sub_bytes : p.b_sub_bytes) : 0);
       const void* tmap = is_a ? static_cast<const void*>(&p.tm_a) : static_cast<const void*>(&p.tm_b);
-      const int mn_add = mn_major ? bx * p.bk : 0;
+      const int mn_add = mn_major ? bx * (is_a ? p.a_box_mn : p.b_box_mn) : sb * sub_step;
+      [[maybe_unused]] const int k_add = mn_major ? sb * sub_step : 0;
+      [[maybe_unused]] const int perm = is_a ? p.a_perm : p.b_perm;
+      [[maybe_unused]] const int mn_div = is_a ? p.a_mn_div : p.b_mn_div;   // RANK5 only
+      [[maybe_unused]] const int k_div = is_a ? p.a_k_div : p.b_k_div;
       const uint32_t full0_signal = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
       const uint32_t tx_bytes = stage_bytes * CG;
       int s = 0;
@@ -231,6 +263,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
             ok = false;
             break;
           }
+          if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 1);   // about to issue first copies
           if (p.debug & 1) {
             if (lane == 0 && leader && is_a) mbar_arrive(bar_full + 8u * s);
           } else {
@@ -240,13 +273,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
             __syncwarp();
             if (active) {
               const int k0 = kb * p.bk;
-              const int c0 = mn_major ? mn : k0;
-              const int c1 = mn_major ? k0 : mn;
               const uint32_t dst = smem_base + s * stage_bytes + dst_off;
-              if constexpr (CG == 2) tma_load_3d_pair(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
-              else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
+              if constexpr (RANK5) {
+                // coordinates of (mn_in, mn_out, k_in, k_out), placed where the tensor map lists them
+                const int kk = k0 + k_add;
+                const int v[4] = {mn % mn_div, mn / mn_div, kk % k_div, kk / k_div};
+                int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const int pos = (perm >> (3 * q)) & 7;
+#pragma unroll
+                  for (int d = 0; d < 4; ++d) c[d] = (pos == d) ? v[q] : c[d];
+                }
+                if constexpr (CG == 2) tma_load_5d_pair(dst, tmap, full0_signal + 8u * s, c[0], c[1], c[2], c[3], pl);
+                else tma_load_5d(dst, tmap, full0_signal + 8u * s, c[0], c[1], c[2], c[3], pl);
+              } else {
+                const int c0 = mn_major ? mn : k0;
+                const int c1 = mn_major ? k0 : mn;
+                if constexpr (CG == 2) tma_load_3d_pair(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
+                else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
+              }
             }
           }
+          if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 2);   // first copies issued
           ++issued;
           if (++s == p.stages) { s = 0; ph ^= 1u; }
           if (prof) pi += clock64() - pt1;
@@ -333,6 +382,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
             break;
           }
           tc_fence_after_sync();
+          if (kb == 0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 1);   // first stage landed
 #pragma unroll
           for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
 #pragma unroll
@@ -346,6 +396,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
             }
           }
           if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
+          if (kb == 0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
           if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }
           if (prof) mi += clock64() - t1;
@@ -395,10 +446,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         break;
       }
       tc_fence_after_sync();
+      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, p.debug, 5, 1);   // first accumulator complete
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * acc_cols;
       const bool m_ok = m < p.M;
       float bias_row = 0.0f;
       if (p.bias_axis == TC_BIAS_ROW && m_ok) bias_row = p.bias[m];
+      const int m_in = m % p.m_div, m_out = m / p.m_div;
+      const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1;
+      const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1;
       for (int c = 0; c < p.bn; c += 32) {
         uint32_t v[PLANES][32];
 #pragma unroll
@@ -406,36 +461,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         tmem_ld_wait();
         const int ncols = p.N - (n0 + c);  // columns of this chunk inside the matrix (may be <= 0)
         if (!m_ok || ncols <= 0) continue;
+        const int n_in = (n0 + c) % p.n_div, n_out = (n0 + c) / p.n_div;  // a chunk never straddles n_div
         if (fast_store) {
           // FP32 output, no C, no per-column bias: one FMA (+ max) and one coalesced store per
           // column; a warp writes 32 consecutive rows = 128 bytes of a column of D.
-          float* dp = static_cast<float*>(p.D) + m + static_cast<int64_t>(n0 + c) * p.ldd;
+          float* dp = static_cast<float*>(p.D) + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
           if (ncols >= 32) {
             if (p.act == TC_ACT_RELU) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                dp[j * p.ldd] = fmaxf(fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row), 0.0f);
+                dp[j * p.d_sn0] = fmaxf(fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row), 0.0f);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                dp[j * p.ldd] = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
+                dp[j * p.d_sn0] = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (j < ncols) {
                 const float x = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
-                dp[j * p.ldd] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
+                dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
               }
             }
           }
         } else {
           const bool c_pairs = PLANES == 2 && p.c_plane == 0;
           const bool d_pairs = PLANES == 2 && p.d_plane == 0;
-          int64_t ci = m + static_cast<int64_t>(n0 + c) * p.ldc;  // element (m, n) of one plane
-          int64_t di = m + static_cast<int64_t>(n0 + c) * p.ldd;
+          int64_t ci = c_row + n_in * p.c_sn0 + n_out * p.c_sn1;  // element (m, n) of one plane
+          int64_t di = d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
 #pragma unroll
-          for (int j = 0; j < 32; ++j, ci += p.ldc, di += p.ldd) {
+          for (int j = 0; j < 32; ++j, ci += p.c_sn0, di += p.d_sn0) {
             if (j < ncols) {
               float bias = bias_row;
               if (p.bias_axis == TC_BIAS_COL) bias = p.bias[n0 + c + j];
@@ -466,6 +522,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * as);
         else mbar_arrive(bar_tempty + 8u * as);
       }
+      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, p.debug, 5, 2);   // first tile stored
       if ((p.debug & 8) && warp == 4 && lane == 0) {
         p.dbg_out[blockIdx.x * 16 + 7] += e1 - e0;
         p.dbg_out[blockIdx.x * 16 + 8] += clock64() - e1;

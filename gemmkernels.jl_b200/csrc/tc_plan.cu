@@ -44,46 +44,115 @@ bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::strin
   return true;
 }
 
-static gk_status encode_operand(gk_handle h, CUtensorMap* tm, const void* base, int32_t dt,
-                                int64_t contiguous_extent, int64_t strided_extent, int64_t ld,
-                                int planes, int64_t plane_stride, int box_contig, int box_strided,
-                                bool atom32) {
-  const int es = dtype_size(dt);
-  CUtensorMapDataType tdt = dt == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                            : dt == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(contiguous_extent),
-                        static_cast<cuuint64_t>(strided_extent), static_cast<cuuint64_t>(planes)};
-  cuuint64_t plane_bytes = planes > 1 ? static_cast<cuuint64_t>(plane_stride) * es
-                                      : static_cast<cuuint64_t>(ld) * es * strided_extent;
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es, plane_bytes};
-  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_contig), static_cast<cuuint32_t>(box_strided), 1};
+// Plain matrix operand -> 3-D tensor map {contiguous, strided, plane}.
+static gk_status encode_plain(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, int box_contig,
+                              int box_other, CUtensorMapSwizzle swizzle) {
+  const int es = dtype_size(op.dtype);
+  CUtensorMapDataType tdt = op.dtype == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                            : op.dtype == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const int64_t c_ext = op.mn_major ? op.mn_ext[0] : op.k_ext[0];
+  const int64_t o_ext = op.mn_major ? op.k_ext[0] : op.mn_ext[0];
+  const int64_t o_str = op.mn_major ? op.k_str[0] : op.mn_str[0];
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(c_ext), static_cast<cuuint64_t>(o_ext), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2];
+  strides[0] = static_cast<cuuint64_t>(o_str) * es;
+  strides[1] = planes > 1 ? static_cast<cuuint64_t>(op.plane_stride) * es : strides[0] * dims[1];
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_contig), static_cast<cuuint32_t>(box_other), 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = h->encode_tiled(tm, tdt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = h->encode_tiled(tm, tdt, 3, const_cast<void*>(op.ptr), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
-    return set_error(GK_ERR_INVALID_CONFIG,
-                     "cuTensorMapEncodeTiled failed (%d): extents (%lld, %lld, %d) ld %lld box (%d, %d)",
-                     static_cast<int>(r), static_cast<long long>(contiguous_extent),
-                     static_cast<long long>(strided_extent), planes, static_cast<long long>(ld),
-                     box_contig, box_strided);
+    return set_error(GK_ERR_INVALID_CONFIG, "cuTensorMapEncodeTiled failed (%d): extents (%llu, %llu, %llu) box (%u, %u)",
+                     static_cast<int>(r), (unsigned long long)dims[0], (unsigned long long)dims[1],
+                     (unsigned long long)dims[2], box[0], box[1]);
   return GK_OK;
 }
 
-template <int CG, int PLANES, bool TF32>
-static const void* tc_kernel_ptr() {
-  return reinterpret_cast<const void*>(&tc_gemm_kernel<CG, PLANES, TF32>);
+// Two-mode operands (contractions) use 5-D tensor maps whose modes are listed by increasing stride
+// (the contiguous one first, unit modes and the plane last), with nested strides as the TMA unit
+// expects.  order[i] = which of (0 mn_in, 1 mn_out, 2 k_in, 3 k_out) sits at position i; *perm packs
+// the position of each of the four, 3 bits apiece.  False when the strides are not nested.
+static bool plan_modes(const TcOperand& op, int order[4], int32_t* perm) {
+  const int64_t ext[4] = {op.mn_ext[0], op.mn_ext[1], op.k_ext[0], op.k_ext[1]};
+  const int64_t str[4] = {op.mn_str[0], op.mn_str[1], op.k_str[0], op.k_str[1]};
+  const int first = op.mn_major ? 0 : 2;
+  int idx[4] = {0, 1, 2, 3};
+  std::stable_sort(idx, idx + 4, [&](int x, int y) {
+    if ((x == first) != (y == first)) return x == first;
+    const bool ux = ext[x] <= 1, uy = ext[y] <= 1;
+    if (ux != uy) return uy;
+    return str[x] < str[y];
+  });
+  int64_t covered = 1;
+  for (int i = 0; i < 4; ++i) {
+    const int m = idx[i];
+    if (i > 0 && ext[m] > 1 && str[m] < covered) return false;   // modes overlap in memory
+    if (ext[m] > 1 || i == 0) covered = str[m] * ext[m];
+    order[i] = m;
+  }
+  *perm = 0;
+  for (int i = 0; i < 4; ++i) *perm |= i << (3 * order[i]);
+  return true;
 }
 
-static const void* tc_kernel_select(int cg, int planes, bool tf32) {
-  if (cg == 1) {
-    if (planes == 1) return tf32 ? tc_kernel_ptr<1, 1, true>() : tc_kernel_ptr<1, 1, false>();
-    return tf32 ? tc_kernel_ptr<1, 2, true>() : tc_kernel_ptr<1, 2, false>();
+// Each box is `box_contig` elements of the contiguous mode by `box_rows` of ONE other mode
+// (`row_mode`, numbered as above); every other mode has box 1.
+static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, int box_contig,
+                              int row_mode, int box_rows, CUtensorMapSwizzle swizzle) {
+  const int es = dtype_size(op.dtype);
+  CUtensorMapDataType tdt = op.dtype == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                            : op.dtype == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const int64_t ext[4] = {op.mn_ext[0], op.mn_ext[1], op.k_ext[0], op.k_ext[1]};
+  const int64_t str[4] = {op.mn_str[0], op.mn_str[1], op.k_str[0], op.k_str[1]};
+  int order[4];
+  int32_t perm;
+  if (!plan_modes(op, order, &perm))
+    return set_error(GK_ERR_INVALID_CONFIG, "tensor strides are not nested");
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+  cuuint64_t covered = 0;   // bytes spanned by the modes so far: the stride given to unit modes
+  for (int i = 0; i < 4; ++i) {
+    const int m = order[i];
+    dims[i] = static_cast<cuuint64_t>(ext[m]);
+    const cuuint64_t sbytes = (ext[m] > 1 || i == 0) ? static_cast<cuuint64_t>(str[m]) * es : covered;
+    if (i > 0) strides[i - 1] = sbytes;
+    covered = std::max<cuuint64_t>(covered, sbytes * dims[i]);
+    box[i] = i == 0 ? static_cast<cuuint32_t>(box_contig) : (m == row_mode ? static_cast<cuuint32_t>(box_rows) : 1u);
   }
-  if (planes == 1) return tf32 ? tc_kernel_ptr<2, 1, true>() : tc_kernel_ptr<2, 1, false>();
-  return tf32 ? tc_kernel_ptr<2, 2, true>() : tc_kernel_ptr<2, 2, false>();
+  dims[4] = static_cast<cuuint64_t>(planes);
+  strides[3] = planes > 1 ? static_cast<cuuint64_t>(op.plane_stride) * es : covered;
+  box[4] = 1;
+  CUresult r = h->encode_tiled(tm, tdt, 5, const_cast<void*>(op.ptr), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(GK_ERR_INVALID_CONFIG,
+                     "cuTensorMapEncodeTiled failed (%d): extents (%llu, %llu, %llu, %llu) box (%u, %u, %u, %u)",
+                     static_cast<int>(r), (unsigned long long)dims[0], (unsigned long long)dims[1],
+                     (unsigned long long)dims[2], (unsigned long long)dims[3], box[0], box[1], box[2], box[3]);
+  return GK_OK;
+}
+
+template <int CG, int PLANES, bool TF32, bool RANK5>
+static const void* tc_kernel_ptr() {
+  return reinterpret_cast<const void*>(&tc_gemm_kernel<CG, PLANES, TF32, RANK5>);
+}
+
+template <bool RANK5>
+static const void* tc_kernel_select_r(int cg, int planes, bool tf32) {
+  if (cg == 1) {
+    if (planes == 1) return tf32 ? tc_kernel_ptr<1, 1, true, RANK5>() : tc_kernel_ptr<1, 1, false, RANK5>();
+    return tf32 ? tc_kernel_ptr<1, 2, true, RANK5>() : tc_kernel_ptr<1, 2, false, RANK5>();
+  }
+  if (planes == 1) return tf32 ? tc_kernel_ptr<2, 1, true, RANK5>() : tc_kernel_ptr<2, 1, false, RANK5>();
+  return tf32 ? tc_kernel_ptr<2, 2, true, RANK5>() : tc_kernel_ptr<2, 2, false, RANK5>();
+}
+
+static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5) {
+  return rank5 ? tc_kernel_select_r<true>(cg, planes, tf32) : tc_kernel_select_r<false>(cg, planes, tf32);
 }
 
 static constexpr int kSmemBudget = 232448;  // 227 KiB opt-in limit per CTA on sm_100
@@ -93,11 +162,20 @@ static int stage_bytes_for(int cg, int bn, int a_planes, int b_planes) {
   return a_planes * kTcTileM * kTcKBytes + b_planes * (bn / cg) * kTcKBytes;
 }
 
+// Can a box of `total` elements starting at multiples of `total` be cut from an index whose inner
+// mode has extent ext0 (and whose outer mode continues it)?
+static bool box_fits(int64_t ext0, int64_t ext1, int total) {
+  if (ext1 <= 1) return true;                 // single mode: TMA clips at the end
+  if (ext0 >= total) return ext0 % total == 0;
+  return total % ext0 == 0 && total / ext0 <= 256;
+}
+
 // Picks (cta_group, tile_n): fewest "tile-time" units over the persistent grid, where a larger
 // tile is worth more per unit time (operand reuse) but quantises worse on small problems.
-static void choose_tile(const gk_gemm_desc& d, int sm_count, int planes, int* cg_out, int* bn_out) {
-  // a transposed (N-contiguous) B is loaded in boxes of 128 bytes of N per CTA
-  const int n_unit = d.trans_b ? kTcKBytes / dtype_size(d.dtype_b) : 8;
+static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_out, int* bn_out) {
+  // an N-contiguous B is loaded in boxes of 128 bytes of N per CTA
+  int n_unit = pr.B.mn_major ? kTcKBytes / dtype_size(pr.B.dtype) : 8;
+  if (pr.rank5 && pr.B.mn_major && pr.B.mn_ext[1] > 1 && pr.B.mn_ext[0] < n_unit) n_unit = static_cast<int>(pr.B.mn_ext[0]);
   struct Cand { int cg, bn; double eff; };
   static const Cand cands[] = {{2, 256, 1.00}, {1, 256, 0.92}, {2, 128, 0.80},
                                {1, 128, 0.74}, {1, 64, 0.50},  {1, 32, 0.30}};
@@ -106,37 +184,63 @@ static void choose_tile(const gk_gemm_desc& d, int sm_count, int planes, int* cg
   for (const Cand& c : cands) {
     if (planes * c.bn > 256) continue;  // two accumulator stages must fit 512 TMEM columns
     if ((c.bn / c.cg) % n_unit) continue;
-    if (d.cta_group && c.cg != d.cta_group) continue;
-    if (d.tile_n && c.bn != d.tile_n) continue;
-    const int64_t tm = (d.m + 128 * c.cg - 1) / (128 * c.cg);
-    const int64_t tn = (d.n + c.bn - 1) / c.bn;
+    if (pr.cta_group && c.cg != pr.cta_group) continue;
+    if (pr.tile_n && c.bn != pr.tile_n) continue;
+    if (!pr.B.mn_major && !box_fits(pr.B.mn_ext[0], pr.B.mn_ext[1], c.bn / c.cg)) continue;
+    if (!pr.B.mn_major && pr.B.mn_ext[1] > 1 && pr.B.mn_ext[0] < c.bn / c.cg && (c.bn / c.cg) / pr.B.mn_ext[0] > 16) continue;
+    if (pr.n_ext0 < pr.N && (pr.n_ext0 % 32 != 0)) continue;
+    const int64_t tm = (pr.M + 128 * c.cg - 1) / (128 * c.cg);
+    const int64_t tn = (pr.N + c.bn - 1) / c.bn;
     const int64_t slots = std::max(1, sm_count / c.cg);
     const int64_t waves = (tm * tn + slots - 1) / slots;
     const double t = static_cast<double>(waves) * c.bn / c.eff;
     if (t < best) { best = t; bcg = c.cg; bbn = c.bn; }
   }
   if (best == 1e300) {  // overrides that match no candidate: honour them if they are valid
-    bcg = d.cta_group ? d.cta_group : 1;
-    bbn = d.tile_n ? d.tile_n : 128;
+    bcg = pr.cta_group ? pr.cta_group : 1;
+    bbn = pr.tile_n ? pr.tile_n : 128;
   }
   *cg_out = bcg;
   *bn_out = bbn;
 }
 
-gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
-                  const void* b, const void* c, void* dd, TcLaunch* out) {
-  std::string why;
-  if (!tc_eligible(d, a ? a : reinterpret_cast<const void*>(16), b ? b : reinterpret_cast<const void*>(16), &why))
-    return set_error(GK_ERR_INVALID_CONFIG, "TCGen05Operator cannot take this GEMM: %s", why.c_str());
+void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
+                          const void* c, void* dd, TcProblem* out) {
+  TcProblem& pr = *out;
+  pr = TcProblem{};
+  pr.M = d.m; pr.N = d.n; pr.K = d.k; pr.number = d.number;
+  pr.A.ptr = a; pr.A.dtype = d.dtype_a; pr.A.mn_major = d.trans_a == 0;  // column-major M x K: M contiguous
+  pr.A.mn_ext[0] = d.m; pr.A.k_ext[0] = d.k;
+  pr.A.mn_str[0] = pr.A.mn_major ? 1 : d.lda; pr.A.k_str[0] = pr.A.mn_major ? d.lda : 1;
+  pr.A.plane_stride = d.plane_a;
+  pr.B.ptr = b; pr.B.dtype = d.dtype_b; pr.B.mn_major = d.trans_b != 0;  // column-major K x N: K contiguous
+  pr.B.mn_ext[0] = d.n; pr.B.k_ext[0] = d.k;
+  pr.B.mn_str[0] = pr.B.mn_major ? 1 : d.ldb; pr.B.k_str[0] = pr.B.mn_major ? d.ldb : 1;
+  pr.B.plane_stride = d.plane_b;
+  pr.C = (d.layout_c == GK_LAYOUT_ZERO) ? nullptr : c; pr.D = dd;
+  pr.dtype_c = d.dtype_c; pr.dtype_d = d.dtype_d;
+  pr.m_ext0 = d.m; pr.n_ext0 = d.n;
+  pr.c_sm[0] = 1; pr.c_sn[0] = d.ldc; pr.d_sm[0] = 1; pr.d_sn[0] = d.ldd;
+  pr.c_plane = d.plane_c; pr.d_plane = d.plane_d;
+  pr.alpha = d.alpha; pr.beta = d.beta; pr.epi = epi;
+  pr.tile_n = d.tile_n; pr.cta_group = d.cta_group; pr.stages = d.stages; pr.raster = d.raster;
+  pr.raster_group = d.raster_group; pr.max_ctas = d.max_ctas; pr.debug = d.reserved[0];
+}
 
+static int32_t clamp_div(int64_t ext0, int64_t ext1) {
+  if (ext1 <= 1 || ext0 >= INT32_MAX) return INT32_MAX;
+  return static_cast<int32_t>(ext0);
+}
+
+gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) {
   TcParams& p = out->params;
   std::memset(&p, 0, sizeof(p));
-  const int es = dtype_size(d.dtype_a);
-  const bool tf32 = d.dtype_a == GK_F32;
-  const int planes = d.number == GK_REAL ? 1 : 2;
+  const int es = dtype_size(pr.A.dtype);
+  const bool tf32 = pr.A.dtype == GK_F32;
+  const int planes = pr.number == GK_REAL ? 1 : 2;
 
   int cg, bn;
-  choose_tile(d, h->sm_count, planes, &cg, &bn);
+  choose_tile(pr, h->sm_count, planes, &cg, &bn);
   if (cg != 1 && cg != 2)
     return set_error(GK_ERR_INVALID_CONFIG, "cta_group must be 1 or 2, got %d", cg);
   if (bn < 32 || bn > 256 || bn % 32 || planes * bn > 256 || (cg == 2 && bn % 64))
@@ -144,66 +248,127 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
                      "tile_n = %d is not usable (multiple of 32 (64 for CTA pairs), <= %d)", bn,
                      256 / planes);
 
-  p.M = static_cast<int32_t>(d.m);
-  p.N = static_cast<int32_t>(d.n);
-  p.K = static_cast<int32_t>(d.k);
+  p.M = static_cast<int32_t>(pr.M);
+  p.N = static_cast<int32_t>(pr.N);
+  p.K = static_cast<int32_t>(pr.K);
   p.bn = bn;
   p.bk = kTcKBytes / es;
   p.k_blocks = (p.K + p.bk - 1) / p.bk;
   p.tiles_m = (p.M + kTcTileM * cg - 1) / (kTcTileM * cg);
   p.tiles_n = (p.N + bn - 1) / bn;
   p.a_planes = p.b_planes = planes;
-  p.a_mn_major = d.trans_a ? 0 : 1;  // column-major M x K: M is contiguous
-  p.b_mn_major = d.trans_b ? 1 : 0;  // column-major K x N: K is contiguous
+  p.a_mn_major = pr.A.mn_major ? 1 : 0;
+  p.b_mn_major = pr.B.mn_major ? 1 : 0;
   const int bn_cta = bn / cg;
-  const int mn_box_bytes = p.bk * p.bk * es;  // MN-major box: 128 B of M/N by one k-block
   p.a_plane_bytes = kTcTileM * kTcKBytes;
   p.b_plane_bytes = bn_cta * kTcKBytes;
-  // MN-major operands: 16-bit types use the plain 128-byte swizzle (atoms of 8 k rows, 1024 B);
-  // 32-bit types must use the 128-byte swizzle with 32-byte units (atoms of 4 k rows, 512 B).
-  // Either way one MMA consumes 32 / es rows of K, i.e. 2048 B (16-bit) or 1024 B (32-bit).
-  const uint32_t mn_sbo = es == 4 ? 512 : 1024;
-  const uint32_t mn_swz = es == 4 ? 1 : 2;
-  const uint32_t mn_kadv = (32 / es) * 128;
+  // MN-major operands are staged in boxes of one swizzle span of M/N by one k-block.  The span is
+  // 128 bytes, except for a contraction whose contiguous mode is only 64 or 32 bytes long: the box
+  // then is exactly that mode and the swizzle shrinks with it (a box is never narrower than its
+  // swizzle span).  Atoms are 8 k rows of one span (16-bit types); 32-bit types must use the
+  // 128-byte swizzle with 32-byte units (atoms of 4 k rows).  One MMA consumes 32 / es rows of K.
+  struct MnGeom { uint32_t span, box_mn, box_bytes, sbo, swz, kadv; CUtensorMapSwizzle tma; bool ok; };
+  auto mn_geom = [&](const TcOperand& op) {
+    MnGeom g{};
+    const int64_t inner_bytes = op.mn_ext[0] * es;
+    uint32_t span = 128;
+    if (pr.rank5 && op.mn_ext[1] > 1 && inner_bytes % 128 != 0) span = inner_bytes % 64 == 0 ? 64 : (inner_bytes % 32 == 0 ? 32 : 0);
+    g.ok = span != 0 && !(es == 4 && span != 128);
+    if (!g.ok) return g;
+    g.span = span; g.box_mn = span / es; g.box_bytes = span * p.bk;
+    if (es == 4) { g.sbo = 512; g.swz = 1; g.tma = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B; }
+    else {
+      g.sbo = 8 * span;
+      g.swz = span == 128 ? 2 : (span == 64 ? 4 : 6);
+      g.tma = span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (span == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    }
+    g.kadv = (32 / es) * span;
+    return g;
+  };
+  CUtensorMapSwizzle a_tma = CU_TENSOR_MAP_SWIZZLE_128B, b_tma = CU_TENSOR_MAP_SWIZZLE_128B;
+  p.a_box_mn = p.b_box_mn = p.bk;
   if (p.a_mn_major) {
-    p.a_boxes = kTcTileM / p.bk; p.a_box_bytes = mn_box_bytes;
-    p.a_lbo = mn_box_bytes; p.a_sbo = mn_sbo; p.a_kadv = mn_kadv; p.a_swz = mn_swz;
+    const MnGeom g = mn_geom(pr.A);
+    if (!g.ok) return set_error(GK_ERR_INVALID_CONFIG, "contiguous mode of A does not fill a swizzle span");
+    p.a_box_mn = g.box_mn; p.a_boxes = kTcTileM / g.box_mn; p.a_box_bytes = g.box_bytes;
+    p.a_lbo = g.box_bytes; p.a_sbo = g.sbo; p.a_kadv = g.kadv; p.a_swz = g.swz; a_tma = g.tma;
   } else {
     p.a_boxes = 1; p.a_box_bytes = p.a_plane_bytes;
     p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = 32; p.a_swz = 2;
   }
   if (p.b_mn_major) {
-    if (bn_cta % p.bk)
+    const MnGeom g = mn_geom(pr.B);
+    if (!g.ok) return set_error(GK_ERR_INVALID_CONFIG, "contiguous mode of B does not fill a swizzle span");
+    if (bn_cta % g.box_mn)
       return set_error(GK_ERR_INVALID_CONFIG, "tile_n = %d too small for a transposed B of this type", bn);
-    p.b_boxes = bn_cta / p.bk; p.b_box_bytes = mn_box_bytes;
-    p.b_lbo = mn_box_bytes; p.b_sbo = mn_sbo; p.b_kadv = mn_kadv; p.b_swz = mn_swz;
+    p.b_box_mn = g.box_mn; p.b_boxes = bn_cta / g.box_mn; p.b_box_bytes = g.box_bytes;
+    p.b_lbo = g.box_bytes; p.b_sbo = g.sbo; p.b_kadv = g.kadv; p.b_swz = g.swz; b_tma = g.tma;
   } else {
     p.b_boxes = 1; p.b_box_bytes = p.b_plane_bytes;
     p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32; p.b_swz = 2;
   }
+  if (planes * std::max(p.a_boxes, p.b_boxes) > 32)
+    return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
+  // Two-mode operands: a box covers one swizzle span of the contiguous mode and rows of ONE other
+  // mode; what a k-block (MN-major) or the tile's rows (K-major) need beyond that comes from
+  // `sub` boxes stepping through the outer mode.
+  int a_row_mode = 0, a_rows = 0, b_row_mode = 0, b_rows = 0;
+  p.a_sub = p.b_sub = 1;
+  if (pr.rank5) {
+    auto plan_sub = [&](const TcOperand& op, bool mn_major, int tile_rows, uint32_t row_bytes, int32_t* sub,
+                        int32_t* step, int32_t* sub_bytes, int* row_mode, int* rows) -> bool {
+      const int need = mn_major ? p.bk : tile_rows;       // rows of one chunk
+      const int64_t* e = mn_major ? op.k_ext : op.mn_ext;
+      *row_mode = mn_major ? 2 : 0;
+      if (e[1] <= 1 || e[0] % need == 0) { *rows = need; *sub = 1; }
+      else if (need % e[0] == 0) { *rows = static_cast<int>(e[0]); *sub = need / *rows; }
+      else return false;
+      *step = *rows;
+      *sub_bytes = static_cast<int32_t>(*rows * row_bytes);
+      // K-major operands need whole 128-byte runs of their inner contracted mode
+      if (!mn_major && op.k_ext[1] > 1 && op.k_ext[0] % p.bk != 0) return false;
+      // MN-major operands: the chunk must be cut from the inner mode
+      if (mn_major && op.mn_ext[1] > 1 && op.mn_ext[0] % (mn_major ? (&op == &pr.A ? p.a_box_mn : p.b_box_mn) : 1) != 0) return false;
+      return true;
+    };
+    const uint32_t a_row_bytes = p.a_mn_major ? static_cast<uint32_t>(p.a_box_bytes / p.bk) : kTcKBytes;
+    const uint32_t b_row_bytes = p.b_mn_major ? static_cast<uint32_t>(p.b_box_bytes / p.bk) : kTcKBytes;
+    int order[4];
+    const bool ok =
+        plan_sub(pr.A, p.a_mn_major != 0, kTcTileM, a_row_bytes, &p.a_sub, &p.a_sub_step, &p.a_sub_bytes, &a_row_mode, &a_rows) &&
+        plan_sub(pr.B, p.b_mn_major != 0, bn_cta, b_row_bytes, &p.b_sub, &p.b_sub_step, &p.b_sub_bytes, &b_row_mode, &b_rows) &&
+        plan_modes(pr.A, order, &p.a_perm) && plan_modes(pr.B, order, &p.b_perm) &&
+        planes * p.a_boxes * p.a_sub <= 32 && planes * p.b_boxes * p.b_sub <= 32;
+    if (!ok)
+      return set_error(GK_ERR_INVALID_CONFIG, "tensor modes do not tile into TMA boxes (extents or strides)");
+  }
+  p.a_mn_div = clamp_div(pr.A.mn_ext[0], pr.A.mn_ext[1]);
+  p.a_k_div = clamp_div(pr.A.k_ext[0], pr.A.k_ext[1]);
+  p.b_mn_div = clamp_div(pr.B.mn_ext[0], pr.B.mn_ext[1]);
+  p.b_k_div = clamp_div(pr.B.k_ext[0], pr.B.k_ext[1]);
 
   // terms of the product
   auto term = [](int ap, int bp, int acc, int neg, int first) {
     TcTerm t{}; t.a_plane = ap; t.b_plane = bp; t.acc_plane = acc; t.negate_a = neg; t.first = first;
     return t;
   };
-  if (d.number == GK_REAL) {
+  if (pr.number == GK_REAL) {
     p.n_terms = 1; p.terms[0] = term(0, 0, 0, 0, 1);
-  } else if (d.number == GK_COMPLEX) {
+  } else if (pr.number == GK_COMPLEX) {
     // re = a_re b_re - a_im b_im ; im = a_re b_im + a_im b_re   (src/operator.jl:301-314)
     p.n_terms = 4;
     p.terms[0] = term(0, 0, 0, 0, 1); p.terms[1] = term(1, 1, 0, 1, 0);
     p.terms[2] = term(0, 1, 1, 0, 1); p.terms[3] = term(1, 0, 1, 0, 0);
-  } else if (d.number == GK_DUAL) {
+  } else if (pr.number == GK_DUAL) {
     // re = a_re b_re ; du = a_re b_du + a_du b_re               (src/operator.jl:360-372)
     p.n_terms = 3;
     p.terms[0] = term(0, 0, 0, 0, 1);
     p.terms[1] = term(0, 1, 1, 0, 1); p.terms[2] = term(1, 0, 1, 0, 0);
   } else {
-    return set_error(GK_ERR_INVALID_CONFIG, "unknown number system %d", d.number);
+    return set_error(GK_ERR_INVALID_CONFIG, "unknown number system %d", pr.number);
   }
 
-  const uint32_t fmt = d.dtype_a == GK_F16 ? 0u : d.dtype_a == GK_BF16 ? 1u : 2u;
+  const uint32_t fmt = pr.A.dtype == GK_F16 ? 0u : pr.A.dtype == GK_BF16 ? 1u : 2u;
   uint32_t idesc = 0;
   idesc |= 1u << 4;                                   // accumulate in FP32
   idesc |= fmt << 7;                                  // A format
@@ -218,7 +383,7 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
   const int stage_bytes = stage_bytes_for(cg, bn, planes, planes);
   int stages = (kSmemBudget - 1024 - kCtrlBytes) / stage_bytes;
   stages = std::min(stages, 8);
-  if (d.stages) stages = std::min(stages, d.stages);
+  if (pr.stages) stages = std::min(stages, pr.stages);
   stages = std::min(stages, std::max(2, p.k_blocks));
   if (stages < 2)
     return set_error(GK_ERR_INVALID_CONFIG, "Requested too much shared memory: one pipeline stage needs %d bytes", stage_bytes);
@@ -229,45 +394,51 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
 
   // raster
   const int slots_guess = std::max(1, h->sm_count / cg);
-  int group = d.raster_group;
-  if (d.raster == GK_RASTER_IDENTITY) group = p.tiles_m;
+  int group = pr.raster_group;
+  if (pr.raster == GK_RASTER_IDENTITY) group = p.tiles_m;
   if (group <= 0)
     group = static_cast<int>(std::lround(std::sqrt(static_cast<double>(slots_guess) * bn / (kTcTileM * cg))));
   p.raster_group = std::max(1, std::min(group, p.tiles_m));
 
   // epilogue
-  p.C = c; p.D = dd;
-  p.ldc = d.ldc; p.ldd = d.ldd;
-  p.c_plane = d.plane_c; p.d_plane = d.plane_d;
-  p.dtype_c = tc_dtype_of(d.dtype_c); p.dtype_d = tc_dtype_of(d.dtype_d);
-  p.alpha = static_cast<float>(d.alpha);
-  p.beta = (d.layout_c == GK_LAYOUT_ZERO || c == nullptr) ? 0.0f : static_cast<float>(d.beta);
+  if (pr.n_ext0 < pr.N && pr.n_ext0 % 32 != 0)
+    return set_error(GK_ERR_INVALID_CONFIG, "inner N mode of the output must be a multiple of 32 elements");
+  p.C = pr.C; p.D = pr.D;
+  p.m_div = clamp_div(pr.m_ext0, pr.m_ext0 < pr.M ? 2 : 1);
+  p.n_div = clamp_div(pr.n_ext0, pr.n_ext0 < pr.N ? 2 : 1);
+  p.c_sm0 = pr.c_sm[0]; p.c_sm1 = pr.c_sm[1]; p.c_sn0 = pr.c_sn[0]; p.c_sn1 = pr.c_sn[1];
+  p.d_sm0 = pr.d_sm[0]; p.d_sm1 = pr.d_sm[1]; p.d_sn0 = pr.d_sn[0]; p.d_sn1 = pr.d_sn[1];
+  p.c_plane = pr.c_plane; p.d_plane = pr.d_plane;
+  p.dtype_c = tc_dtype_of(pr.dtype_c); p.dtype_d = tc_dtype_of(pr.dtype_d);
+  p.alpha = static_cast<float>(pr.alpha);
+  p.beta = pr.C == nullptr ? 0.0f : static_cast<float>(pr.beta);
   p.bias = nullptr; p.bias_axis = TC_BIAS_NONE; p.act = TC_ACT_NONE;
-  if (epi) {
-    if (epi->bias_axis != GK_BIAS_NONE) {
-      if (!epi->bias && a) return set_error(GK_ERR_INVALID_ARGUMENT, "bias axis set but bias pointer is NULL");
-      p.bias = epi->bias; p.bias_axis = epi->bias_axis;
+  if (pr.epi) {
+    if (pr.epi->bias_axis != GK_BIAS_NONE) {
+      if (!pr.epi->bias && encode) return set_error(GK_ERR_INVALID_ARGUMENT, "bias axis set but bias pointer is NULL");
+      p.bias = pr.epi->bias; p.bias_axis = pr.epi->bias_axis;
     }
-    if (epi->activation < GK_ACT_NONE || epi->activation > GK_ACT_GELU)
-      return set_error(GK_ERR_UNSUPPORTED, "activation %d is not one of none/ReLU/GELU", epi->activation);
-    p.act = epi->activation;
+    if (pr.epi->activation < GK_ACT_NONE || pr.epi->activation > GK_ACT_GELU)
+      return set_error(GK_ERR_UNSUPPORTED, "activation %d is not one of none/ReLU/GELU", pr.epi->activation);
+    p.act = pr.epi->activation;
   }
   p.status = h->status_dev;
-  p.debug = d.reserved[0];
+  p.debug = pr.debug;
   p.dbg_out = nullptr;
 
   out->cg = cg;
   out->planes = planes;
   out->tf32 = tf32;
+  out->rank5 = pr.rank5;
   out->smem_bytes = stages * stage_bytes + kCtrlBytes + 1024;
-  out->kernel = tc_kernel_select(cg, planes, tf32);
+  out->kernel = tc_kernel_select(cg, planes, tf32, pr.rank5);
 
   // persistent grid
   const int tiles = p.tiles_m * p.tiles_n;
   int slots;
   {
     std::lock_guard<std::mutex> lock(h->mu);
-    bool& set = h->attr_set[cg - 1][planes - 1][tf32 ? 1 : 0];
+    bool& set = h->attr_set[cg - 1][planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
     if (!set) {
       GK_CUDA_CHECK(cudaFuncSetAttribute(out->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
       set = true;
@@ -275,7 +446,7 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
     if (cg == 1) {
       slots = h->sm_count;
     } else {
-      int& cached = h->max_clusters[planes - 1][tf32 ? 1 : 0][0];
+      int& cached = h->max_clusters[planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
       if (cached == 0) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * (h->sm_count / 2));
@@ -293,8 +464,22 @@ gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* ep
       slots = cached;
     }
   }
-  if (d.max_ctas > 0) slots = std::max(1, std::min(slots, d.max_ctas / cg));
+  if (pr.max_ctas > 0) slots = std::max(1, std::min(slots, pr.max_ctas / cg));
   out->grid = cg * std::min(tiles, slots);
+
+  if (encode) {
+    gk_status s;
+    if (pr.rank5) {
+      s = encode_modes(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, a_row_mode, a_rows, a_tma);
+      if (s != GK_OK) return s;
+      s = encode_modes(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, b_row_mode, b_rows, b_tma);
+    } else {
+      s = encode_plain(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, p.a_mn_major ? p.bk : kTcTileM, a_tma);
+      if (s != GK_OK) return s;
+      s = encode_plain(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, p.b_mn_major ? p.bk : bn_cta, b_tma);
+    }
+    if (s != GK_OK) return s;
+  }
   return GK_OK;
 }
 
@@ -313,23 +498,6 @@ gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {
   void* args[1] = {const_cast<TcParams*>(&L.params)};
   GK_CUDA_CHECK(cudaLaunchKernelExC(&cfg, L.kernel, args));
   return GK_OK;
-}
-
-gk_status tc_encode_maps(gk_handle h, const gk_gemm_desc& d, const void* a, const void* b, TcLaunch* L) {
-  TcParams& p = L->params;
-  const int planes = L->planes;
-  const int bn_cta = p.bn / L->cg;
-  gk_status s;
-  if (p.a_mn_major)
-    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.m, d.k, d.lda, planes, d.plane_a, p.bk, p.bk, p.a_swz == 1);
-  else
-    s = encode_operand(h, &p.tm_a, a, d.dtype_a, d.k, d.m, d.lda, planes, d.plane_a, p.bk, kTcTileM, false);
-  if (s != GK_OK) return s;
-  if (p.b_mn_major)
-    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.n, d.k, d.ldb, planes, d.plane_b, p.bk, p.bk, p.b_swz == 1);
-  else
-    s = encode_operand(h, &p.tm_b, b, d.dtype_b, d.k, d.n, d.ldb, planes, d.plane_b, p.bk, bn_cta, false);
-  return s;
 }
 
 }  // namespace gk

@@ -7,22 +7,51 @@
 
 namespace gk {
 
+// An operand of the product as the tcgen05 path sees it.  An index (M or N, and K) may be split in
+// two modes: index = in + ext[0] * out, with its own stride per mode (tensor contractions); plain
+// matrices have ext[1] == 1.
+struct TcOperand {
+  const void* ptr = nullptr;
+  int32_t dtype = 0;
+  bool mn_major = false;         // the stride-1 index is the M/N index (else the K index)
+  int64_t mn_ext[2] = {1, 1}, mn_str[2] = {0, 0};
+  int64_t k_ext[2] = {1, 1}, k_str[2] = {0, 0};
+  int64_t plane_stride = 0;      // complex / dual: elements between the two planes
+};
+
+struct TcProblem {
+  int64_t M = 0, N = 0, K = 0;
+  int32_t number = GK_REAL;
+  TcOperand A, B;
+  bool rank5 = false;            // operands need the two-mode split (5-D tensor maps)
+  // output / C: two-mode split of M and N with strides per mode
+  const void* C = nullptr;
+  void* D = nullptr;
+  int32_t dtype_c = GK_F32, dtype_d = GK_F32;
+  int64_t m_ext0 = 0, n_ext0 = 0;           // inner extents (== M, N for plain matrices)
+  int64_t c_sm[2] = {1, 0}, c_sn[2] = {0, 0}, d_sm[2] = {1, 0}, d_sn[2] = {0, 0};
+  int64_t c_plane = 0, d_plane = 0;
+  double alpha = 1.0, beta = 0.0;
+  const gk_epilogue_desc* epi = nullptr;
+  int32_t tile_n = 0, cta_group = 0, stages = 0, raster = 0, raster_group = 0, max_ctas = 0, debug = 0;
+};
+
 struct TcLaunch {
   TcParams params;
   const void* kernel = nullptr;
   int cg = 1, planes = 1;
-  bool tf32 = false;
+  bool tf32 = false, rank5 = false;
   int grid = 0;
   int smem_bytes = 0;
 };
 
 // True when the descriptor (and, if given, the operand addresses) can go through TMA + tcgen05.
 bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::string* why);
-// Fills everything but the tensor maps (tile choice, descriptors, grid, epilogue).
-gk_status tc_plan(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
-                  const void* b, const void* c, void* dd, TcLaunch* out);
-// Encodes the TMA tensor maps of A and B for the planned tile.
-gk_status tc_encode_maps(gk_handle h, const gk_gemm_desc& d, const void* a, const void* b, TcLaunch* L);
+// gk_gemm_desc -> TcProblem (plain matrices).
+void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
+                          const void* c, void* dd, TcProblem* out);
+// Tile choice, descriptors, grid, epilogue and (when `encode`) the TMA tensor maps.
+gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out);
 gk_status tc_launch(const TcLaunch& L, cudaStream_t stream);
 
 }  // namespace gk

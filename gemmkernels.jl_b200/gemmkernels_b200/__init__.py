@@ -20,6 +20,7 @@ from . import layout as Layout
 from . import operator as Operator
 from . import transform as Transform
 from .arrays import cuarray, to_cuarray, to_numpy
+from .contract import contract_, contract_query
 from .config import Config, ConfigError, DimensionMismatch, get_config, heuristic_block_shape
 from .eltypes import (BFloat16, ComplexF16, ComplexF32, Float16, Float32, Float64, Int16, Int32, Int64)
 from .matmul import (DeviceTimeout, GemmKernelsError, create_config, handle, lower, matmatmul_, matmul,
@@ -28,7 +29,7 @@ from .matmul import (DeviceTimeout, GemmKernelsError, create_config, handle, low
 __all__ = [
     "CTASwizzle", "Epilogue", "Kernel", "Layout", "Operator", "Transform",
     "Config", "ConfigError", "DimensionMismatch", "get_config", "heuristic_block_shape",
-    "matmul", "matmul_host", "matmatmul_", "mul_", "query", "lower", "create_config", "handle", "poll_status",
+    "contract_", "contract_query", "matmul", "matmul_host", "matmatmul_", "mul_", "query", "lower", "create_config", "handle", "poll_status",
     "cuarray", "to_cuarray", "to_numpy",
     "Float16", "BFloat16", "Float32", "Float64", "Int16", "Int32", "Int64", "ComplexF16", "ComplexF32",
     "GemmKernelsError", "DeviceTimeout",

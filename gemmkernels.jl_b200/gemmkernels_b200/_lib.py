@@ -26,8 +26,9 @@ GK_RASTER_AUTO, GK_RASTER_IDENTITY, GK_RASTER_HORIZONTAL, GK_RASTER_VERTICAL, GK
 
 EXPORTS = (
     "gk_version", "gk_last_error_message", "gk_create", "gk_destroy", "gk_poll_status",
-    "gk_gemm_query", "gk_gemm", "gk_gemm_host",
+    "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks",
 )
+GK_MAX_MODES = 8
 
 
 class GemmDesc(C.Structure):
@@ -73,6 +74,25 @@ class GemmPlan(C.Structure):
     ]
 
 
+class ContractDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("rank_a", C.c_int32), ("rank_b", C.c_int32), ("rank_c", C.c_int32),
+        ("modes_a", C.c_int32 * 8), ("modes_b", C.c_int32 * 8), ("modes_c", C.c_int32 * 8),
+        ("extents_a", C.c_int64 * 8), ("extents_b", C.c_int64 * 8), ("extents_c", C.c_int64 * 8),
+        ("strides_a", C.c_int64 * 8), ("strides_b", C.c_int64 * 8), ("strides_c", C.c_int64 * 8),
+        ("strides_d", C.c_int64 * 8),
+        ("dtype_a", C.c_int32), ("dtype_b", C.c_int32), ("dtype_c", C.c_int32), ("dtype_d", C.c_int32),
+        ("compute", C.c_int32), ("force_gather", C.c_int32),
+        ("alpha", C.c_double), ("beta", C.c_double),
+        ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32),
+        ("reserved", C.c_int32 * 3),
+    ]
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.struct_size = C.sizeof(ContractDesc)
+
+
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
@@ -97,6 +117,13 @@ def _load() -> C.CDLL:
     lib.gk_gemm_host.restype = C.c_int
     lib.gk_gemm_host.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p]
+    lib.gk_debug_marks.restype = C.c_int
+    lib.gk_debug_marks.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    lib.gk_contract_query.restype = C.c_int
+    lib.gk_contract_query.argtypes = [C.c_void_p, C.POINTER(ContractDesc), C.POINTER(GemmPlan)]
+    lib.gk_contract.restype = C.c_int
+    lib.gk_contract.argtypes = [C.c_void_p, C.POINTER(ContractDesc), C.c_void_p, C.c_void_p, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
     return lib
 
 

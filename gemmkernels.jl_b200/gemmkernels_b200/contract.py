@@ -1,0 +1,88 @@
+"""Tensor contraction entry point: `contract_(D, modes_d, A, modes_a, B, modes_b, alpha, beta, C)`.
+
+The reference ships no contraction function; its benchmark
+(benchmarks/tensor-contractions/run.jl:88-131) expresses one contraction through custom Layouts.
+This is the entry point the engine defines for it (Julia: `GemmKernels.contract!`): mode strings as
+in the TCCG benchmark notation, tensors read in place with their own strides.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib as L
+from . import arrays
+from .matmul import _raise, handle
+from .operator import TF32
+
+
+def _desc(D, modes_d, A, modes_a, B, modes_b, alpha, beta, Cin, compute, force_gather, tile_n, cta_group):
+    for name, t, modes in (("A", A, modes_a), ("B", B, modes_b), ("D", D, modes_d)):
+        if t.dim() != len(modes):
+            raise ValueError(f"{name} has {t.dim()} dimensions but {len(modes)} modes ('{modes}')")
+        if len(modes) > L.GK_MAX_MODES:
+            raise ValueError(f"at most {L.GK_MAX_MODES} modes per tensor")
+    d = L.ContractDesc(rank_a=len(modes_a), rank_b=len(modes_b), rank_c=len(modes_d), alpha=float(alpha),
+                       beta=float(beta), force_gather=int(force_gather), tile_n=tile_n, cta_group=cta_group)
+    for i, ch in enumerate(modes_a):
+        d.modes_a[i], d.extents_a[i], d.strides_a[i] = ord(ch), A.shape[i], A.stride(i)
+    for i, ch in enumerate(modes_b):
+        d.modes_b[i], d.extents_b[i], d.strides_b[i] = ord(ch), B.shape[i], B.stride(i)
+    csrc = Cin if Cin is not None else D
+    for i, ch in enumerate(modes_d):
+        d.modes_c[i], d.extents_c[i] = ord(ch), D.shape[i]
+        d.strides_d[i], d.strides_c[i] = D.stride(i), csrc.stride(i)
+    ea, eb, ed = arrays.eltype_of(A), arrays.eltype_of(B), arrays.eltype_of(D)
+    d.dtype_a, d.dtype_b, d.dtype_d = ea.gk, eb.gk, ed.gk
+    d.dtype_c = arrays.eltype_of(csrc).gk
+    if compute is None:
+        compute = {"Float16": L.GK_F16, "BFloat16": L.GK_BF16}.get(ea.name, L.GK_F32)
+    elif compute is TF32:
+        compute = L.GK_TF32
+    elif not isinstance(compute, int):
+        compute = compute.gk
+    d.compute = compute
+    return d
+
+
+def contract_query(D, modes_d, A, modes_a, B, modes_b, alpha=1.0, beta=0.0, C_in=None, *, compute=None,
+                   force_gather=False, tile_n=0, cta_group=0) -> L.GemmPlan:
+    """Which kernel `contract_` would use and how much workspace it needs."""
+    d = _desc(D, modes_d, A, modes_a, B, modes_b, alpha, beta, C_in, compute, force_gather, tile_n, cta_group)
+    plan = L.GemmPlan()
+    st = L.lib.gk_contract_query(handle(), C.byref(d), C.byref(plan))
+    if st != L.GK_OK:
+        _raise(st)
+    return plan
+
+
+def contract_(D, modes_d: str, A, modes_a: str, B, modes_b: str, alpha=1.0, beta=0.0, C_in=None, *,
+              compute=None, workspace=None, force_gather=False, tile_n=0, cta_group=0, stream=None):
+    """D[modes_d] = alpha * sum over shared modes of A[modes_a] * B[modes_b] + beta * C[modes_d].
+
+    Tensors are torch CUDA tensors with any strides (Julia arrays are column-major: use `cuarray`).
+    C defaults to D (in place) when beta != 0.  If the contraction needs the gather kernel and no
+    `workspace` (uint8/int64 CUDA tensor) is given, one is allocated with torch for this call.
+    Returns D."""
+    import torch
+    if beta != 0 and C_in is None:
+        C_in = D
+    d = _desc(D, modes_d, A, modes_a, B, modes_b, alpha, beta, C_in, compute, force_gather, tile_n, cta_group)
+    dev = D.device.index if D.device.index is not None else torch.cuda.current_device()
+    ws_ptr, ws_bytes = None, 0
+    with torch.cuda.device(dev):
+        h = handle(dev)
+        if workspace is None:
+            plan = L.GemmPlan()
+            st = L.lib.gk_contract_query(h, C.byref(d), C.byref(plan))
+            if st != L.GK_OK:
+                _raise(st)
+            if plan.workspace_bytes:
+                workspace = torch.empty(plan.workspace_bytes // 8 + 1, dtype=torch.int64, device=D.device)
+        if workspace is not None:
+            ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+        st = L.lib.gk_contract(h, C.byref(d), A.data_ptr(), B.data_ptr(), C_in.data_ptr() if C_in is not None else None,
+                               D.data_ptr(), ws_ptr, ws_bytes, C.c_void_p(s))
+    if st != L.GK_OK:
+        _raise(st)
+    return D

@@ -130,7 +130,8 @@ typedef struct gk_epilogue_desc {
 } gk_epilogue_desc;
 
 typedef struct gk_gemm_plan {
-  int32_t kernel;       /* 1 = tcgen05, 2 = FPU (SIMT FFMA), 3 = generic SIMT, 4 = diagonal scale */
+  int32_t kernel;       /* 1 = tcgen05, 2 = FPU (SIMT FFMA), 3 = generic SIMT, 4 = diagonal scale,
+                           5 = contraction gather kernel */
   int32_t grid, block, cluster;
   int32_t smem_bytes, tmem_columns;
   int32_t tile_m, tile_n, tile_k, stages;
@@ -152,6 +153,11 @@ GK_API gk_status gk_destroy(gk_handle h);
  * a kernel launched through this handle abandoned a wait since the last call. */
 GK_API gk_status gk_poll_status(gk_handle h, int32_t* raw_code);
 
+/* Copies the 16 host-visible diagnostic words of the handle: word 0 is the status word above; words
+ * 1..15 are progress marks that tcgen05 kernels launched with the debug-marks bit leave behind
+ * (how far each role got).  Reads host memory only: usable even after the context has failed. */
+GK_API gk_status gk_debug_marks(gk_handle h, int32_t* out16);
+
 /* Fills *plan with what gk_gemm would launch for this descriptor; launches nothing. */
 GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
                         gk_gemm_plan* plan);
@@ -162,6 +168,45 @@ GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_e
 GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
                   gk_stream stream);
+
+/*
+ * Tensor contraction (GETT): D[modes_c] = alpha * sum over contracted modes of A[modes_a] * B[modes_b]
+ * + beta * C[modes_c].  The reference has no such function in src/; this replaces the driver of
+ * benchmarks/tensor-contractions/run.jl:88-131 (custom layouts that map one contraction onto the
+ * GEMM kernels) with an entry point, e.g. GemmKernels.contract!(D, "abcd", A, "aebf", B, "dfce").
+ * A mode label is any integer (characters, usually).  A label in A and C is a free mode of A, in B
+ * and C a free mode of B, in A and B a contracted mode; a label in all three is rejected.  Strides
+ * are in elements and arbitrary (column-major tensors have strides 1, e0, e0*e1, ...); C and D share
+ * modes_c / extents_c and have their own strides.  Tensors are read in place: when every index
+ * splits into at most two modes that tile into TMA boxes the tensor cores run it through 5-D tensor
+ * maps; otherwise a gather kernel runs it and needs a workspace (gk_contract_query reports
+ * plan.kernel == 5 and plan.workspace_bytes).
+ */
+#define GK_MAX_MODES 8
+
+typedef struct gk_contract_desc {
+  uint32_t struct_size;
+  int32_t rank_a, rank_b, rank_c;
+  int32_t modes_a[GK_MAX_MODES], modes_b[GK_MAX_MODES], modes_c[GK_MAX_MODES];
+  int64_t extents_a[GK_MAX_MODES], extents_b[GK_MAX_MODES], extents_c[GK_MAX_MODES];
+  int64_t strides_a[GK_MAX_MODES], strides_b[GK_MAX_MODES], strides_c[GK_MAX_MODES],
+      strides_d[GK_MAX_MODES];
+  int32_t dtype_a, dtype_b, dtype_c, dtype_d; /* gk_dtype */
+  int32_t compute;      /* F16 / BF16 / TF32: tensor cores when possible; F32: gather kernel */
+  int32_t force_gather; /* 1 = always use the gather kernel (testing) */
+  double alpha, beta;
+  int32_t tile_n, cta_group, stages; /* tuning overrides, 0 = choose */
+  int32_t reserved[3];
+} gk_contract_desc;
+
+GK_API gk_status gk_contract_query(gk_handle h, const gk_contract_desc* desc, gk_gemm_plan* plan);
+
+/* Enqueues the contraction on `stream`.  c may be NULL when beta == 0; c == d is allowed.
+ * workspace / workspace_bytes: device scratch for the gather path (offset tables, 8-byte aligned);
+ * may be NULL / 0 when the query reports workspace_bytes == 0. */
+GK_API gk_status gk_contract(gk_handle h, const gk_contract_desc* desc, const void* a, const void* b,
+                             const void* c, void* d, void* workspace, int64_t workspace_bytes,
+                             gk_stream stream);
 
 /* The same GEMM for callers whose matrices live in host memory (Julia `Array`s rather than
  * `CuArray`s; the reference has no such method — CUDA.jl users would `CuArray(A)` first, which is

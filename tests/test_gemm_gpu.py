@@ -367,3 +367,62 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     GK.mul_(c, a, a)
     torch.cuda.synchronize(); GK.poll_status()
     assert torch.all(c == n)
+
+
+# ------------------------------------------------------------------------------------------------
+# tensor contraction (GETT)
+# ------------------------------------------------------------------------------------------------
+def _julia_tensor(x):
+    """numpy array -> device tensor with column-major (Julia) strides."""
+    return GK.to_cuarray(np.asarray(x))
+
+
+def test_contraction_golden_extents8_gather_and_any_path(golden):
+    """C[a,b,c,d] = sum_{e,f} A[a,e,b,f] B[d,f,c,e] with extents 8 (the committed fixture): too small
+    for TMA boxes, so it exercises the gather kernel and its offset tables."""
+    cases, want = golden
+    A, B = cases["contraction_aebf_dfce"]["A"], cases["contraction_aebf_dfce"]["B"]
+    d = GK.cuarray(GK.Float32, 8, 8, 8, 8)
+    plan = GK.contract_query(d, "abcd", _julia_tensor(A), "aebf", _julia_tensor(B), "dfce")
+    assert plan.kernel == 5 and plan.workspace_bytes == 8 * (3 * 64 + 3 * 64 + 2 * 64)
+    GK.contract_(d, "abcd", _julia_tensor(A), "aebf", _julia_tensor(B), "dfce")
+    torch.cuda.synchronize(); GK.poll_status()
+    assert O.normwise_error(GK.to_numpy(d), want["contraction_aebf_dfce/D"]) <= TOL_TENSOR
+
+
+@pytest.mark.parametrize("force_gather", [False, True])
+def test_config4_contraction_extents32(force_gather):
+    """Configuration 4: extents 32 (M = N = K = 1024), A, B Float16 ~ U[-1,1), C Float32, modes
+    permuted as written; tensor-core path through 5-D tensor maps, and the gather path."""
+    A, B = O.inputs_contraction(4, 32)
+    a, b = _julia_tensor(A), _julia_tensor(B)
+    d = GK.cuarray(GK.Float32, 32, 32, 32, 32)
+    plan = GK.contract_query(d, "abcd", a, "aebf", b, "dfce", force_gather=force_gather)
+    assert plan.kernel == (5 if force_gather else 1)
+    GK.contract_(d, "abcd", a, "aebf", b, "dfce", force_gather=force_gather)
+    torch.cuda.synchronize(); GK.poll_status()
+    want = O.contract(A, "aebf", B, "dfce", "abcd")
+    assert O.normwise_error(GK.to_numpy(d), want) <= TOL_TENSOR
+
+
+def test_contraction_alpha_beta_and_three_index_case():
+    """D_abc = alpha * sum_d A_bda B_dc + beta * C_abc (the contraction of the reference's benchmark,
+    benchmarks/tensor-contractions/run.jl:10), scaled down."""
+    rng = np.random.default_rng(31)
+    ea, eb, ec, ed = 64, 32, 96, 128
+    A = (rng.random((eb, ed, ea)) * 2 - 1).astype(np.float16)
+    B = (rng.random((ed, ec)) * 2 - 1).astype(np.float16)
+    Cm = rng.random((ea, eb, ec)).astype(np.float32)
+    d = _julia_tensor(Cm)
+    GK.contract_(d, "abc", _julia_tensor(A), "bda", _julia_tensor(B), "dc", alpha=2.0, beta=0.5)
+    torch.cuda.synchronize(); GK.poll_status()
+    want = O.contract(A, "bda", B, "dc", "abc", 2.0, 0.5, Cm)
+    assert O.normwise_error(GK.to_numpy(d), want) <= TOL_TENSOR
+
+
+def test_contraction_errors():
+    a = GK.cuarray(GK.Float16, 8, 8); b = GK.cuarray(GK.Float16, 8, 4); d = GK.cuarray(GK.Float32, 8, 8)
+    with pytest.raises(GK.DimensionMismatch):
+        GK.contract_(d, "ij", a, "ik", b, "kj")              # j: 8 vs 4
+    with pytest.raises(Transform.UnsupportedFunctor):
+        GK.contract_(d, "ij", a, "ij", GK.cuarray(GK.Float16, 8, 8), "ij")   # batched modes
