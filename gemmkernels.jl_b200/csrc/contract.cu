@@ -9,6 +9,7 @@
 //   * on a gather kernel that reads through per-index offset tables built in the caller's workspace.
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <vector>
 
 #include "common.h"
@@ -360,6 +361,37 @@ static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const 
   return launch_gather(*desc, g, a, b, (desc->beta != 0.0) ? c : nullptr, dd, static_cast<int64_t*>(workspace), stream);
 }
 
+// ------------------------------------------------------------------------------------------------
+// gather path without any allocation: the offset tables live in this fixed device array
+// ------------------------------------------------------------------------------------------------
+// GK_STATIC_TABLE_ENTRIES 64-bit offsets (256 KiB).  Every GPU that loads the library holds this
+// array from load until the process exits.  All calls of gk_contract_static on a device share it.
+static __device__ __align__(256) long long g_static_tables[GK_STATIC_TABLE_ENTRIES];
+
+// In host code the name `g_static_tables` is only a stand-in for the symbol, not a device address:
+// the address each device uses is asked for once, with that device current, and cached here.
+static constexpr int kMaxDevices = 64;
+static std::mutex g_static_mu;
+static int64_t* g_static_ptr[kMaxDevices] = {};
+
+static gk_status static_tables_for_current_device(int64_t** out) {
+  int dev = -1;
+  GK_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return set_error(GK_ERR_CUDA, "device ordinal %d is outside the supported range 0..%d", dev, kMaxDevices - 1);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_tables);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error(GK_ERR_CUDA, "cudaGetSymbolAddress(g_static_tables) failed on device %d: %s", dev,
+                       cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<int64_t*>(ptr);
+  }
+  *out = g_static_ptr[dev];
+  return GK_OK;
+}
+
 }  // namespace gk
 
 using namespace gk;
@@ -377,6 +409,32 @@ gk_status gk_contract(gk_handle h, const gk_contract_desc* desc, const void* a, 
   clear_error();
   if (!a || !b || !d) return set_error(GK_ERR_INVALID_ARGUMENT, "A, B or D is NULL");
   return contract_impl(h, desc, a, b, c, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+gk_status gk_contract_static(const gk_contract_desc* desc, const void* a, const void* b, const void* c,
+                             void* d, gk_stream stream) {
+  clear_error();
+  if (!a || !b || !d) return set_error(GK_ERR_INVALID_ARGUMENT, "A, B or D is NULL");
+  if (!desc || desc->struct_size != sizeof(gk_contract_desc))
+    return set_error(GK_ERR_INVALID_ARGUMENT, "gk_contract_desc.struct_size does not match this library (%zu)",
+                     sizeof(gk_contract_desc));
+  if (desc->compute == GK_TF32)
+    return set_error(GK_ERR_INVALID_CONFIG, "gk_contract_static runs the gather kernel only; TF32 needs the tensor cores");
+  Groups g;
+  gk_status s = classify(*desc, &g);
+  if (s != GK_OK) return s;
+  const int64_t entries = 3 * g.M + 3 * g.N + 2 * g.K;
+  if (entries > GK_STATIC_TABLE_ENTRIES)
+    return set_error(GK_ERR_INVALID_CONFIG,
+                     "contraction too large for gk_contract_static: 3*M + 3*N + 2*K = %lld offset-table entries, "
+                     "the fixed table holds %d (M = %lld, N = %lld, K = %lld); use gk_contract with a workspace",
+                     (long long)entries, GK_STATIC_TABLE_ENTRIES, (long long)g.M, (long long)g.N, (long long)g.K);
+  int64_t* tables = nullptr;
+  s = static_tables_for_current_device(&tables);   // first call on a device: symbol address look-up
+  if (s != GK_OK) return s;
+  // The tables are rewritten in full for this contraction before the gather kernel reads them
+  // (same stream), so nothing has to start at zero.
+  return launch_gather(*desc, g, a, b, (desc->beta != 0.0) ? c : nullptr, d, tables, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -27,8 +27,10 @@ GK_RASTER_AUTO, GK_RASTER_IDENTITY, GK_RASTER_HORIZONTAL, GK_RASTER_VERTICAL, GK
 EXPORTS = (
     "gk_version", "gk_last_error_message", "gk_create", "gk_destroy", "gk_poll_status",
     "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks",
+    "gk_contract_static",
 )
 GK_MAX_MODES = 8
+GK_STATIC_TABLE_ENTRIES = 32768
 
 
 class GemmDesc(C.Structure):
@@ -124,6 +126,9 @@ def _load() -> C.CDLL:
     lib.gk_contract.restype = C.c_int
     lib.gk_contract.argtypes = [C.c_void_p, C.POINTER(ContractDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    lib.gk_contract_static.restype = C.c_int
+    lib.gk_contract_static.argtypes = [C.POINTER(ContractDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p]
     return lib
 
 

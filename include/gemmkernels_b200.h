@@ -208,6 +208,41 @@ GK_API gk_status gk_contract(gk_handle h, const gk_contract_desc* desc, const vo
                              const void* c, void* d, void* workspace, int64_t workspace_bytes,
                              gk_stream stream);
 
+/*
+ * gk_contract_static — the gather-path contraction for callers that must not allocate.
+ * (No counterpart in the reference.)
+ *
+ * Who this is for: code that runs where device memory cannot be asked for at all — a host
+ * application whose memory pool has already claimed the whole GPU (CUDA.jl's and PyTorch's caching
+ * allocators do this under pressure, so a plain cudaMalloc from a library fails), a plug-in
+ * callback whose contract forbids allocation, or a latency-bound loop that cannot afford the
+ * device-wide synchronisation an allocation may imply.  Such callers have no handle either
+ * (gk_create allocates), so this entry point takes none.
+ *
+ * What it does: the same arithmetic as gk_contract on its gather path (plan.kernel == 5): inputs
+ * and outputs are the caller's; the per-index offset tables, which gk_contract puts in the caller's
+ * workspace, go into a fixed array inside the library instead.  It calls no cudaMalloc, cudaFree or
+ * any other allocating routine.
+ *
+ * Limits and rules:
+ *  - The array holds GK_STATIC_TABLE_ENTRIES 64-bit offsets (256 KiB, held by every GPU that loads
+ *    the library until the process exits).  A contraction needs 3*M + 3*N + 2*K entries (M, N, K =
+ *    products of the free modes of A, of B, and of the contracted modes); anything larger is
+ *    rejected with GK_ERR_INVALID_CONFIG and a message giving the numbers.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ *    caches it; make that first call outside any stream capture.
+ *  - All calls on one device share the one array and it keeps the last call's tables.  Each call
+ *    rewrites every entry it reads before reading it, so stale contents are harmless, but two calls
+ *    whose kernels can overlap on the GPU (different streams, no dependency) race on the tables:
+ *    keep calls on one stream or order them with events.
+ *  - Same element types as the gather path: A/B Float16, BFloat16 or Float32 (one type), C/D
+ *    Float32 (or Float16 with Float16 inputs); FP32 accumulation; compute = GK_TF32 is rejected.
+ */
+#define GK_STATIC_TABLE_ENTRIES 32768
+
+GK_API gk_status gk_contract_static(const gk_contract_desc* desc, const void* a, const void* b,
+                                    const void* c, void* d, gk_stream stream);
+
 /* The same GEMM for callers whose matrices live in host memory (Julia `Array`s rather than
  * `CuArray`s; the reference has no such method — CUDA.jl users would `CuArray(A)` first, which is
  * what this call does internally): copies a, b (and c, and the bias named by epi) to device
