@@ -49,7 +49,13 @@ def measured_peaks():
     return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-def workload_config(n_gpus: int) -> dict:
+def workload_config(n_gpus: int, workload: str = "c0") -> dict:
+    if workload == "c5":
+        n = 16384
+        return {"workload": f"c5: C=A*B, A,B BFloat16 N(0,0.02) {n}x{n} col-major, C Float32; column blocks of B,C over "
+                            f"{n_gpus} rank(s) ({n // n_gpus} columns each), A broadcast once (NCCL), resident",
+                "m": n, "n_total": n, "k": n, "operator": "TCGen05Operator{BFloat16,Float32}",
+                "l2": "operands and output per GPU are larger than L2; no flush between steps"}
     return {"workload": f"c0: C=A*B, A,B Float16 U[0,1) {N_DIM}x{N_DIM} col-major, C Float32, alpha=1 beta=0"
                         + (f"; column blocks of B,C over {n_gpus} ranks, A broadcast once (NCCL), resident" if n_gpus > 1 else ""),
             "m": N_DIM, "n_per_gpu": N_DIM, "k": N_DIM, "operator": "TCGen05Operator{Float16,Float32}",
@@ -174,32 +180,50 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    n = N_DIM
+    from gemmkernels_b200 import multigpu
     # Inputs: A is generated on rank 0 and broadcast (the one exchange of the sharded path);
     # every rank draws its own column block of B.
-    A_host, _ = O.inputs_fp16_uniform01(0, n, 8, n)
-    B_host = np.random.default_rng(2000 + rank).random((n, n), dtype=np.float32).astype(np.float16)
-    a_pin = torch.from_numpy(np.ascontiguousarray(A_host.T)).pin_memory().T      # column-major, pinned
-    b_pin = torch.from_numpy(np.ascontiguousarray(B_host.T)).pin_memory().T
-    d_pin = torch.empty(n, n, dtype=torch.float32).pin_memory().T
-    a = GK.cuarray(GK.Float16, n, n)
-    b = GK.cuarray(GK.Float16, n, n); b.copy_(b_pin, non_blocking=True)
-    d = GK.cuarray(GK.Float32, n, n)
+    if args.workload == "c5":
+        # strong scaling: one 16384^3 BFloat16 product, columns of B and C split over the ranks
+        n = m_dim = k_dim = 16384
+        shard = multigpu.column_shard(n, world, rank, 256)
+        n_loc, ET, tdt = shard.count, GK.BFloat16, torch.bfloat16
+        A_host = O.inputs_bf16_normal(5, m_dim, 8, k_dim)[0]
+        B_host = O.bf16_round(np.random.default_rng(2005 + rank).standard_normal((k_dim, n_loc), dtype=np.float32) * np.float32(0.02))
+        flops_total = 2.0 * m_dim * n * k_dim
+        flops_rank = 2.0 * m_dim * n_loc * k_dim
+    else:
+        # weak scaling: every rank owns 8192 columns of an 8192 x (8192 * ranks) product
+        m_dim = k_dim = n_loc = N_DIM
+        ET, tdt = GK.Float16, torch.float16
+        A_host, _ = O.inputs_fp16_uniform01(0, m_dim, 8, k_dim)
+        B_host = np.random.default_rng(2000 + rank).random((k_dim, n_loc), dtype=np.float32).astype(np.float16)
+        flops_total = world * FLOPS_PER_GEMM
+        flops_rank = FLOPS_PER_GEMM
+    a_pin = torch.from_numpy(np.ascontiguousarray(A_host.T)).to(tdt).pin_memory().T      # column-major, pinned
+    b_pin = torch.from_numpy(np.ascontiguousarray(B_host.T)).to(tdt).pin_memory().T
+    d_pin = torch.empty(n_loc, m_dim, dtype=torch.float32).pin_memory().T
+    a = GK.cuarray(ET, m_dim, k_dim)
+    b = GK.cuarray(ET, k_dim, n_loc); b.copy_(b_pin, non_blocking=True)
+    d = GK.cuarray(GK.Float32, m_dim, n_loc)
     bcast_ms = None
     if rank == 0:
         a.copy_(a_pin, non_blocking=True)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+        warm = torch.zeros(1024, device="cuda")
+        dist.broadcast(warm, src=0)     # first collective pays NCCL's lazy set-up; keep it out of the timing
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        dist.broadcast(a.T, src=0)      # a.T is the contiguous view of the column-major storage
+        multigpu.broadcast_a(a.T, src=0)      # a.T is the contiguous view of the column-major storage
         e1.record(); torch.cuda.synchronize()
         bcast_ms = e0.elapsed_time(e1)
 
     # the call a user makes: GemmKernels.matmul with a Config (TCGen05Operator, aligned layouts)
-    conf = GK.get_config(gemm_shape=(n, n, n), operator=GK.Operator.TCGen05Operator[GK.Float16, GK.Float32],
-                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float16],
+    conf = GK.get_config(gemm_shape=(m_dim, n_loc, k_dim), operator=GK.Operator.TCGen05Operator[ET, GK.Float32],
+                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[ET],
                          global_c_layout=GK.Layout.Zero[GK.Float32],
                          global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
     plan = GK.query(conf, a, b, None, d)
@@ -234,10 +258,14 @@ def run_gpu(args):
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     GK.poll_status()
     ms_per_step = total_ms / args.steps
-    value = world * FLOPS_PER_GEMM / (ms_per_step * 1e-3) / 1e12
+    value = flops_total / (ms_per_step * 1e-3) / 1e12
 
     # correctness spot check of the timed result (one row against the oracle's product)
     row = np.asarray(A_host[7:8].astype(np.float32) @ B_host.astype(np.float32)) if rank == 0 else None
+    if args.workload == "c5":
+        METRIC_NAME = "GEMM TFLOP/s (BF16->FP32, 16384^3, column-sharded)"
+    else:
+        METRIC_NAME = METRIC
     if rank == 0:
         got = d[7:8].cpu().numpy()
         err = O.normwise_error(got, row)
@@ -259,7 +287,7 @@ def run_gpu(args):
         err = O.normwise_error(d_pin[7:8].numpy(), row)
         if not err <= 1e-3:
             raise SystemExit(f"end-to-end result is wrong: normwise error {err}")
-    e2e_value = world * FLOPS_PER_GEMM / (e2e_ms * 1e-3) / 1e12
+    e2e_value = flops_total / (e2e_ms * 1e-3) / 1e12
     h2d = a_pin.numel() * 2 + b_pin.numel() * 2
     d2h = d_pin.numel() * 4
 
@@ -269,17 +297,20 @@ def run_gpu(args):
         return 0
 
     peaks = measured_peaks()
-    achieved = FLOPS_PER_GEMM / (ms_per_step * 1e-3) / 1e12     # per launch, one GPU
+    achieved = flops_rank / (ms_per_step * 1e-3) / 1e12     # per launch, one GPU (rank 0's block)
     line = {
-        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+        "metric": METRIC_NAME, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "c5" else "weak",
+        "vs_baseline": None, "dtype": "bf16" if args.workload == "c5" else "f16", "data": "synthetic",
+        "config": workload_config(world, args.workload),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["tflops"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "frac": achieved / peaks["tflops"],
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if args.workload == "c0" else None,
                      "peak_source": f"{peaks['source']} cuBLAS bf16 burst; sustained {peaks['tflops_sustained']}",
                      "frac_of_nominal_dense_2250": achieved / 2250.0},
         "kernel": {"family": int(plan.kernel), "grid": int(plan.grid), "cluster": int(plan.cluster),
@@ -288,7 +319,7 @@ def run_gpu(args):
     }
     if bcast_ms is not None:
         line["a_broadcast_ms"] = bcast_ms
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.workload == "c0":
         cols = 2048
         dt, flops, threads = cpu_sgemm_sample(cols, 3, 1)
         line["cpu_baseline"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
@@ -307,6 +338,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="c0", choices=["c0", "c5"],
+                    help="c0: the headline 8192^3 FP16 GEMM per GPU (weak scaling); c5: one 16384^3 BF16 GEMM "
+                         "split by column blocks (strong scaling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

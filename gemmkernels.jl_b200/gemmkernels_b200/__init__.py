@@ -17,6 +17,7 @@ from . import cta_swizzle as CTASwizzle
 from . import epilogue as Epilogue
 from . import kernel as Kernel
 from . import layout as Layout
+from . import multigpu
 from . import operator as Operator
 from . import transform as Transform
 from .arrays import cuarray, to_cuarray, to_numpy
