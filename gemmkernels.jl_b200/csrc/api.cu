@@ -5,8 +5,10 @@
 #include <new>
 
 #include "common.h"
+#include "diag_gemm.cuh"
 #include "fpu_gemm.cuh"
 #include "simt_gemm.cuh"
+#include "split_planes.cuh"
 #include "tc_plan.h"
 
 namespace gk {
@@ -111,8 +113,92 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   return GK_OK;
 }
 
-// Which kernel family serves this descriptor: 1 tcgen05, 2 FP32 FFMA, 3 generic SIMT.
+// Interleaved complex / dual operands (plane_x == 0) are split into planes in the workspace first.
+// Layout of the workspace: A planes, then B planes; leading dimensions rounded up to 8 elements.
+struct SplitPlan {
+  bool a = false, b = false;
+  int64_t a_rows = 0, a_cols = 0, a_ld = 0, b_rows = 0, b_cols = 0, b_ld = 0;
+  int64_t a_bytes = 0, b_bytes = 0;
+};
+
+static SplitPlan plan_split(const gk_gemm_desc& d) {
+  SplitPlan sp;
+  if (d.number == GK_REAL || d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE) return sp;
+  auto up8 = [](int64_t x) { return (x + 7) / 8 * 8; };
+  const int64_t es = dtype_size(d.dtype_a);
+  if (d.plane_a == 0) {
+    sp.a = true; sp.a_rows = d.trans_a ? d.k : d.m; sp.a_cols = d.trans_a ? d.m : d.k; sp.a_ld = up8(sp.a_rows);
+    sp.a_bytes = (2 * sp.a_ld * sp.a_cols * es + 255) / 256 * 256;
+  }
+  if (d.plane_b == 0) {
+    sp.b = true; sp.b_rows = d.trans_b ? d.n : d.k; sp.b_cols = d.trans_b ? d.k : d.n; sp.b_ld = up8(sp.b_rows);
+    sp.b_bytes = (2 * sp.b_ld * sp.b_cols * dtype_size(d.dtype_b) + 255) / 256 * 256;
+  }
+  return sp;
+}
+
+static gk_status launch_split(int dtype, const void* in, void* out, int64_t rows, int64_t cols, int64_t ld_in,
+                              int64_t ld_out, int sm_count, cudaStream_t stream) {
+  const int64_t total = rows * cols;
+  if (total == 0) return GK_OK;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(sm_count) * 16)));
+  const int64_t plane = ld_out * cols;
+  if (dtype == GK_F16 || dtype == GK_BF16)
+    split_planes_kernel<ushort2, unsigned short><<<grid, 256, 0, stream>>>(
+        static_cast<const ushort2*>(in), static_cast<unsigned short*>(out), rows, cols, ld_in, ld_out, plane);
+  else if (dtype == GK_F32)
+    split_planes_kernel<float2, float><<<grid, 256, 0, stream>>>(
+        static_cast<const float2*>(in), static_cast<float*>(out), rows, cols, ld_in, ld_out, plane);
+  else
+    return set_error(GK_ERR_UNSUPPORTED, "interleaved operands must be Float16, BFloat16 or Float32 pairs");
+  GK_CUDA_CHECK(cudaGetLastError());
+  return GK_OK;
+}
+
+// Diagonal A: row scaling of B (HBM-bound).
+static gk_status launch_diag(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
+                             const void* b, const void* c, void* dd, cudaStream_t stream, gk_gemm_plan* plan_only) {
+  auto dt3 = [](int32_t t) { return t == GK_F16 ? 0 : t == GK_BF16 ? 1 : t == GK_F32 ? 2 : -1; };
+  if (d.m != d.k)
+    return set_error(GK_ERR_INVALID_CONFIG, "Diagonal only supports square A matrix (M == K), got M = %lld, K = %lld",
+                     (long long)d.m, (long long)d.k);
+  if (d.number != GK_REAL || d.op == GK_OP_FPU_TROPICAL)
+    return set_error(GK_ERR_INVALID_CONFIG, "Diagonal layout is for real products only");
+  if (d.dtype_a != d.dtype_b || dt3(d.dtype_a) < 0 || dt3(d.dtype_d) < 0 || dt3(d.dtype_c) < 0)
+    return set_error(GK_ERR_UNSUPPORTED, "Diagonal layout takes Float16/BFloat16/Float32 operands (A and B of one type)");
+  if (d.layout_b != GK_LAYOUT_DENSE)
+    return set_error(GK_ERR_INVALID_CONFIG, "Diagonal A needs a dense B");
+  DiagParams p{};
+  p.v = a; p.B = b; p.C = c; p.D = dd; p.M = d.m; p.N = d.n;
+  p.b_sm = d.trans_b ? d.ldb : 1; p.b_sn = d.trans_b ? 1 : d.ldb;   // op(B)(m, n): B is K x N, K == M
+  p.ldc = d.ldc; p.ldd = d.ldd;
+  p.dtype_ab = dt3(d.dtype_a); p.dtype_c = dt3(d.dtype_c); p.dtype_d = dt3(d.dtype_d);
+  p.alpha = static_cast<float>(d.alpha); p.beta = static_cast<float>(d.beta);
+  p.has_c = (d.layout_c == GK_LAYOUT_DENSE && c != nullptr && d.beta != 0.0) ? 1 : 0;
+  if (epi) { p.bias = epi->bias; p.bias_axis = epi->bias_axis; p.act = epi->activation; }
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool vec = !d.trans_b && (d.dtype_a == GK_F16 || d.dtype_a == GK_BF16) && d.dtype_d == GK_F32 &&
+                   (!p.has_c || d.dtype_c == GK_F32) && d.m % 8 == 0 && d.ldb % 8 == 0 && d.ldd % 4 == 0 &&
+                   (!p.has_c || d.ldc % 4 == 0) && (plan_only || (al16(a) && al16(b) && al16(dd) && (!p.has_c || al16(c))));
+  const int64_t work = vec ? (d.m / 8) * d.n : d.m * d.n;
+  const int64_t want = (work + 255) / 256;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(h->sm_count) * 16)));
+  if (plan_only) {
+    plan_only->kernel = 4; plan_only->grid = grid; plan_only->block = 256; plan_only->cluster = 1;
+    plan_only->tile_m = vec ? 8 : 1; plan_only->tile_n = 1; plan_only->tile_k = 1; plan_only->stages = 1;
+    return GK_OK;
+  }
+  if (d.m == 0 || d.n == 0) return GK_OK;
+  if (!vec) diag_gemm_scalar_kernel<<<grid, 256, 0, stream>>>(p);
+  else if (d.dtype_a == GK_F16) diag_gemm_vec_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  else diag_gemm_vec_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  GK_CUDA_CHECK(cudaGetLastError());
+  return GK_OK;
+}
+
+// Which kernel family serves this descriptor: 1 tcgen05, 2 FP32 FFMA, 3 generic SIMT, 4 diagonal.
 static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+  if (d.layout_a == GK_LAYOUT_DIAGONAL) return 4;
   // Nothing to multiply (Layout.Zero operands, alpha == 0, K == 0): D = act(beta * C + bias),
   // which the generic kernel does without touching A or B.
   const bool no_product = d.layout_a == GK_LAYOUT_ZERO || d.layout_b == GK_LAYOUT_ZERO ||
@@ -270,9 +356,15 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
   if (s != GK_OK) return s;
   std::memset(plan, 0, sizeof(*plan));
   std::string why;
+  gk_gemm_desc planar = *desc;          // what the kernel sees once interleaved operands are split
+  const SplitPlan sp = plan_split(*desc);
+  if (sp.a) { planar.lda = sp.a_ld; planar.plane_a = sp.a_ld * sp.a_cols; }
+  if (sp.b) { planar.ldb = sp.b_ld; planar.plane_b = sp.b_ld * sp.b_cols; }
+  desc = &planar;
   const int fam = choose_family(*desc, nullptr, nullptr, &why);
   if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
   plan->kernel = fam;
+  if (fam == 4) return launch_diag(h, *desc, epi, nullptr, nullptr, nullptr, nullptr, nullptr, plan);
   if (fam == 1) {
     TcLaunch L;
     TcProblem pr;
@@ -283,6 +375,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
+    plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
   } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {
     plan->kernel = 2;
     plan->grid = static_cast<int32_t>((desc->m / kFpuBM) * (desc->n / kFpuBN));
@@ -307,8 +400,29 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
   if (!d && desc->m > 0 && desc->n > 0) return set_error(GK_ERR_INVALID_ARGUMENT, "D is NULL");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   std::string why;
+  gk_gemm_desc planar = *desc;
+  const SplitPlan sp = plan_split(*desc);
+  if (sp.a || sp.b) {
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255))
+      return set_error(GK_ERR_INVALID_ARGUMENT,
+                       "interleaved complex/dual operands are split into planes first: pass a 256-byte aligned "
+                       "workspace of %lld bytes (gk_gemm_query reports it)", (long long)(sp.a_bytes + sp.b_bytes));
+    char* ws = static_cast<char*>(workspace);
+    if (sp.a) {
+      s = launch_split(desc->dtype_a, a, ws, sp.a_rows, sp.a_cols, desc->lda, sp.a_ld, h->sm_count, st);
+      if (s != GK_OK) return s;
+      a = ws; planar.lda = sp.a_ld; planar.plane_a = sp.a_ld * sp.a_cols;
+    }
+    if (sp.b) {
+      s = launch_split(desc->dtype_b, b, ws + sp.a_bytes, sp.b_rows, sp.b_cols, desc->ldb, sp.b_ld, h->sm_count, st);
+      if (s != GK_OK) return s;
+      b = ws + sp.a_bytes; planar.ldb = sp.b_ld; planar.plane_b = sp.b_ld * sp.b_cols;
+    }
+    desc = &planar;
+  }
   int fam = choose_family(*desc, a, b, &why);
   if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
+  if (fam == 4) return launch_diag(h, *desc, epi, a, b, c, d, st, nullptr);
   if (desc->m == 0 || desc->n == 0) return GK_OK;
   if (fam == 1 && (desc->k == 0 || desc->alpha == 0.0)) fam = 3;  // nothing to multiply
   if (fam == 1) {

@@ -186,6 +186,10 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
         if et != want:
             raise ConfigError(f"{name} holds {et} but its layout is {layout!r}")
         if layout.diagonal:
+            # the diagonal is the first M elements of the array's memory (the reference's harness
+            # allocates a full M x K matrix and uses its first column, configs/configs.jl:338-340)
+            if arr.numel() < rows or (arr.dim() >= 1 and arr.stride(0) != 1 and arr.shape[0] > 1):
+                raise DimensionMismatch(f"{name}: Diagonal layout needs at least {rows} contiguous elements")
             return arr.data_ptr(), et.gk, max(rows, 1), 0, L.GK_LAYOUT_DIAGONAL
         if number != L.GK_REAL:
             if layout.split:
@@ -251,8 +255,16 @@ def matmul(conf: Config, a, b, c, d, *,
     desc, epi, (pa, pb, pc, pd) = lower(conf, a, b, c, d, hooks, epilogue or Epilogue.Default(), kernel)
     dev = d.device.index if d.device.index is not None else torch.cuda.current_device()
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
-    ws = workspace.data_ptr() if workspace is not None else None
     with torch.cuda.device(dev):
+        if workspace is None and desc.number != L.GK_REAL and (desc.plane_a == 0 or desc.plane_b == 0):
+            # interleaved complex / dual operands: the library splits them into planes in a workspace
+            plan = L.GemmPlan()
+            st = L.lib.gk_gemm_query(handle(dev), C.byref(desc), C.byref(epi), C.byref(plan))
+            if st != L.GK_OK:
+                _raise(st)
+            if plan.workspace_bytes:
+                workspace = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=d.device)
+        ws = workspace.data_ptr() if workspace is not None else None
         st = L.lib.gk_gemm(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), ws, C.c_void_p(s))
     if st != L.GK_OK:
         _raise(st)

@@ -426,3 +426,89 @@ def test_contraction_errors():
         GK.contract_(d, "ij", a, "ik", b, "kj")              # j: 8 vs 4
     with pytest.raises(Transform.UnsupportedFunctor):
         GK.contract_(d, "ij", a, "ij", GK.cuarray(GK.Float16, 8, 8), "ij")   # batched modes
+
+
+# ------------------------------------------------------------------------------------------------
+# Diagonal A (Layout.Diagonal): D = diag(v) * B + C
+# ------------------------------------------------------------------------------------------------
+def test_golden_diagonal(golden):
+    cases, want = golden
+    cs = cases["diagonal"]
+    v, B, Cm = cs["A"], cs["B"], cs["C"]
+    M, N = B.shape
+    # as in the reference's harness: a full M x K matrix whose first column holds the diagonal
+    Afull = np.zeros((M, M), dtype=np.float16); Afull[:, 0] = v
+    c = dev(Cm); d = GK.cuarray(GK.Float32, M, N)
+    conf = run_matmul(dev(Afull), dev(B), c, d, M=M, N=N, K=M, op=Operator.WMMAOp[16, 16, 16, GK.Float16, GK.Float32],
+                      la=Layout.Diagonal[GK.Float16], lb=Layout.ColMajor[GK.Float16], lc=Layout.ColMajor[GK.Float32],
+                      ld=Layout.ColMajor[GK.Float32], block_shape=(64, 64, 32),
+                      shared_a_layout=Layout.Padded[Layout.UnsafeAlignedColMajor[GK.Float16], 8])
+    assert GK.query(conf, dev(Afull), dev(B), c, d).kernel == 4
+    assert O.normwise_error(GK.to_numpy(d), want["diagonal/D"]) <= 1e-6
+
+
+@pytest.mark.parametrize("tb", [False, True])
+def test_diagonal_4096_matches_oracle_and_dense_product(tb):
+    """4096^2 (the size of the reference's diagonal benchmark): against the oracle, and against the
+    dense tensor-core product with the same diagonal matrix written out in full."""
+    n = 4096
+    rng = np.random.default_rng(51 + tb)
+    v = rng.random(n).astype(np.float16)
+    B = rng.random((n, n)).astype(np.float16)
+    Cm = rng.random((n, n)).astype(np.float32)
+    b = dev(B.T.copy() if tb else B)
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float16]
+    c = dev(Cm); d = GK.cuarray(GK.Float32, n, n)
+    run_matmul(dev(v), b, c, d, M=n, N=n, K=n, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+               la=Layout.Diagonal[GK.Float16], lb=lb, lc=Layout.UnsafeAlignedColMajor[GK.Float32],
+               ld=Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64),
+               shared_a_layout=Layout.Padded[Layout.UnsafeAlignedColMajor[GK.Float16], 8])
+    got = GK.to_numpy(d)
+    assert O.normwise_error(got, O.diagonal_gemm(v, B, Cm)) <= 1e-6
+    dense = GK.cuarray(GK.Float32, n, n); dense.copy_(c)
+    GK.matmatmul_(dense, "N", "T" if tb else "N", dev(np.diag(v)), b, 1.0, 1.0)
+    torch.cuda.synchronize()
+    assert O.normwise_error(got, GK.to_numpy(dense)) <= 1e-6
+
+
+# ------------------------------------------------------------------------------------------------
+# replay of the reference's complex / dual configurations (configs/configs.jl:385-486, 656-695):
+# interleaved Complex{Float16} global arrays, D = A*B + C
+# ------------------------------------------------------------------------------------------------
+def _interleaved(z_re, z_im, eltype):
+    """two numpy planes (r, c) -> device array of (re, im) pairs, shape (2, r, c), strides (1, 2, 2r)"""
+    return GK.to_cuarray(np.stack([z_re, z_im], axis=0), eltype)
+
+
+@pytest.mark.parametrize("n", [128, 256, 2048])
+@pytest.mark.parametrize("ta,tb,number", [(0, 0, "complex"), (0, 1, "complex"), (1, 0, "complex"), (1, 1, "complex"),
+                                          (0, 0, "dual")])
+def test_reference_complex_dual_configs_interleaved(n, ta, tb, number):
+    rng = np.random.default_rng(n + 10 * ta + 100 * tb + (7 if number == "dual" else 0))
+    A = rng.random((2, n, n)).astype(np.float16); B = rng.random((2, n, n)).astype(np.float16)
+    Cm = rng.random((2, n, n)).astype(np.float32)
+    a = _interleaved(A[0], A[1], GK.Float16); b = _interleaved(B[0], B[1], GK.Float16)
+    c = _interleaved(Cm[0], Cm[1], GK.Float32); d = GK.cuarray(GK.ComplexF32, n, n)
+    opcls = Operator.WMMAComplexOp if number == "complex" else Operator.WMMADualOp
+    la = (Layout.InterleavedRowMajor if ta else Layout.InterleavedColMajor)[GK.Float16]
+    lb = (Layout.InterleavedRowMajor if tb else Layout.InterleavedColMajor)[GK.Float16]
+    conf = GK.get_config(
+        gemm_shape=(n, n, n), operator=opcls[16, 16, 16, GK.Float16, GK.Float32],
+        global_a_layout=la, global_b_layout=lb,
+        global_c_layout=Layout.InterleavedColMajor[GK.Float32], global_d_layout=Layout.InterleavedColMajor[GK.Float32],
+        shared_a_layout=Layout.Padded[(Layout.SplitRowMajor if ta else Layout.SplitColMajor)[GK.Float16], 8],
+        shared_b_layout=Layout.Padded[(Layout.SplitRowMajor if tb else Layout.SplitColMajor)[GK.Float16], 8],
+        shared_c_layout=Layout.SplitColMajor[GK.Float32], shared_d_layout=Layout.SplitColMajor[GK.Float32],
+        warps_per_block=8, compute_warp=(16, 32, 16), block_shape=(64, 64, 32),
+        mem_a_warp=(4, 32) if ta else (64, 2), mem_b_warp=(2, 64) if tb else (32, 4), mem_cd_warp=(64, 1),
+        mem_a_thread=(1, 4) if ta else (4, 1), mem_b_thread=(1, 4) if tb else (4, 1), mem_cd_thread=(2, 1),
+        is_a_col_major=not ta, is_b_col_major=not tb)
+    plan = GK.query(conf, a, b, c, d)
+    assert plan.kernel == 1 and plan.workspace_bytes == 2 * (2 * n * n * 2)
+    GK.matmul(conf, a, b, c, d, kernel=Kernel.matmul_pipelined)
+    torch.cuda.synchronize(); GK.poll_status()
+    f = O.complex_gemm if number == "complex" else O.dual_gemm
+    re, im = f(A[0], A[1], B[0], B[1], Cm[0], Cm[1], 1.0, 1.0, bool(ta), bool(tb))
+    got = GK.to_numpy(d)                      # (2, n, n)
+    assert O.normwise_error(got[0], re) <= TOL_TENSOR and O.normwise_error(got[1], im) <= TOL_TENSOR
+    assert O.isapprox_elementwise(re, got[0], "Float16") or number == "complex"   # sums of positives only for dual/re
