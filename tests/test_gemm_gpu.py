@@ -512,3 +512,99 @@ def test_reference_complex_dual_configs_interleaved(n, ta, tb, number):
     got = GK.to_numpy(d)                      # (2, n, n)
     assert O.normwise_error(got[0], re) <= TOL_TENSOR and O.normwise_error(got[1], im) <= TOL_TENSOR
     assert O.isapprox_elementwise(re, got[0], "Float16") or number == "complex"   # sums of positives only for dual/re
+
+
+# ------------------------------------------------------------------------------------------------
+# replay of the reference's configuration zoo (configs/configs.jl:492-653), one case per family,
+# transpose pair and size class; alpha = 2, beta = 3 as there; elementwise sqrt(eps) rule
+# ------------------------------------------------------------------------------------------------
+FPU_TYPES = [("Float16", "Float32"), ("Float32", "Float32"), ("Float32", "Float64"), ("Float64", "Float64"),
+             ("Int16", "Int16"), ("Int32", "Int32"), ("Int64", "Int64")]
+
+
+@pytest.mark.parametrize("ab,cd", FPU_TYPES)
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("n", [128, 256])
+def test_zoo_fpu_types(ab, cd, ta, tb, n):
+    AB, CD = getattr(GK, ab), getattr(GK, cd)
+    rng = np.random.default_rng(n + ta + 2 * tb)
+    if AB.is_integer:
+        info = np.iinfo(AB.np_dtype)
+        A = rng.integers(info.min, info.max, (n, n), dtype=AB.np_dtype)
+        B = rng.integers(info.min, info.max, (n, n), dtype=AB.np_dtype)
+        Cm = rng.integers(info.min, info.max, (n, n), dtype=CD.np_dtype)
+    else:
+        A = rng.random((n, n)).astype(AB.np_dtype); B = rng.random((n, n)).astype(AB.np_dtype)
+        Cm = rng.random((n, n)).astype(CD.np_dtype)
+    c = dev(Cm); d = GK.cuarray(CD, n, n)
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[AB]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[AB]
+    run_matmul(dev(A), dev(B), c, d, M=n, N=n, K=n, op=Operator.FPUOp[8, 16, 2, 4, 8, 1, AB, CD], la=la, lb=lb,
+               lc=Layout.UnsafeAlignedColMajor[CD], ld=Layout.UnsafeAlignedColMajor[CD], alpha=2, beta=3,
+               block_shape=(64, 64, 32))
+    got = GK.to_numpy(d)
+    if AB.is_integer:
+        assert np.array_equal(got, O.integer_gemm(A, B, Cm, 2, 3, bool(ta), bool(tb)))
+    else:
+        want = O.gemm64(A, B, Cm, 2.0, 3.0, bool(ta), bool(tb))
+        assert O.isapprox_elementwise(want, got, ab)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("mnk", [(128, 128, 128), (256, 256, 128), (128, 128, 256), (256, 256, 256)])
+def test_zoo_tropical(ta, tb, mnk):
+    M, N, K = mnk
+    rng = np.random.default_rng(M + N + K + ta + 2 * tb)
+    A = rng.random((K, M) if ta else (M, K)).astype(np.float32); B = rng.random((N, K) if tb else (K, N)).astype(np.float32)
+    Cm = rng.random((M, N)).astype(np.float32)
+    c = dev(Cm); d = GK.cuarray(GK.Float32, M, N)
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float32]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float32]
+    run_matmul(dev(A), dev(B), c, d, M=M, N=N, K=K, op=Operator.TropicalFPUOp[8, 16, 2, 4, 8, 1, GK.Float32, GK.Float32],
+               la=la, lb=lb, lc=Layout.UnsafeAlignedColMajor[GK.Float32], ld=Layout.UnsafeAlignedColMajor[GK.Float32],
+               block_shape=(64, 64, 32))
+    assert np.array_equal(GK.to_numpy(d), O.tropical_gemm(A, B, Cm, bool(ta), bool(tb)))
+
+
+@pytest.mark.parametrize("cd,min_dim", [("Float16", 256), ("Float32", 128)])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("op_shape", [(16, 16, 16), (8, 32, 16), (32, 8, 16)])
+@pytest.mark.parametrize("zero_c", [False, True])
+def test_zoo_wmma(cd, min_dim, ta, tb, op_shape, zero_c):
+    """WMMA configurations (configs.jl:573-612): sizes {1,2} x min_dimension mixes and 2048^3,
+    alpha = 2, beta = 3 (0 when C is Layout.Zero).  The WMMA operator shapes are accepted and run on
+    the tcgen05 kernel."""
+    CD = getattr(GK, cd)
+    for (M, N, K) in [(min_dim, min_dim, min_dim), (2 * min_dim, 2 * min_dim, min_dim), (min_dim, min_dim, 2 * min_dim),
+                      (2048, 2048, 2048)]:
+        rng = np.random.default_rng(M + N + K)
+        A = rng.random((K, M) if ta else (M, K)).astype(np.float16); B = rng.random((N, K) if tb else (K, N)).astype(np.float16)
+        Cm = rng.random((M, N)).astype(CD.np_dtype)
+        c = dev(Cm); d = GK.cuarray(CD, M, N)
+        la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float16]
+        lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float16]
+        beta = 0.0 if zero_c else 3.0
+        run_matmul(dev(A), dev(B), None if zero_c else c, d, M=M, N=N, K=K,
+                   op=Operator.WMMAOp[(*op_shape, GK.Float16, CD)], la=la, lb=lb,
+                   lc=(Layout.Zero if zero_c else Layout.UnsafeAlignedColMajor)[CD], ld=Layout.UnsafeAlignedColMajor[CD],
+                   alpha=2.0, beta=3.0, block_shape=(128, 128, 64), warps_per_block=8,
+                   compute_warp=(32, 64, 16), kernel=Kernel.matmul_pipelined)
+        want = O.gemm(A, B, Cm, 2.0, beta, bool(ta), bool(tb))
+        assert O.isapprox_elementwise(want, GK.to_numpy(d), "Float16"), (M, N, K)
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("n", [128, 256, 4096])
+def test_zoo_bias(ta, tb, n):
+    """Bias configurations (configs.jl:615-633): per-column Float32 bias, alpha = beta = 1."""
+    rng = np.random.default_rng(n + ta + 2 * tb)
+    A = rng.random((n, n)).astype(np.float16); B = rng.random((n, n)).astype(np.float16)
+    Cm = rng.random((n, n)).astype(np.float32); bias = rng.random((1, n)).astype(np.float32)
+    c = dev(Cm); d = GK.cuarray(GK.Float32, n, n)
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float16]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float16]
+    run_matmul(dev(A), dev(B), c, d, M=n, N=n, K=n, op=Operator.WMMAOp[16, 16, 16, GK.Float16, GK.Float32], la=la, lb=lb,
+               lc=Layout.UnsafeAlignedColMajor[GK.Float32], ld=Layout.UnsafeAlignedColMajor[GK.Float32],
+               epilogue=Epilogue.Bias(dev(bias.reshape(-1))), block_shape=(128, 128, 64), kernel=Kernel.matmul_pipelined)
+    want = O.gemm(A, B, Cm, 1.0, 1.0, bool(ta), bool(tb)) + bias
+    assert O.isapprox_elementwise(want, GK.to_numpy(d), "Float16")
