@@ -93,11 +93,14 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
   const int tx = threadIdx.x & 15;  // strip along M
   const int ty = threadIdx.x >> 4;  // strip along N
 
-  float acc[8][8];
+  // Accumulators are kept as pairs of consecutive rows: Blackwell's packed FP32 FMA (fma.rn.f32x2)
+  // does two IEEE fused multiply-adds per issued instruction, which halves the issue slots the
+  // 64 FMAs per k-step need and leaves room for the shared-memory loads.
+  float2 acc[4][8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    for (int j = 0; j < 8; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
 
   float4 ra[2], rb[2];
   const int kt_count = p.K / kFpuBK;
@@ -121,12 +124,15 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
       const float4 a1 = *reinterpret_cast<const float4*>(&As[cur][k][64 + tx * 4]);
       const float4 b0 = *reinterpret_cast<const float4*>(&Bs[cur][k][ty * 4]);
       const float4 b1 = *reinterpret_cast<const float4*>(&Bs[cur][k][64 + ty * 4]);
-      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float2 a[4] = {make_float2(a0.x, a0.y), make_float2(a0.z, a0.w), make_float2(a1.x, a1.y),
+                           make_float2(a1.z, a1.w)};
       const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int j = 0; j < 8; ++j) {
+        const float2 bb = make_float2(b[j], b[j]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int i = 0; i < 4; ++i) acc[i][j] = __ffma2_rn(a[i], bb, acc[i][j]);
+      }
     }
     if (more) {
       fpu_store_tile<A_KMAJOR>(As[cur ^ 1], ra, p.alpha);
@@ -146,7 +152,7 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
 #pragma unroll
       for (int ih = 0; ih < 2; ++ih) {
         const int m = m0 + ih * 64 + tx * 4;
-        float4 v = make_float4(acc[ih * 4 + 0][j], acc[ih * 4 + 1][j], acc[ih * 4 + 2][j], acc[ih * 4 + 3][j]);
+        float4 v = make_float4(acc[ih * 2][j].x, acc[ih * 2][j].y, acc[ih * 2 + 1][j].x, acc[ih * 2 + 1][j].y);
         if (p.beta != 0.0f) {
           const float4 c = *reinterpret_cast<const float4*>(p.C + m + static_cast<int64_t>(n) * p.ldc);
           v.x = fmaf(p.beta, c.x, v.x); v.y = fmaf(p.beta, c.y, v.y);
