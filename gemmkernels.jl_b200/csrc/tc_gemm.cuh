@@ -407,6 +407,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         long long* o = p.dbg_out + blockIdx.x * 16;
         o[2] = mw; o[3] = mi; o[4] = mt; o[5] = clock64() - k_start;
         o[6] = static_cast<long long>(global_timer_ns() - g_start);
+        o[11] = static_cast<long long>(g_start);          // absolute times: the launch's timeline
+        o[12] = static_cast<long long>(global_timer_ns());
       }
       // Drain: nothing below may free TMEM or shared memory while an MMA is still running.
       // The commit must come from the thread that issued the MMAs.
