@@ -331,6 +331,129 @@ def run_gpu(args):
     return 0
 
 
+# ------------------------------------------------------------------------------------------------
+# the other configurations, kernel-only (one GPU): parity cases first, timed here for the record
+# ------------------------------------------------------------------------------------------------
+def run_side(args):
+    """c1 2048^3 FP16; c2 4096^3 FP32 FFMA, A transposed, bias(M)+ReLU; c3 4096^3 planar complex FP16;
+    c4 the contraction C[a,b,c,d] = sum A[a,e,b,f] B[d,f,c,e], extents 32; diag 4096^2 diagonal A.
+    Inputs are drawn on the device (torch RNG) and stay resident; no end-to-end leg, no CPU leg.
+    A sample of the timed result is checked against a torch FP32 product of the same operands."""
+    import torch
+
+    import gemmkernels_b200 as GK
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    Lay, Op = GK.Layout, GK.Operator
+
+    def rnd(et, *shape, lo=0.0, hi=1.0):
+        t = GK.cuarray(et, *shape)
+        t.copy_((torch.rand(tuple(reversed(shape)), device="cuda", generator=g) * (hi - lo) + lo).permute(*reversed(range(len(shape)))))
+        return t
+
+    w = args.workload
+    bound, unit = "tensor", "TFLOP/s"
+    if w == "c1":
+        n = 2048
+        a, b, d = rnd(GK.Float16, n, n), rnd(GK.Float16, n, n), GK.cuarray(GK.Float32, n, n)
+        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.TCGen05Operator[GK.Float16, GK.Float32],
+                             global_a_layout=Lay.UnsafeAlignedColMajor[GK.Float16], global_c_layout=Lay.Zero[GK.Float32],
+                             global_d_layout=Lay.UnsafeAlignedColMajor[GK.Float32])
+        step = lambda: GK.matmul(conf, a, b, None, d)
+        check = lambda: (d[5:9], a[5:9].float() @ b.float())
+        flops, name = 2.0 * n ** 3, "c1: 2048^3 Float16 -> Float32, col-major, tcgen05"
+        plan = GK.query(conf, a, b, None, d)
+    elif w == "c2":
+        n = 4096
+        a, b, d = rnd(GK.Float32, n, n, lo=-1), rnd(GK.Float32, n, n, lo=-1), GK.cuarray(GK.Float32, n, n)
+        bias = torch.rand(n, device="cuda", generator=g) - 0.5
+        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.FPUOp[8, 8, 1, 4, 8, 1, GK.Float32, GK.Float32],
+                             global_a_layout=Lay.UnsafeAlignedRowMajor[GK.Float32],
+                             global_b_layout=Lay.UnsafeAlignedColMajor[GK.Float32], global_c_layout=Lay.Zero[GK.Float32],
+                             global_d_layout=Lay.UnsafeAlignedColMajor[GK.Float32])
+        epi = GK.Epilogue.Bias(bias, axis="row")
+        step = lambda: GK.matmul(conf, a, b, None, d, epilogue=epi, transform_shared_to_global_d=GK.Transform.ReLU())
+        check = lambda: (d[5:9], torch.relu(a[:, 5:9].t().double() @ b.double() + bias[5:9, None].double()).float())
+        flops, name, bound = 2.0 * n ** 3, "c2: 4096^3 Float32 FFMA, A transposed, bias(M)+ReLU fused", "fp32-fma"
+        plan = GK.query(conf, a, b, None, d, epilogue=epi, transform_shared_to_global_d=GK.Transform.ReLU())
+    elif w == "c3":
+        n = 4096
+        a, b = rnd(GK.Float16, n, n, 2, lo=-1), rnd(GK.Float16, n, n, 2, lo=-1)
+        d = GK.cuarray(GK.Float32, n, n, 2)
+        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.WMMAComplexOp[16, 16, 16, GK.Float16, GK.Float32],
+                             global_a_layout=Lay.SplitColMajor[GK.Float16], global_c_layout=Lay.Zero[GK.Float32],
+                             global_d_layout=Lay.SplitColMajor[GK.Float32], block_shape=(64, 64, 32))
+        step = lambda: GK.matmul(conf, a, b, None, d)
+        def check():
+            ar, ai, br, bi = a[5:9, :, 0].float(), a[5:9, :, 1].float(), b[..., 0].float(), b[..., 1].float()
+            return d[5:9], torch.stack([ar @ br - ai @ bi, ar @ bi + ai @ br], dim=-1)
+        flops, name = 8.0 * n ** 3, "c3: 4096^3 planar Complex{Float16} -> Complex{Float32} (8 N^3 real flops), tcgen05"
+        plan = GK.query(conf, a, b, None, d)
+    elif w == "c4":
+        e = 32
+        a, b = rnd(GK.Float16, e, e, e, e, lo=-1), rnd(GK.Float16, e, e, e, e, lo=-1)
+        d = GK.cuarray(GK.Float32, e, e, e, e)
+        step = lambda: GK.contract_(d, "abcd", a, "aebf", b, "dfce")
+        check = lambda: (d[3], torch.einsum("ebf,dfce->bcd", a[3].float(), b.float()))
+        flops, name = 2.0 * e ** 6, "c4: C[a,b,c,d] = sum_ef A[a,e,b,f] B[d,f,c,e], extents 32 (M=N=K=1024), tcgen05 via 5-D TMA"
+        plan = GK.contract_query(d, "abcd", a, "aebf", b, "dfce")
+    else:
+        n = 4096
+        v, b, c, d = rnd(GK.Float16, n), rnd(GK.Float16, n, n), rnd(GK.Float32, n, n), GK.cuarray(GK.Float32, n, n)
+        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.TCGen05Operator[GK.Float16, GK.Float32],
+                             global_a_layout=Lay.Diagonal[GK.Float16], global_b_layout=Lay.UnsafeAlignedColMajor[GK.Float16],
+                             global_c_layout=Lay.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64),
+                             shared_a_layout=Lay.Padded[Lay.UnsafeAlignedColMajor[GK.Float16], 8])
+        step = lambda: GK.matmul(conf, v, b, c, d)
+        check = lambda: (d[5:9], v[5:9, None].float() * b[5:9].float() + c[5:9])
+        # streams B (2 B), C (4 B) in and D (4 B) out per element
+        flops, name, bound, unit = 10.0 * n * n, "diag: D = diag(v) B + C, 4096^2, Float16 B, Float32 C/D (10 B per element)", "hbm", "GB/s"
+        plan = GK.query(conf, v, b, c, d)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    GK.poll_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    got, want = check()
+    err = (torch.linalg.norm(got.double() - want.double()) / torch.linalg.norm(want.double())).item()
+    if not err <= 1e-3:
+        raise SystemExit(f"bench result is wrong: normwise error {err}")
+    peaks = measured_peaks()
+    scale = 1e9 if bound == "hbm" else 1e12
+    achieved = flops / (ms * 1e-3) / scale
+    if bound == "tensor":
+        peak, src = peaks["tflops"], f"{peaks['source']} cuBLAS bf16 burst"
+    elif bound == "hbm":
+        peak, src = peaks["hbm_gbs"], f"{peaks['source']} copy bandwidth"
+    else:
+        sm = torch.cuda.get_device_properties(0).multi_processor_count
+        mhz = clocks.get("sm_max_mhz") or 1965
+        peak, src = sm * 128 * 2 * mhz * 1e6 / 1e12, f"nominal: {sm} SMs x 128 FMA lanes x 2 x {mhz} MHz"
+    print(json.dumps({
+        "metric": f"{unit} ({name})", "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {"c2": "f32", "diag": "f32"}.get(w, "f16"), "data": "synthetic",
+        "config": {"workload": name, "l2": "back-to-back launches on resident operands; kernel-only, no end-to-end leg"},
+        "clocks": clocks, "gpu_launches": args.steps, "sample_normwise_error": err,
+        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                     "traffic": None, "peak_source": src},
+        "kernel": {"family": int(plan.kernel), "grid": int(plan.grid), "cluster": int(plan.cluster),
+                   "tile": [int(plan.tile_m), int(plan.tile_n), int(plan.tile_k)], "stages": int(plan.stages),
+                   "smem_bytes": int(plan.smem_bytes), "tmem_columns": int(plan.tmem_columns)},
+    }), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -338,12 +461,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="c0", choices=["c0", "c5"],
+    ap.add_argument("--workload", default="c0", choices=["c0", "c5", "c1", "c2", "c3", "c4", "diag"],
                     help="c0: the headline 8192^3 FP16 GEMM per GPU (weak scaling); c5: one 16384^3 BF16 GEMM "
-                         "split by column blocks (strong scaling)")
+                         "split by column blocks (strong scaling); c1-c4, diag: the other configurations, "
+                         "kernel-only on one GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload in ("c1", "c2", "c3", "c4", "diag"):
+        return run_side(args)
     return run_gpu(args)
 
 

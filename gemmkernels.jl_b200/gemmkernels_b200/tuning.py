@@ -1,0 +1,300 @@
+"""Autotuner for the tcgen05 GEMM on B200: sweeps tile width, CTA pairing, pipeline depth and raster
+band per problem, through the C ABI, timing with CUDA events.
+
+Mirrors what tuning/tune.jl of the reference does where it still applies:
+  * a parameter sweep per (shape, transposes) — there: block/warp/operator shapes (tuning/wmma.jl:34-47);
+    here: tile_n, cta_group, stages, raster_group;
+  * "measure until no improvement" timing (tuning/tune.jl:143-163);
+  * each candidate's result is verified (tune.jl:172-176) — here against the output of the built-in
+    configuration, which the parity tests pin;
+  * an error taxonomy per candidate (tune.jl:90-179): config_error / cuda_error / invalid_result / timeout;
+  * checkpoint and resume (tune.jl:315-357): one JSON line per measured candidate, measured keys are
+    skipped on restart, unreadable lines are ignored;
+  * waiting out thermal throttling before a measurement (tune.jl:223-247), with read-only NVML.
+Locking GPU clocks (tuning/setup.sh:29-43) changes a setting that outlasts the process; `lock_clocks`
+exists for machines where the operator wants it, is never called by the tuner itself, and is off by
+default.
+"""
+from __future__ import annotations
+
+import itertools
+import json
+import os
+import time
+from dataclasses import asdict, dataclass
+from pathlib import Path
+from typing import Callable, Iterable, Iterator
+
+TILE_N = (64, 128, 192, 256)
+CTA_GROUP = (1, 2)
+STAGES = (0, 3, 4, 6)          # 0 = as many as shared memory holds
+RASTER_GROUP = (0, 4, 8, 16)   # 0 = built-in choice
+
+
+@dataclass(frozen=True)
+class Problem:
+    m: int
+    n: int
+    k: int
+    trans_a: bool = False
+    trans_b: bool = False
+    dtype: str = "Float16"      # Float16 | BFloat16 | TF32
+
+    def key(self) -> str:
+        return f"{self.dtype}:{self.m}x{self.n}x{self.k}:{'T' if self.trans_a else 'N'}{'T' if self.trans_b else 'N'}"
+
+
+@dataclass(frozen=True)
+class Candidate:
+    tile_n: int
+    cta_group: int
+    stages: int
+    raster_group: int
+
+    def key(self) -> str:
+        return f"tn{self.tile_n}-cg{self.cta_group}-st{self.stages}-rg{self.raster_group}"
+
+
+def candidates(problem: Problem, tile_n=TILE_N, cta_group=CTA_GROUP, stages=STAGES,
+               raster_group=RASTER_GROUP) -> Iterator[Candidate]:
+    """The sweep for one problem, without the combinations the engine would refuse anyway."""
+    for tn, cg, st, rg in itertools.product(tile_n, cta_group, stages, raster_group):
+        if cg == 2 and tn % 64:
+            continue
+        if tn > max(64, -(-problem.n // 32) * 32):        # wider than the whole matrix: a duplicate
+            continue
+        yield Candidate(tn, cg, st, rg)
+
+
+# ------------------------------------------------------------------------------------------------
+# results file: JSON lines, append-only
+# ------------------------------------------------------------------------------------------------
+def load_results(path) -> dict:
+    """(problem key, candidate key) -> record.  Lines that do not parse are skipped, as a run killed
+    mid-write leaves at most one such line."""
+    out = {}
+    p = Path(path)
+    if not p.exists():
+        return out
+    for line in p.read_text().splitlines():
+        try:
+            rec = json.loads(line)
+            out[(rec["problem"], rec["candidate"])] = rec
+        except (ValueError, KeyError):
+            continue
+    return out
+
+
+def append_result(path, rec: dict) -> None:
+    """Appends one line; a torn last line (no newline) is closed first so the new record stays readable."""
+    torn = False
+    if os.path.exists(path) and os.path.getsize(path):
+        with open(path, "rb") as f:
+            f.seek(-1, os.SEEK_END)
+            torn = f.read(1) != b"\n"
+    with open(path, "a") as f:
+        f.write(("\n" if torn else "") + json.dumps(rec) + "\n")
+        f.flush()
+        os.fsync(f.fileno())
+
+
+def best(results: dict, problem: Problem):
+    """Fastest successful record of a problem, or None."""
+    ok = [r for (pk, _), r in results.items() if pk == problem.key() and r.get("category") == "success"]
+    return min(ok, key=lambda r: r["time_us"]) if ok else None
+
+
+# ------------------------------------------------------------------------------------------------
+# timing: repeat batches until the minimum stops improving
+# ------------------------------------------------------------------------------------------------
+def measure_until_stable(run_batch: Callable[[int], float], batch: int = 10, patience: int = 3,
+                         max_batches: int = 50, rel_improvement: float = 0.002) -> float:
+    """`run_batch(n)` returns the mean time of n back-to-back launches (any unit).  Batches are
+    repeated until `patience` in a row fail to beat the best by `rel_improvement`."""
+    best_t = float("inf")
+    stale = 0
+    for _ in range(max_batches):
+        t = run_batch(batch)
+        if t < best_t * (1.0 - rel_improvement):
+            best_t, stale = t, 0
+        else:
+            best_t = min(best_t, t)
+            stale += 1
+            if stale >= patience:
+                break
+    return best_t
+
+
+# ------------------------------------------------------------------------------------------------
+# NVML (read-only): wait while the GPU is thermally throttled
+# ------------------------------------------------------------------------------------------------
+THERMAL_BITS = 0x8 | 0x20 | 0x40     # hw_slowdown | sw_thermal_slowdown | hw_thermal_slowdown
+
+
+def wait_if_throttled(nvml, handle, max_wait_s: float = 30.0, poll_s: float = 0.5, sleep=time.sleep) -> bool:
+    """Returns True once no thermal reason is active (False if `max_wait_s` ran out)."""
+    waited = 0.0
+    while True:
+        try:
+            mask = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+        except AttributeError:
+            mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+        if not (mask & THERMAL_BITS):
+            return True
+        if waited >= max_wait_s:
+            return False
+        sleep(poll_s)
+        waited += poll_s
+
+
+def lock_clocks(nvml, handle, sm_mhz: int, *, i_understand_this_outlasts_the_process: bool = False) -> None:
+    """What tuning/setup.sh does with `nvidia-smi -lgc`.  Never called by this module; refuses unless
+    the caller states that the setting persists after the process (it needs root, and the next user
+    of the GPU inherits it).  Pair with `nvmlDeviceResetGpuLockedClocks`."""
+    if not i_understand_this_outlasts_the_process:
+        raise PermissionError("locking clocks changes a GPU setting that outlasts this process; not done by default")
+    nvml.nvmlDeviceSetGpuLockedClocks(handle, sm_mhz, sm_mhz)
+
+
+# ------------------------------------------------------------------------------------------------
+# the sweep
+# ------------------------------------------------------------------------------------------------
+def tune(problems: Iterable[Problem], results_path, *, measure: Callable[[Problem, Candidate | None], dict] | None = None,
+         candidate_fn=candidates, log=print) -> dict:
+    """Measures every candidate of every problem that the results file does not hold yet.
+    `measure(problem, candidate)` returns {"category": ..., "time_us": ...}; it defaults to the GPU
+    measurement below.  Returns the results dictionary."""
+    measure = measure or gpu_measure
+    results = load_results(results_path)
+    for prob in problems:
+        for cand in candidate_fn(prob):
+            k = (prob.key(), cand.key())
+            if k in results:
+                continue
+            try:
+                rec = measure(prob, cand)
+            except Exception as e:     # a candidate must never take the sweep down
+                rec = {"category": "unknown_error", "message": str(e)[:200]}
+            rec.update(problem=prob.key(), candidate=cand.key(), **asdict(cand))
+            append_result(results_path, rec)
+            results[k] = rec
+            log(f"{prob.key()} {cand.key()}: {rec['category']}" + (f" {rec['time_us']:.1f} us" if "time_us" in rec else ""))
+        b = best(results, prob)
+        if b:
+            flops = 2.0 * prob.m * prob.n * prob.k
+            log(f"best for {prob.key()}: {b['candidate']} {b['time_us']:.1f} us = {flops / b['time_us'] / 1e6:.0f} TFLOP/s")
+    return results
+
+
+# ------------------------------------------------------------------------------------------------
+# one candidate on the GPU
+# ------------------------------------------------------------------------------------------------
+_ELTYPES = {"Float16": "Float16", "BFloat16": "BFloat16", "TF32": "Float32"}
+_cache: dict = {}
+
+
+def _operands(prob: Problem):
+    """Seeded operands and the built-in configuration's output, made once per problem."""
+    import torch
+    from . import eltypes, arrays
+    if prob.key() in _cache:
+        return _cache[prob.key()]
+    _cache.clear()                                     # one problem resident at a time
+    et = getattr(eltypes, _ELTYPES[prob.dtype])
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    def rnd(r, c):
+        t = arrays.cuarray(et, r, c)
+        t.copy_((torch.rand(c, r, device="cuda", generator=g) - 0.5).t())
+        return t
+    a = rnd(*((prob.k, prob.m) if prob.trans_a else (prob.m, prob.k)))
+    b = rnd(*((prob.n, prob.k) if prob.trans_b else (prob.k, prob.n)))
+    c = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
+    c.zero_()
+    d_ref = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
+    d = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
+    _cache[prob.key()] = (a, b, c, d, d_ref, [False])
+    return _cache[prob.key()]
+
+
+def _config(prob: Problem, cand: Candidate | None):
+    from . import eltypes, layout as Layout, operator as Operator
+    from .config import get_config
+    et = getattr(eltypes, _ELTYPES[prob.dtype])
+    la = Layout.UnsafeAlignedRowMajor[et] if prob.trans_a else Layout.UnsafeAlignedColMajor[et]
+    lb = Layout.UnsafeAlignedRowMajor[et] if prob.trans_b else Layout.UnsafeAlignedColMajor[et]
+    extra = {} if cand is None else dict(tile_n=cand.tile_n, cta_group=cand.cta_group, stages=cand.stages,
+                                         raster_group=cand.raster_group)
+    return get_config(gemm_shape=dict(M=prob.m, N=prob.n, K=prob.k),
+                      operator=Operator.TCGen05Operator[et, eltypes.Float32],
+                      global_a_layout=la, global_b_layout=lb,
+                      global_c_layout=Layout.UnsafeAlignedColMajor[eltypes.Float32], **extra)
+
+
+def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None, nvml_handle=None) -> dict:
+    """Verifies and times one candidate.  Categories: success, config_error (the engine refused the
+    combination), invalid_result (differs from the built-in configuration's output), timeout (a
+    device-side wait gave up), cuda_error (anything else the library reported)."""
+    import torch
+    from .config import ConfigError
+    from .matmul import matmul, poll_status, DeviceTimeout, GemmKernelsError
+    a, b, c, d, d_ref, have_ref = _operands(prob)
+    try:
+        if not have_ref[0]:
+            matmul(_config(prob, None), a, b, c, d_ref)
+            torch.cuda.synchronize()
+            poll_status()
+            have_ref[0] = True
+        conf = _config(prob, cand)
+        d.zero_()
+        matmul(conf, a, b, c, d)
+        torch.cuda.synchronize()
+        poll_status()
+    except ConfigError as e:
+        return {"category": "config_error", "message": str(e)[:200]}
+    except DeviceTimeout as e:
+        return {"category": "timeout", "message": str(e)[:200]}
+    except GemmKernelsError as e:
+        return {"category": "cuda_error", "message": str(e)[:200]}
+    err = (torch.linalg.norm(d - d_ref) / torch.linalg.norm(d_ref).clamp_min(1e-30)).item()
+    if not err <= rtol:
+        return {"category": "invalid_result", "rel_error": err}
+    if nvml is not None:
+        wait_if_throttled(nvml, nvml_handle)
+
+    def run_batch(n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            matmul(conf, a, b, c, d)
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / n
+
+    run_batch(3)
+    t = measure_until_stable(run_batch)
+    poll_status()
+    return {"category": "success", "time_us": t, "rel_error": err,
+            "tflops": 2.0 * prob.m * prob.n * prob.k / t / 1e6}
+
+
+DEFAULT_PROBLEMS = tuple(Problem(n, n, n, ta, tb) for n in (2048, 4096, 8192)
+                         for ta in (False, True) for tb in (False, True))
+
+
+def main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description="Sweep the tcgen05 GEMM's tile parameters on this GPU.")
+    ap.add_argument("--out", default="tuning_results.jsonl")
+    ap.add_argument("--sizes", type=int, nargs="*", default=[2048, 4096, 8192])
+    ap.add_argument("--dtype", default="Float16", choices=sorted(_ELTYPES))
+    ap.add_argument("--layouts", nargs="*", default=["NN", "NT", "TN", "TT"])
+    ap.add_argument("--quick", action="store_true", help="stages and raster band left to the built-in choice")
+    args = ap.parse_args(argv)
+    probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype) for n in args.sizes for l in args.layouts]
+    fn = (lambda p: candidates(p, stages=(0,), raster_group=(0,))) if args.quick else candidates
+    tune(probs, args.out, candidate_fn=fn)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
