@@ -323,7 +323,7 @@ def run_gpu(args):
         cols = 2048
         dt, flops, threads = cpu_sgemm_sample(cols, 3, 1)
         line["cpu_baseline"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                                "sample": f"{n}x{cols}x{n} slice of the 8192^3 product, 3 timed runs after 1 warm-up, "
+                                "sample": f"{N_DIM}x{cols}x{N_DIM} slice of the 8192^3 product, 3 timed runs after 1 warm-up, "
                                           "numpy/OpenBLAS sgemm on Float32-promoted inputs"}
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -359,7 +359,7 @@ def run_side(args):
         conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.TCGen05Operator[GK.Float16, GK.Float32],
                              global_a_layout=Lay.UnsafeAlignedColMajor[GK.Float16], global_c_layout=Lay.Zero[GK.Float32],
                              global_d_layout=Lay.UnsafeAlignedColMajor[GK.Float32])
-        step = lambda: GK.matmul(conf, a, b, None, d)
+        step = GK.bind(conf, a, b, None, d)
         check = lambda: (d[5:9], a[5:9].float() @ b.float())
         flops, name = 2.0 * n ** 3, "c1: 2048^3 Float16 -> Float32, col-major, tcgen05"
         plan = GK.query(conf, a, b, None, d)
@@ -372,7 +372,7 @@ def run_side(args):
                              global_b_layout=Lay.UnsafeAlignedColMajor[GK.Float32], global_c_layout=Lay.Zero[GK.Float32],
                              global_d_layout=Lay.UnsafeAlignedColMajor[GK.Float32])
         epi = GK.Epilogue.Bias(bias, axis="row")
-        step = lambda: GK.matmul(conf, a, b, None, d, epilogue=epi, transform_shared_to_global_d=GK.Transform.ReLU())
+        step = GK.bind(conf, a, b, None, d, epilogue=epi, transform_shared_to_global_d=GK.Transform.ReLU())
         check = lambda: (d[5:9], torch.relu(a[:, 5:9].t().double() @ b.double() + bias[5:9, None].double()).float())
         flops, name, bound = 2.0 * n ** 3, "c2: 4096^3 Float32 FFMA, A transposed, bias(M)+ReLU fused", "fp32-fma"
         plan = GK.query(conf, a, b, None, d, epilogue=epi, transform_shared_to_global_d=GK.Transform.ReLU())
@@ -383,7 +383,7 @@ def run_side(args):
         conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.WMMAComplexOp[16, 16, 16, GK.Float16, GK.Float32],
                              global_a_layout=Lay.SplitColMajor[GK.Float16], global_c_layout=Lay.Zero[GK.Float32],
                              global_d_layout=Lay.SplitColMajor[GK.Float32], block_shape=(64, 64, 32))
-        step = lambda: GK.matmul(conf, a, b, None, d)
+        step = GK.bind(conf, a, b, None, d)
         def check():
             ar, ai, br, bi = a[5:9, :, 0].float(), a[5:9, :, 1].float(), b[..., 0].float(), b[..., 1].float()
             return d[5:9], torch.stack([ar @ br - ai @ bi, ar @ bi + ai @ br], dim=-1)
@@ -393,7 +393,7 @@ def run_side(args):
         e = 32
         a, b = rnd(GK.Float16, e, e, e, e, lo=-1), rnd(GK.Float16, e, e, e, e, lo=-1)
         d = GK.cuarray(GK.Float32, e, e, e, e)
-        step = lambda: GK.contract_(d, "abcd", a, "aebf", b, "dfce")
+        step = GK.bind_contract(d, "abcd", a, "aebf", b, "dfce")
         check = lambda: (d[3], torch.einsum("ebf,dfce->bcd", a[3].float(), b.float()))
         flops, name = 2.0 * e ** 6, "c4: C[a,b,c,d] = sum_ef A[a,e,b,f] B[d,f,c,e], extents 32 (M=N=K=1024), tcgen05 via 5-D TMA"
         plan = GK.contract_query(d, "abcd", a, "aebf", b, "dfce")
@@ -404,7 +404,7 @@ def run_side(args):
                              global_a_layout=Lay.Diagonal[GK.Float16], global_b_layout=Lay.UnsafeAlignedColMajor[GK.Float16],
                              global_c_layout=Lay.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64),
                              shared_a_layout=Lay.Padded[Lay.UnsafeAlignedColMajor[GK.Float16], 8])
-        step = lambda: GK.matmul(conf, v, b, c, d)
+        step = GK.bind(conf, v, b, c, d)
         check = lambda: (d[5:9], v[5:9, None].float() * b[5:9].float() + c[5:9])
         # streams B (2 B), C (4 B) in and D (4 B) out per element
         flops, name, bound, unit = 10.0 * n * n, "diag: D = diag(v) B + C, 4096^2, Float16 B, Float32 C/D (10 B per element)", "hbm", "GB/s"

@@ -373,7 +373,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     if (s != GK_OK) return s;
     plan->grid = L.grid; plan->block = kTcThreads; plan->cluster = L.cg;
     plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
-    plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn; plan->tile_k = L.params.bk;
+    plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
   } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {

@@ -6,7 +6,8 @@
 // accumulator planes) and the dual-number product (three terms).  Operands reach shared memory by
 // TMA with the 128-byte swizzle and are consumed by tcgen05.mma straight from there; accumulators
 // live in tensor memory, double-buffered so the epilogue of one tile overlaps the main loop of the
-// next.  With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of
+// next (single-buffered for the widest tiles, which fill all 512 columns: n_sub == 2 makes one tile
+// of two column blocks that reuse the same A stage, halving A's share of the shared-memory feed).  With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of
 // A and its own half of B's columns (no multicast), and the pair leader issues the MMAs for both.
 //
 // Warp roles (256 threads): warp 0 = TMA producer for A, warp 1 = MMA issuer, warp 2 = TMEM
@@ -52,10 +53,12 @@ struct TcParams {
   CUtensorMap tm_a;  // dims {contiguous, strided, plane}
   CUtensorMap tm_b;
   int32_t M, N, K;
-  int32_t tiles_m, tiles_n;  // cluster tiles: (128*CG) x bn
+  int32_t tiles_m, tiles_n;  // cluster tiles: (128*CG) x (n_sub*bn)
   int32_t k_blocks;
   int32_t raster_group;      // cluster tiles along M walked before stepping along N
-  int32_t bn;                // columns per cluster tile (multiple of 32; per-CTA B rows = bn/CG)
+  int32_t bn;                // columns per MMA (multiple of 32; per-CTA B rows = bn/CG)
+  int32_t n_sub;             // a cluster tile is n_sub (1 or 2) such column blocks that share A
+  int32_t acc_stages;        // accumulator stages in TMEM: 2, or 1 when one tile fills all 512 columns
   int32_t bk;                // K elements per k-block (128 bytes)
   int32_t stages;
   int32_t a_mn_major, b_mn_major;
@@ -69,7 +72,7 @@ struct TcParams {
   uint32_t idesc, idesc_neg;  // instruction descriptors (second one negates A)
   uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
   uint32_t a_swz, b_swz;      // descriptor swizzle field per operand (ptx.cuh: smem_desc_hi)
-  uint32_t tmem_cols;         // power of two >= 2 * acc_planes * bn
+  uint32_t tmem_cols;         // power of two >= acc_stages * n_sub * acc_planes * bn
   // Tensor contractions split an index of the product in two modes: index = in + div * out.
   // For a plain matrix the divisor is INT32_MAX (out == 0).  RANK5 kernels use these in the
   // producers (5-D tensor maps: {in, out} of the contiguous index, {in, out} of the other, plane).
@@ -139,6 +142,46 @@ __device__ __forceinline__ float tc_activation(float v, int32_t act) {
   return v;
 }
 
+// Epilogue of one full 32-column chunk with the element types fixed at compile time (DTC < 0: no C
+// operand).  All loads of C are issued before the first use, so their latencies overlap; the
+// arithmetic is the same expression, in the same order, as the element-wise path for ragged chunks.
+template <int PLANES, int DTC, int DTD>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint32_t (&v)[PLANES][32], int64_t ci,
+                                                  int64_t di, float bias_row, int col0) {
+  const bool c_pairs = PLANES == 2 && p.c_plane == 0;
+  const bool d_pairs = PLANES == 2 && p.d_plane == 0;
+  float cv[PLANES][32];
+  if constexpr (DTC >= 0) {
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+      const int64_t base = c_pairs ? 2 * ci + pl : pl * p.c_plane + ci;
+      const int64_t step = c_pairs ? 2 * p.c_sn0 : p.c_sn0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) cv[pl][j] = tc_load_elem(p.C, base + j * step, DTC);
+    }
+  }
+  const float* bias_col = p.bias_axis == TC_BIAS_COL ? p.bias + col0 : nullptr;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float bias = bias_col ? bias_col[j] : bias_row;
+    float out[PLANES];
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+      float x = p.alpha * __uint_as_float(v[pl][j]);
+      if constexpr (DTC >= 0) x += p.beta * cv[pl][j];
+      if (pl == 0) x += bias;
+      out[pl] = tc_activation(x, p.act);
+    }
+    const int64_t dj = di + j * p.d_sn0;
+    if (DTD == TC_F32 && d_pairs) {
+      reinterpret_cast<float2*>(p.D)[dj] = make_float2(out[0], out[PLANES - 1]);
+    } else {
+#pragma unroll
+      for (int pl = 0; pl < PLANES; ++pl) tc_store_elem(p.D, d_pairs ? 2 * dj + pl : pl * p.d_plane + dj, DTD, out[pl]);
+    }
+  }
+}
+
 // Cluster tile index -> (tile_m, tile_n): walk `raster_group` tiles down M, then step along N,
 // so that the tiles in flight at any time share A rows and B columns in L2.
 __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm, int& tn) {
@@ -164,7 +207,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
   const uint32_t rank = (CG == 2) ? cluster_cta_rank() : 0u;
   const bool leader = (rank == 0);
 
-  const uint32_t stage_bytes = p.a_planes * p.a_plane_bytes + p.b_planes * p.b_plane_bytes;
+  const uint32_t b_sub_bytes = p.b_planes * p.b_plane_bytes;   // one column block of B in a stage
+  const uint32_t stage_bytes = p.a_planes * p.a_plane_bytes + p.n_sub * b_sub_bytes;
   const uint32_t ctrl = smem_base + p.stages * stage_bytes;  // control block after the stages
   // control block layout (8-byte slots): full[stages], empty[stages], tmem_full[2], tmem_empty[2],
   // drain, then two 32-bit words: tmem base, abort flag.
@@ -209,7 +253,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
   const int bn_cta = p.bn / CG;
-  const uint32_t acc_cols = PLANES * p.bn;  // TMEM columns per accumulator stage
+  const int bn_tile = p.bn * p.n_sub;       // columns per cluster tile
+  const uint32_t sub_cols = PLANES * p.bn;  // TMEM columns per column block
+  const uint32_t acc_cols = p.n_sub * sub_cols;  // TMEM columns per accumulator stage
+  const bool two_acc = p.acc_stages == 2;
 
   if (warp == 0 || warp == 3) {
     // ------------------------------------------------------------------ TMA producers
@@ -223,19 +270,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const bool is_a = warp == 0;
       const int subs = RANK5 ? (is_a ? p.a_sub : p.b_sub) : 1;
       const int per_plane = (is_a ? p.a_boxes : p.b_boxes) * subs;
-      const int n_boxes = (is_a ? p.a_planes : p.b_planes) * per_plane;
+      const int per_block = (is_a ? p.a_planes : p.b_planes) * per_plane;   // boxes of one column block
+      const int n_boxes = (is_a ? 1 : p.n_sub) * per_block;
       const bool active = lane < n_boxes;
-      const int pl = active ? lane / per_plane : 0;
+      const int nb = active ? lane / per_block : 0;            // which column block (B only)
+      const int pl = active ? (lane % per_block) / per_plane : 0;
       const int bx = active ? (lane % per_plane) / subs : 0;   // which swizzle-span chunk
       const int sb = active ? (lane % per_plane) % subs : 0;   // which sub-box of it (RANK5)
       const bool mn_major = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
       const int sub_step = RANK5 ? (is_a ? p.a_sub_step : p.b_sub_step) : 0;
       const uint32_t dst_off =
           (is_a ? pl * p.a_plane_bytes + bx * p.a_box_bytes
-                : p.a_planes * p.a_plane_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes) +
+                : p.a_planes * p.a_plane_bytes + nb * b_sub_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes) +
           (RANK5 ? sb * (is_a ? p.a_sub_bytes : p.b_sub_bytes) : 0);
       const void* tmap = is_a ? static_cast<const void*>(&p.tm_a) : static_cast<const void*>(&p.tm_b);
-      const int mn_add = mn_major ? bx * (is_a ? p.a_box_mn : p.b_box_mn) : sb * sub_step;
+      const int mn_add = (mn_major ? bx * (is_a ? p.a_box_mn : p.b_box_mn) : sb * sub_step) + nb * p.bn;
       [[maybe_unused]] const int k_add = mn_major ? sb * sub_step : 0;
       [[maybe_unused]] const int perm = is_a ? p.a_perm : p.b_perm;
       [[maybe_unused]] const int mn_div = is_a ? p.a_mn_div : p.b_mn_div;   // RANK5 only
@@ -252,7 +301,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         int tm, tn;
         tc_tile_coords(p, t, tm, tn);
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
-        const int n_cta = tn * p.bn + static_cast<int>(rank) * bn_cta;
+        const int n_cta = tn * bn_tile + static_cast<int>(rank) * bn_cta;
         const int mn = (is_a ? m_cta : n_cta) + mn_add;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (prof) pt0 = clock64();
@@ -349,6 +398,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const uint32_t base16 = (smem_base & 0x3FFFFu) >> 4;
       const uint32_t stage16 = stage_bytes >> 4;
       const uint32_t a_k16 = p.a_kadv >> 4, b_k16 = p.b_kadv >> 4;
+      const uint32_t b_sub16 = b_sub_bytes >> 4;
       const int n_terms = (p.debug & 2) ? 0 : p.n_terms;
       int s = 0;
       uint32_t s16 = base16;
@@ -360,8 +410,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const long long k_start = clock64();
       const uint64_t g_start = global_timer_ns();
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
-        const uint32_t as = acc_it & 1u;
-        const uint32_t aph = (acc_it >> 1) & 1u;
+        const uint32_t as = two_acc ? (acc_it & 1u) : 0u;
+        const uint32_t aph = (two_acc ? (acc_it >> 1) : acc_it) & 1u;
         if (prof) t0 = clock64();
         const bool tgot = mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs);
         if (prof) mt += clock64() - t0;
@@ -386,12 +436,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
 #pragma unroll
           for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
 #pragma unroll
-            for (int ti = 0; ti < kMaxTerms; ++ti) {
-              if (ti < n_terms) {
-                const uint64_t da = smem_desc(s16 + t_a[ti] + ks * a_k16, hi_a);
-                const uint64_t db = smem_desc(s16 + t_b[ti] + ks * b_k16, hi_b);
-                const uint32_t acc = (kb | ks) ? 1u : t_keep[ti];
-                if (elected) umma<CG, TF32>(d_base + t_d[ti], da, db, t_id[ti], acc);
+            for (int nb = 0; nb < 2; ++nb) {
+              if (nb < p.n_sub) {
+#pragma unroll
+                for (int ti = 0; ti < kMaxTerms; ++ti) {
+                  if (ti < n_terms) {
+                    const uint64_t da = smem_desc(s16 + t_a[ti] + ks * a_k16, hi_a);
+                    const uint64_t db = smem_desc(s16 + t_b[ti] + nb * b_sub16 + ks * b_k16, hi_b);
+                    const uint32_t acc = (kb | ks) ? 1u : t_keep[ti];
+                    if (elected) umma<CG, TF32>(d_base + nb * sub_cols + t_d[ti], da, db, t_id[ti], acc);
+                  }
+                }
               }
             }
           }
@@ -431,13 +486,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     bool ok = true;
     const bool fast_store = PLANES == 1 && p.dtype_d == TC_F32 && p.beta == 0.0f &&
                             p.bias_axis != TC_BIAS_COL && p.act != TC_ACT_GELU;
+    const bool has_c = p.beta != 0.0f;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;
       tc_tile_coords(p, t, tm, tn);
       const int m = (tm * CG + static_cast<int>(rank)) * kTcTileM + q * 32 + lane;
-      const int n0 = tn * p.bn;
-      const uint32_t as = acc_it & 1u;
-      const uint32_t aph = (acc_it >> 1) & 1u;
+      const int n0 = tn * bn_tile;
+      const uint32_t as = two_acc ? (acc_it & 1u) : 0u;
+      const uint32_t aph = (two_acc ? (acc_it >> 1) : acc_it) & 1u;
       // all-or-nothing per warp: the TMEM loads below are warp-collective
       const long long e0 = (p.debug & 8) ? clock64() : 0;
       const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);
@@ -456,11 +512,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const int m_in = m % p.m_div, m_out = m / p.m_div;
       const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1;
-      for (int c = 0; c < p.bn; c += 32) {
+      for (int c = 0; c < bn_tile; c += 32) {
         uint32_t v[PLANES][32];
+        // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)
+        const uint32_t t_col = t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c);
+        if (!(p.debug & 64)) {
 #pragma unroll
-        for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_row + pl * p.bn + c, v[pl]);
-        tmem_ld_wait();
+          for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_col + pl * p.bn, v[pl]);
+          tmem_ld_wait();
+        }
+        if (p.debug & 32) continue;
         const int ncols = p.N - (n0 + c);  // columns of this chunk inside the matrix (may be <= 0)
         if (!m_ok || ncols <= 0) continue;
         const int n_in = (n0 + c) % p.n_div, n_out = (n0 + c) / p.n_div;  // a chunk never straddles n_div
@@ -492,6 +553,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
           const bool d_pairs = PLANES == 2 && p.d_plane == 0;
           int64_t ci = c_row + n_in * p.c_sn0 + n_out * p.c_sn1;  // element (m, n) of one plane
           int64_t di = d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
+          if (ncols >= 32 && (!has_c || p.dtype_c == p.dtype_d)) {
+            // full chunk, C (if any) of D's type: the specialised, load-batched variants
+            const int col0 = n0 + c;
+            if (p.dtype_d == TC_F32) {
+              if (has_c) tc_epilogue_chunk<PLANES, TC_F32, TC_F32>(p, v, ci, di, bias_row, col0);
+              else tc_epilogue_chunk<PLANES, -1, TC_F32>(p, v, ci, di, bias_row, col0);
+            } else if (p.dtype_d == TC_F16) {
+              if (has_c) tc_epilogue_chunk<PLANES, TC_F16, TC_F16>(p, v, ci, di, bias_row, col0);
+              else tc_epilogue_chunk<PLANES, -1, TC_F16>(p, v, ci, di, bias_row, col0);
+            } else {
+              if (has_c) tc_epilogue_chunk<PLANES, TC_BF16, TC_BF16>(p, v, ci, di, bias_row, col0);
+              else tc_epilogue_chunk<PLANES, -1, TC_BF16>(p, v, ci, di, bias_row, col0);
+            }
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j, ci += p.c_sn0, di += p.d_sn0) {
             if (j < ncols) {

@@ -157,9 +157,10 @@ static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5) {
 
 static constexpr int kSmemBudget = 232448;  // 227 KiB opt-in limit per CTA on sm_100
 static constexpr int kCtrlBytes = 256;
+static constexpr double kWideEff = 1.08;   // measured gain of the single-stage 512-column tiles on large products
 
-static int stage_bytes_for(int cg, int bn, int a_planes, int b_planes) {
-  return a_planes * kTcTileM * kTcKBytes + b_planes * (bn / cg) * kTcKBytes;
+static int stage_bytes_for(int cg, int bn, int n_sub, int a_planes, int b_planes) {
+  return a_planes * kTcTileM * kTcKBytes + n_sub * b_planes * (bn / cg) * kTcKBytes;
 }
 
 // Can a box of `total` elements starting at multiples of `total` be cut from an index whose inner
@@ -172,36 +173,46 @@ static bool box_fits(int64_t ext0, int64_t ext1, int total) {
 
 // Picks (cta_group, tile_n): fewest "tile-time" units over the persistent grid, where a larger
 // tile is worth more per unit time (operand reuse) but quantises worse on small problems.
-static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_out, int* bn_out) {
+// A tile is n_sub column blocks of bn columns (bn = the MMA's N, <= 256).  Tiles whose accumulators
+// fill all 512 TMEM columns (n_sub * planes * bn == 512) run with one accumulator stage: their
+// epilogue is not overlapped, which the efficiency figure accounts for; they pay off on large
+// problems, where the main loop is limited by the operand feed from L2 rather than by the MMAs.
+static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_out, int* bn_out, int* nsub_out) {
   // an N-contiguous B is loaded in boxes of 128 bytes of N per CTA
   int n_unit = pr.B.mn_major ? kTcKBytes / dtype_size(pr.B.dtype) : 8;
   if (pr.rank5 && pr.B.mn_major && pr.B.mn_ext[1] > 1 && pr.B.mn_ext[0] < n_unit) n_unit = static_cast<int>(pr.B.mn_ext[0]);
-  struct Cand { int cg, bn; double eff; };
-  static const Cand cands[] = {{2, 256, 1.00}, {1, 256, 0.92}, {2, 128, 0.80},
-                               {1, 128, 0.74}, {1, 64, 0.50},  {1, 32, 0.30}};
+  struct Cand { int cg, bn, n_sub; double eff; };
+  static const Cand cands[] = {{2, 256, 2, kWideEff}, {2, 256, 1, 1.00}, {1, 256, 1, 0.92}, {2, 128, 1, 0.80},
+                               {1, 128, 1, 0.74},     {1, 64, 1, 0.50},  {1, 32, 1, 0.30}};
   double best = 1e300;
-  int bcg = 1, bbn = 128;
+  int bcg = 1, bbn = 128, bns = 1;
   for (const Cand& c : cands) {
-    if (planes * c.bn > 256) continue;  // two accumulator stages must fit 512 TMEM columns
+    if (c.n_sub * planes * c.bn > 512) continue;  // accumulators of one tile must fit 512 TMEM columns
+    if (c.n_sub > 1 && pr.rank5) continue;
     if ((c.bn / c.cg) % n_unit) continue;
     if (pr.cta_group && c.cg != pr.cta_group) continue;
-    if (pr.tile_n && c.bn != pr.tile_n) continue;
+    if (pr.tile_n && c.bn * c.n_sub != pr.tile_n) continue;
     if (!pr.B.mn_major && !box_fits(pr.B.mn_ext[0], pr.B.mn_ext[1], c.bn / c.cg)) continue;
     if (!pr.B.mn_major && pr.B.mn_ext[1] > 1 && pr.B.mn_ext[0] < c.bn / c.cg && (c.bn / c.cg) / pr.B.mn_ext[0] > 16) continue;
     if (pr.n_ext0 < pr.N && (pr.n_ext0 % 32 != 0)) continue;
     const int64_t tm = (pr.M + 128 * c.cg - 1) / (128 * c.cg);
-    const int64_t tn = (pr.N + c.bn - 1) / c.bn;
+    const int64_t tn = (pr.N + c.bn * c.n_sub - 1) / (c.bn * c.n_sub);
     const int64_t slots = std::max(1, sm_count / c.cg);
     const int64_t waves = (tm * tn + slots - 1) / slots;
-    const double t = static_cast<double>(waves) * c.bn / c.eff;
-    if (t < best) { best = t; bcg = c.cg; bbn = c.bn; }
+    // a single accumulator stage exposes the epilogue: worth it only when the main loop is long
+    double eff = c.eff;
+    if (c.n_sub * planes * c.bn > 256) eff = pr.K >= 1024 ? kWideEff : 0.5;
+    const double t = static_cast<double>(waves) * c.bn * c.n_sub / eff;
+    if (t < best) { best = t; bcg = c.cg; bbn = c.bn; bns = c.n_sub; }
   }
   if (best == 1e300) {  // overrides that match no candidate: honour them if they are valid
     bcg = pr.cta_group ? pr.cta_group : 1;
     bbn = pr.tile_n ? pr.tile_n : 128;
+    if (bbn == 512) { bbn = 256; bns = 2; }
   }
   *cg_out = bcg;
   *bn_out = bbn;
+  *nsub_out = bns;
 }
 
 void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
@@ -239,23 +250,26 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   const bool tf32 = pr.A.dtype == GK_F32;
   const int planes = pr.number == GK_REAL ? 1 : 2;
 
-  int cg, bn;
-  choose_tile(pr, h->sm_count, planes, &cg, &bn);
+  int cg, bn, n_sub;
+  choose_tile(pr, h->sm_count, planes, &cg, &bn, &n_sub);
   if (cg != 1 && cg != 2)
     return set_error(GK_ERR_INVALID_CONFIG, "cta_group must be 1 or 2, got %d", cg);
-  if (bn < 32 || bn > 256 || bn % 32 || planes * bn > 256 || (cg == 2 && bn % 64))
+  if (bn < 32 || bn > 256 || bn % 32 || n_sub * planes * bn > 512 || (cg == 2 && bn % 64))
     return set_error(GK_ERR_INVALID_CONFIG,
-                     "tile_n = %d is not usable (multiple of 32 (64 for CTA pairs), <= %d)", bn,
-                     256 / planes);
+                     "tile_n = %d is not usable (multiple of 32 (64 for CTA pairs), <= %d)", bn * n_sub,
+                     512 / planes);
+  const int acc_stages = n_sub * planes * bn > 256 ? 1 : 2;
 
   p.M = static_cast<int32_t>(pr.M);
   p.N = static_cast<int32_t>(pr.N);
   p.K = static_cast<int32_t>(pr.K);
   p.bn = bn;
+  p.n_sub = n_sub;
+  p.acc_stages = acc_stages;
   p.bk = kTcKBytes / es;
   p.k_blocks = (p.K + p.bk - 1) / p.bk;
   p.tiles_m = (p.M + kTcTileM * cg - 1) / (kTcTileM * cg);
-  p.tiles_n = (p.N + bn - 1) / bn;
+  p.tiles_n = (p.N + bn * n_sub - 1) / (bn * n_sub);
   p.a_planes = p.b_planes = planes;
   p.a_mn_major = pr.A.mn_major ? 1 : 0;
   p.b_mn_major = pr.B.mn_major ? 1 : 0;
@@ -307,7 +321,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
     p.b_boxes = 1; p.b_box_bytes = p.b_plane_bytes;
     p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32; p.b_swz = 2;
   }
-  if (planes * std::max(p.a_boxes, p.b_boxes) > 32)
+  if (planes * std::max(p.a_boxes, n_sub * p.b_boxes) > 32)
     return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
   // Two-mode operands: a box covers one swizzle span of the contiguous mode and rows of ONE other
   // mode; what a k-block (MN-major) or the tile's rows (K-major) need beyond that comes from
@@ -380,7 +394,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   p.idesc = idesc;
   p.idesc_neg = idesc | (1u << 13);                   // negate A
 
-  const int stage_bytes = stage_bytes_for(cg, bn, planes, planes);
+  const int stage_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
   int stages = (kSmemBudget - 1024 - kCtrlBytes) / stage_bytes;
   stages = std::min(stages, 8);
   if (pr.stages) stages = std::min(stages, pr.stages);
@@ -389,7 +403,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
     return set_error(GK_ERR_INVALID_CONFIG, "Requested too much shared memory: one pipeline stage needs %d bytes", stage_bytes);
   p.stages = stages;
   uint32_t cols = 32;
-  while (cols < static_cast<uint32_t>(2 * planes * bn)) cols <<= 1;
+  while (cols < static_cast<uint32_t>(acc_stages * n_sub * planes * bn)) cols <<= 1;
   p.tmem_cols = cols;
 
   // raster
@@ -397,7 +411,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   int group = pr.raster_group;
   if (pr.raster == GK_RASTER_IDENTITY) group = p.tiles_m;
   if (group <= 0)
-    group = static_cast<int>(std::lround(std::sqrt(static_cast<double>(slots_guess) * bn / (kTcTileM * cg))));
+    group = static_cast<int>(std::lround(std::sqrt(static_cast<double>(slots_guess) * bn * n_sub / (kTcTileM * cg))));
   p.raster_group = std::max(1, std::min(group, p.tiles_m));
 
   // epilogue

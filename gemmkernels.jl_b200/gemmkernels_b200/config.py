@@ -230,8 +230,8 @@ def get_config(*, gemm_shape, operator, global_a_layout, global_c_layout, **para
     cta_group = int(params.get("cta_group", 0))
     if cta_group not in (0, 1, 2):
         raise ConfigError("cta_group must be 1 or 2 (0 = choose)")
-    if tile_n and (tile_n % 32 or not 32 <= tile_n <= 256):
-        raise ConfigError("tile_n must be a multiple of 32 between 32 and 256 (0 = choose)")
+    if tile_n and tile_n != 512 and (tile_n % 32 or not 32 <= tile_n <= 256):
+        raise ConfigError("tile_n must be a multiple of 32 between 32 and 256, or 512 (0 = choose)")
 
     return Config(
         gemm_shape, block_shape, warps_per_block,

@@ -86,3 +86,40 @@ def contract_(D, modes_d: str, A, modes_a: str, B, modes_b: str, alpha=1.0, beta
     if st != L.GK_OK:
         _raise(st)
     return D
+
+
+class BoundContraction:
+    """`contract_` with its descriptor built once (and its workspace allocated once): calling the
+    object enqueues the same contraction again for the cost of one FFI call."""
+
+    def __init__(self, D, modes_d, A, modes_a, B, modes_b, alpha=1.0, beta=0.0, C_in=None, *, compute=None,
+                 workspace=None, force_gather=False, tile_n=0, cta_group=0):
+        import torch
+        if beta != 0 and C_in is None:
+            C_in = D
+        self.desc = _desc(D, modes_d, A, modes_a, B, modes_b, alpha, beta, C_in, compute, force_gather, tile_n, cta_group)
+        self.device = D.device.index if D.device.index is not None else torch.cuda.current_device()
+        with torch.cuda.device(self.device):
+            self.handle = handle(self.device)
+            if workspace is None:
+                plan = L.GemmPlan()
+                st = L.lib.gk_contract_query(self.handle, C.byref(self.desc), C.byref(plan))
+                if st != L.GK_OK:
+                    _raise(st)
+                if plan.workspace_bytes:
+                    workspace = torch.empty(plan.workspace_bytes // 8 + 1, dtype=torch.int64, device=D.device)
+        self.ws = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
+        self.ptrs = (A.data_ptr(), B.data_ptr(), C_in.data_ptr() if C_in is not None else None, D.data_ptr())
+        self._keep = (A, B, C_in, D, workspace)
+        self._torch = torch
+
+    def __call__(self, stream=None):
+        s = stream if stream is not None else self._torch.cuda.current_stream(self.device).cuda_stream
+        st = L.lib.gk_contract(self.handle, C.byref(self.desc), *self.ptrs, *self.ws, C.c_void_p(s))
+        if st != L.GK_OK:
+            _raise(st)
+
+
+def bind_contract(*args, **kwargs) -> BoundContraction:
+    """Same arguments as `contract_` (without `stream`); returns a callable that enqueues it."""
+    return BoundContraction(*args, **kwargs)

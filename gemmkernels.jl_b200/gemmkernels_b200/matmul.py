@@ -271,6 +271,46 @@ def matmul(conf: Config, a, b, c, d, *,
     return None
 
 
+class BoundMatmul:
+    """`matmul` with its arguments lowered once: calling the object enqueues the same GEMM again
+    (same arrays, same descriptors) for the cost of one FFI call.  The Julia package gets the same
+    effect from its compiled-kernel cache; in Python the per-call lowering (~25 us) would otherwise
+    dominate small problems.  The arrays are kept alive by the object."""
+
+    def __init__(self, conf, a, b, c, d, hooks, epilogue, kernel, workspace):
+        import torch
+        self._keep = (a, b, c, d, epilogue, workspace)
+        self.desc, self.epi, self.ptrs = lower(conf, a, b, c, d, hooks, epilogue, kernel)
+        self.device = d.device.index if d.device.index is not None else torch.cuda.current_device()
+        with torch.cuda.device(self.device):
+            self.handle = handle(self.device)
+            if workspace is None and self.desc.number != L.GK_REAL and (self.desc.plane_a == 0 or self.desc.plane_b == 0):
+                plan = L.GemmPlan()
+                st = L.lib.gk_gemm_query(self.handle, C.byref(self.desc), C.byref(self.epi), C.byref(plan))
+                if st != L.GK_OK:
+                    _raise(st)
+                if plan.workspace_bytes:
+                    workspace = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=d.device)
+                    self._keep += (workspace,)
+        self.ws = workspace.data_ptr() if workspace is not None else None
+        self._torch = torch
+
+    def __call__(self, stream=None):
+        """Enqueues on `stream` (a raw CUDA stream handle) or on torch's current stream of the
+        device that holds D; that device must be current."""
+        s = stream if stream is not None else self._torch.cuda.current_stream(self.device).cuda_stream
+        pa, pb, pc, pd = self.ptrs
+        st = L.lib.gk_gemm(self.handle, C.byref(self.desc), pa, pb, pc, pd, C.byref(self.epi), self.ws, C.c_void_p(s))
+        if st != L.GK_OK:
+            _raise(st)
+
+
+def bind(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, workspace=None, **transforms):
+    """Lower `matmul(conf, a, b, c, d; ...)` once and return a callable that enqueues it."""
+    hooks = {k.replace("transform_", ""): v for k, v in transforms.items()}
+    return BoundMatmul(conf, a, b, c, d, hooks, epilogue or Epilogue.Default(), kernel, workspace)
+
+
 def matmul_host(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, stream=None,
                 device_index=None, **transforms):
     """`matmul` for matrices in host memory (column-major CPU tensors, ideally pinned): copies the

@@ -39,9 +39,11 @@ class Problem:
     trans_a: bool = False
     trans_b: bool = False
     dtype: str = "Float16"      # Float16 | BFloat16 | TF32
+    with_c: bool = False        # D = A*B + C (C Float32) instead of D = A*B
 
     def key(self) -> str:
-        return f"{self.dtype}:{self.m}x{self.n}x{self.k}:{'T' if self.trans_a else 'N'}{'T' if self.trans_b else 'N'}"
+        return (f"{self.dtype}:{self.m}x{self.n}x{self.k}:{'T' if self.trans_a else 'N'}{'T' if self.trans_b else 'N'}"
+                + ("+C" if self.with_c else ""))
 
 
 @dataclass(frozen=True)
@@ -208,8 +210,10 @@ def _operands(prob: Problem):
         return t
     a = rnd(*((prob.k, prob.m) if prob.trans_a else (prob.m, prob.k)))
     b = rnd(*((prob.n, prob.k) if prob.trans_b else (prob.k, prob.n)))
-    c = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
-    c.zero_()
+    c = None
+    if prob.with_c:
+        c = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
+        c.copy_(torch.rand(prob.n, prob.m, device="cuda", generator=g).t())
     d_ref = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
     d = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
     _cache[prob.key()] = (a, b, c, d, d_ref, [False])
@@ -227,7 +231,8 @@ def _config(prob: Problem, cand: Candidate | None):
     return get_config(gemm_shape=dict(M=prob.m, N=prob.n, K=prob.k),
                       operator=Operator.TCGen05Operator[et, eltypes.Float32],
                       global_a_layout=la, global_b_layout=lb,
-                      global_c_layout=Layout.UnsafeAlignedColMajor[eltypes.Float32], **extra)
+                      global_c_layout=(Layout.UnsafeAlignedColMajor if prob.with_c else Layout.Zero)[eltypes.Float32],
+                      global_d_layout=Layout.UnsafeAlignedColMajor[eltypes.Float32], **extra)
 
 
 def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None, nvml_handle=None) -> dict:
@@ -236,7 +241,7 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
     device-side wait gave up), cuda_error (anything else the library reported)."""
     import torch
     from .config import ConfigError
-    from .matmul import matmul, poll_status, DeviceTimeout, GemmKernelsError
+    from .matmul import bind, matmul, poll_status, DeviceTimeout, GemmKernelsError
     a, b, c, d, d_ref, have_ref = _operands(prob)
     try:
         if not have_ref[0]:
@@ -246,7 +251,8 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
             have_ref[0] = True
         conf = _config(prob, cand)
         d.zero_()
-        matmul(conf, a, b, c, d)
+        launch = bind(conf, a, b, c, d)
+        launch()
         torch.cuda.synchronize()
         poll_status()
     except ConfigError as e:
@@ -265,7 +271,7 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n):
-            matmul(conf, a, b, c, d)
+            launch()
         e1.record()
         e1.synchronize()
         return e0.elapsed_time(e1) * 1e3 / n
@@ -288,9 +294,10 @@ def main(argv=None) -> int:
     ap.add_argument("--sizes", type=int, nargs="*", default=[2048, 4096, 8192])
     ap.add_argument("--dtype", default="Float16", choices=sorted(_ELTYPES))
     ap.add_argument("--layouts", nargs="*", default=["NN", "NT", "TN", "TT"])
+    ap.add_argument("--with-c", action="store_true", help="tune D = A*B + C instead of D = A*B")
     ap.add_argument("--quick", action="store_true", help="stages and raster band left to the built-in choice")
     args = ap.parse_args(argv)
-    probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype) for n in args.sizes for l in args.layouts]
+    probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype, args.with_c) for n in args.sizes for l in args.layouts]
     fn = (lambda p: candidates(p, stages=(0,), raster_group=(0,))) if args.quick else candidates
     tune(probs, args.out, candidate_fn=fn)
     return 0

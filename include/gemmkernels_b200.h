@@ -113,7 +113,8 @@ typedef struct gk_gemm_desc {
   int32_t raster;       /* gk_raster */
   double alpha, beta;
   /* Tuning overrides; 0 = use the built-in table. */
-  int32_t tile_n;       /* 32..256, multiple of 32 (per CTA pair when cta_group = 2) */
+  int32_t tile_n;       /* 32..256, multiple of 32 (per CTA pair when cta_group = 2); 512 = two 256-column
+                           accumulators that share each A stage, single accumulator stage (real products) */
   int32_t cta_group;    /* 1 or 2 */
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t raster_group; /* T of the tiled rasters */

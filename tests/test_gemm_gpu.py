@@ -246,7 +246,7 @@ def test_metric_shape_8192_sampled_rows_and_linearity():
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("cg,bn", [(1, 128), (2, 256), (1, 256), (2, 128)])
+@pytest.mark.parametrize("cg,bn", [(1, 128), (2, 256), (1, 256), (2, 128), (2, 512)])
 def test_tile_shapes_and_transposes_exact(ta, tb, cg, bn):
     """Small-integer inputs make the FP16 -> FP32 product exact, so any layout / descriptor slip
     shows as a hard mismatch rather than as noise."""
@@ -294,6 +294,25 @@ def test_config3_planar_complex_4096_sampled():
     assert O.normwise_error(got[..., 0], re) <= TOL_TENSOR and O.normwise_error(got[..., 1], im) <= TOL_TENSOR
 
 
+@pytest.mark.parametrize("opcls,ref", [(Operator.WMMAComplexOp, "complex"), (Operator.WMMADualOp, "dual")])
+def test_planar_complex_dual_single_accumulator_stage(opcls, ref):
+    """tile_n = 256 with two accumulator planes fills all 512 TMEM columns: the single-stage
+    schedule (epilogue not overlapped) must give the same numbers; several tiles per CTA pair."""
+    M, N, K = 4096, 2560, 256
+    rng = np.random.default_rng(77)
+    A = rng.integers(-2, 3, (2, M, K)).astype(np.float16); B = rng.integers(-2, 3, (2, K, N)).astype(np.float16)
+    d = GK.cuarray(GK.Float32, M, N, 2)
+    conf = run_matmul(planar(A), planar(B), None, d, M=M, N=N, K=K, op=opcls[16, 16, 16, GK.Float16, GK.Float32],
+                      la=Layout.SplitColMajor[GK.Float16], lb=Layout.SplitColMajor[GK.Float16],
+                      lc=Layout.Zero[GK.Float32], ld=Layout.SplitColMajor[GK.Float32], block_shape=(64, 64, 32),
+                      tile_n=256, cta_group=2)
+    plan = GK.query(conf, planar(A), planar(B), None, d)
+    assert plan.tile_n == 256 and plan.tmem_columns == 512
+    p0, p1 = (O.complex_gemm if ref == "complex" else O.dual_gemm)(A[0], A[1], B[0], B[1])
+    got = GK.to_numpy(d)
+    assert np.array_equal(got[..., 0], p0) and np.array_equal(got[..., 1], p1)     # small integers: exact
+
+
 # ------------------------------------------------------------------------------------------------
 # edge cases and error behaviour
 # ------------------------------------------------------------------------------------------------
@@ -307,6 +326,45 @@ def test_beta_with_aliased_c_and_d_and_fp16_output():
     torch.cuda.synchronize()
     want = O.gemm(A, B, Cm, 2.0, 3.0)
     assert O.isapprox_elementwise(want, GK.to_numpy(c), "Float16")
+
+
+def test_bound_matmul_replays_the_same_gemm():
+    """GK.bind lowers once; each call of the object enqueues the same GEMM (here in place: D = A*B + D)."""
+    rng = np.random.default_rng(22)
+    M, N, K = 384, 320, 192
+    A = rng.integers(-2, 3, (M, K)).astype(np.float16); B = rng.integers(-2, 3, (K, N)).astype(np.float16)
+    d = dev(np.zeros((M, N), dtype=np.float32))
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=Layout.ColMajor[GK.Float16], global_c_layout=Layout.ColMajor[GK.Float32])
+    launch = GK.bind(conf, dev(A), dev(B), d, d)
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize(); GK.poll_status()
+    assert np.array_equal(GK.to_numpy(d), 3 * (A.astype(np.float32) @ B.astype(np.float32)))
+
+
+@pytest.mark.parametrize("cd", ["Float32", "Float16", "BFloat16"])
+@pytest.mark.parametrize("bias_axis,act", [(None, None), ("col", Transform.GELU()), ("row", Transform.ReLU())])
+def test_epilogue_variants_full_and_ragged_chunks(cd, bias_axis, act):
+    """alpha*A*B + beta*C with C and D of one type, N not a multiple of 32: full chunks take the
+    type-specialised epilogue, the last chunk the element-wise one; both must agree with the oracle."""
+    rng = np.random.default_rng(23)
+    M, N, K = 300, 1000, 136
+    CD = getattr(GK, cd)
+    AB = GK.BFloat16 if cd == "BFloat16" else GK.Float16         # BFloat16 results come from BFloat16 operands
+    A = (rng.integers(-8, 9, (M, K)) / 16).astype(np.float32); B = (rng.integers(-8, 9, (K, N)) / 16).astype(np.float32)
+    Cm = (rng.random((M, N)) - 0.5).astype(np.float32)
+    c = dev(Cm, CD); Cq = GK.to_numpy(c).astype(np.float32)
+    d = GK.cuarray(CD, M, N)
+    bias = (rng.random(M if bias_axis == "row" else N) - 0.5).astype(np.float32) if bias_axis else None
+    epi = Epilogue.Bias(torch.from_numpy(bias).cuda(), axis=bias_axis) if bias_axis else None
+    run_matmul(dev(A, AB), dev(B, AB), c, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[AB, GK.Float32],
+               la=Layout.ColMajor[AB], lb=Layout.ColMajor[AB], lc=Layout.ColMajor[CD], ld=Layout.ColMajor[CD],
+               alpha=1.5, beta=0.5, epilogue=epi, act=act)
+    want = 1.5 * (A.astype(np.float32) @ B.astype(np.float32)) + 0.5 * Cq
+    want = O.epilogue(want, bias, bias_axis or "col", {Transform.ReLU: "relu", Transform.GELU: "gelu"}.get(type(act)))
+    tol = {"Float32": 1e-5, "Float16": 1e-3, "BFloat16": 8e-3}[cd]
+    assert O.normwise_error(GK.to_numpy(d).astype(np.float32), want) <= tol
 
 
 def test_leading_dimension_larger_than_rows():
@@ -403,6 +461,12 @@ def test_config4_contraction_extents32(force_gather):
     torch.cuda.synchronize(); GK.poll_status()
     want = O.contract(A, "aebf", B, "dfce", "abcd")
     assert O.normwise_error(GK.to_numpy(d), want) <= TOL_TENSOR
+    # the bound form enqueues the same contraction
+    d2 = GK.cuarray(GK.Float32, 32, 32, 32, 32)
+    launch = GK.bind_contract(d2, "abcd", a, "aebf", b, "dfce", force_gather=force_gather)
+    launch(); launch()
+    torch.cuda.synchronize(); GK.poll_status()
+    assert torch.equal(d2, d)
 
 
 def test_contraction_alpha_beta_and_three_index_case():
