@@ -324,6 +324,9 @@ gk_status gk_destroy(gk_handle h) {
   if (!h) return GK_OK;
   for (int i = 0; i < 5; ++i)
     if (h->stage_dev[i]) cudaFree(h->stage_dev[i]);
+  for (cudaEvent_t e : h->events) cudaEventDestroy(e);
+  if (h->copy_in) cudaStreamDestroy(h->copy_in);
+  if (h->copy_out) cudaStreamDestroy(h->copy_out);
   if (h->status_host) cudaFreeHost(h->status_host);
   delete h;
   return GK_OK;
@@ -459,6 +462,124 @@ static gk_status stage_reserve(gk_handle h, int slot, size_t bytes) {
   return GK_OK;
 }
 
+// Block (r0.., c0..) of a column-major matrix with leading dimension ld, between host and device images
+// that share the layout.
+static cudaError_t copy_block(void* dst, const void* src, int64_t ld, size_t es, int64_t r0, int64_t nr, int64_t c0,
+                              int64_t nc, cudaMemcpyKind kind, cudaStream_t st) {
+  const size_t off = (static_cast<size_t>(c0) * ld + r0) * es;
+  return cudaMemcpy2DAsync(static_cast<char*>(dst) + off, ld * es, static_cast<const char*>(src) + off, ld * es,
+                           nr * es, nc, kind, st);
+}
+
+// gk_gemm_host for large real products: D is cut into row-chunk x column-chunk blocks; the chunks of A
+// and B go up on one copy stream in the order the blocks need them, each block is multiplied as soon as
+// its two chunks have landed, and finished blocks go back on a second copy stream, so host-to-device
+// traffic, the kernels and device-to-host traffic overlap (PCIe carries both directions at once).
+// Returns GK_ERR_UNSUPPORTED (without setting the error text) when the problem is too small to cut.
+static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const void* a_host, const void* b_host,
+                                     const void* c_host, void* d_host, const gk_epilogue_desc* epi, bool read_c,
+                                     size_t a_bytes, size_t b_bytes, cudaStream_t st) {
+  // chunk size: reserved[1] megabytes when set (a tuning aid), else 32 MiB
+  const size_t target = static_cast<size_t>(d.reserved[1] > 0 ? d.reserved[1] : 32) << 20;
+  auto chunks = [target](size_t bytes) {
+    const int n = static_cast<int>((bytes + target / 2) / target);
+    return std::max(1, std::min(n, 8));
+  };
+  auto ceil_div = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
+  const int64_t mr = ceil_div(ceil_div(d.m, chunks(a_bytes)), 256) * 256;   // rows per chunk
+  const int64_t nc = ceil_div(ceil_div(d.n, chunks(b_bytes)), 512) * 512;   // columns per chunk
+  const int R = static_cast<int>(ceil_div(d.m, mr)), Cn = static_cast<int>(ceil_div(d.n, nc));
+  if (R * Cn <= 1) return GK_ERR_UNSUPPORTED;
+  if (!h->copy_in) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+  if (!h->copy_out) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+  const size_t n_events = 2 * static_cast<size_t>(R) * Cn + 2;
+  while (h->events.size() < n_events) {
+    cudaEvent_t e;
+    GK_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    h->events.push_back(e);
+  }
+  const size_t es_a = dtype_size(d.dtype_a), es_b = dtype_size(d.dtype_b), es_c = dtype_size(d.dtype_c),
+               es_d = dtype_size(d.dtype_d);
+  char* a_dev = static_cast<char*>(h->stage_dev[0]);
+  char* b_dev = static_cast<char*>(h->stage_dev[1]);
+  char* c_dev = static_cast<char*>(h->stage_dev[2]);
+  char* d_dev = static_cast<char*>(h->stage_dev[3]);
+  size_t ev = 0;
+  // the copy streams start after whatever the caller queued before this call
+  GK_CUDA_CHECK(cudaEventRecord(h->events[ev], st));
+  GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_in, h->events[ev], 0));
+  GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_out, h->events[ev], 0));
+  ++ev;
+  gk_epilogue_desc epi_blk;
+  if (epi) epi_blk = *epi;
+  if (epi && epi->bias_axis != GK_BIAS_NONE) {
+    const size_t bias_bytes = sizeof(float) * static_cast<size_t>(epi->bias_axis == GK_BIAS_ROW ? d.m : d.n);
+    GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[4], epi->bias, bias_bytes, cudaMemcpyHostToDevice, h->copy_in));
+  }
+  auto load_a = [&](int i) -> cudaError_t {
+    const int64_t i0 = i * mr, mi = std::min<int64_t>(mr, d.m - i0);
+    return d.trans_a ? copy_block(a_dev, a_host, d.lda, es_a, 0, d.k, i0, mi, cudaMemcpyHostToDevice, h->copy_in)
+                     : copy_block(a_dev, a_host, d.lda, es_a, i0, mi, 0, d.k, cudaMemcpyHostToDevice, h->copy_in);
+  };
+  auto load_b = [&](int j) -> cudaError_t {
+    const int64_t j0 = j * nc, nj = std::min<int64_t>(nc, d.n - j0);
+    return d.trans_b ? copy_block(b_dev, b_host, d.ldb, es_b, j0, nj, 0, d.k, cudaMemcpyHostToDevice, h->copy_in)
+                     : copy_block(b_dev, b_host, d.ldb, es_b, 0, d.k, j0, nj, cudaMemcpyHostToDevice, h->copy_in);
+  };
+  // One block of D: waits for everything queued on the copy-in stream so far, multiplies, sends back.
+  auto block = [&](int i, int j) -> gk_status {
+    const int64_t i0 = i * mr, mi = std::min<int64_t>(mr, d.m - i0);
+    const int64_t j0 = j * nc, nj = std::min<int64_t>(nc, d.n - j0);
+    if (read_c) GK_CUDA_CHECK(copy_block(c_dev, c_host, d.ldc, es_c, i0, mi, j0, nj, cudaMemcpyHostToDevice, h->copy_in));
+    GK_CUDA_CHECK(cudaEventRecord(h->events[ev], h->copy_in));
+    GK_CUDA_CHECK(cudaStreamWaitEvent(st, h->events[ev], 0));
+    ++ev;
+    gk_gemm_desc blk = d;
+    blk.m = mi; blk.n = nj;
+    if (epi && epi->bias_axis != GK_BIAS_NONE)
+      epi_blk.bias = static_cast<const float*>(h->stage_dev[4]) + (epi->bias_axis == GK_BIAS_ROW ? i0 : j0);
+    const size_t a_off = (d.trans_a ? static_cast<size_t>(i0) * d.lda : static_cast<size_t>(i0)) * es_a;
+    const size_t b_off = (d.trans_b ? static_cast<size_t>(j0) : static_cast<size_t>(j0) * d.ldb) * es_b;
+    const size_t c_off = (static_cast<size_t>(j0) * d.ldc + i0) * es_c;
+    const size_t d_off = (static_cast<size_t>(j0) * d.ldd + i0) * es_d;
+    const gk_status s = gk_gemm(h, &blk, a_dev + a_off, b_dev + b_off, read_c ? c_dev + c_off : nullptr, d_dev + d_off,
+                                epi ? &epi_blk : nullptr, nullptr, st);
+    if (s != GK_OK) return s;
+    GK_CUDA_CHECK(cudaEventRecord(h->events[ev], st));
+    GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_out, h->events[ev], 0));
+    ++ev;
+    GK_CUDA_CHECK(copy_block(d_host, d_dev, d.ldd, es_d, i0, mi, j0, nj, cudaMemcpyDeviceToHost, h->copy_out));
+    return GK_OK;
+  };
+  // Chunks go up alternately (A_0 B_0 B_1 A_1 B_2 A_2 ...): with a rows of A and b columns of B on the
+  // device a*b blocks can be done, so growing both together releases blocks soonest and leaves the
+  // smallest batch of blocks behind the last chunk.
+  gk_status s = GK_OK;
+  auto fail = [&](gk_status code) {
+    cudaStreamSynchronize(h->copy_in); cudaStreamSynchronize(st); cudaStreamSynchronize(h->copy_out);
+    return code;
+  };
+  GK_CUDA_CHECK(load_a(0));
+  GK_CUDA_CHECK(load_b(0));
+  if ((s = block(0, 0)) != GK_OK) return fail(s);
+  for (int step = 1; step < std::max(R, Cn); ++step) {
+    if (step < Cn) {
+      GK_CUDA_CHECK(load_b(step));
+      for (int i = 0; i < std::min(step, R); ++i)
+        if ((s = block(i, step)) != GK_OK) return fail(s);
+    }
+    if (step < R) {
+      GK_CUDA_CHECK(load_a(step));
+      for (int j = 0; j <= std::min(step, Cn - 1); ++j)
+        if ((s = block(step, j)) != GK_OK) return fail(s);
+    }
+  }
+  GK_CUDA_CHECK(cudaEventRecord(h->events[ev], h->copy_out));
+  GK_CUDA_CHECK(cudaStreamWaitEvent(st, h->events[ev], 0));
+  GK_CUDA_CHECK(cudaStreamSynchronize(st));
+  return GK_OK;
+}
+
 gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host, const void* b_host,
                        const void* c_host, void* d_host, const gk_epilogue_desc* epi,
                        gk_stream stream) {
@@ -481,6 +602,14 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
   const size_t need[5] = {a_bytes, b_bytes, c_bytes, d_bytes, bias_bytes};
   for (int i = 0; i < 5; ++i)
     if (need[i] && (s = stage_reserve(h, i, need[i])) != GK_OK) return s;
+  if (d.number == GK_REAL && read_ab && d.m > 0 && d.n > 0 && d.k > 0 && a_bytes + b_bytes + d_bytes >= (64u << 20)) {
+    s = gemm_host_pipelined(h, d, a_host, b_host, c_host, d_host, epi, read_c, a_bytes, b_bytes, st);
+    if (s == GK_OK) {
+      int32_t code = 0;
+      return gk_poll_status(h, &code);
+    }
+    if (s != GK_ERR_UNSUPPORTED) return s;
+  }
   if (a_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[0], a_host, a_bytes, cudaMemcpyHostToDevice, st));
   if (b_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[1], b_host, b_bytes, cudaMemcpyHostToDevice, st));
   if (c_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[2], c_host, c_bytes, cudaMemcpyHostToDevice, st));

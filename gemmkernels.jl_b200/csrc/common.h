@@ -8,6 +8,7 @@
 
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/gemmkernels_b200.h"
 
@@ -69,4 +70,7 @@ struct gk_handle_s {
   // staging buffers of gk_gemm_host (grown on demand, freed by gk_destroy)
   void* stage_dev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, D, bias
   size_t stage_bytes[5] = {0, 0, 0, 0, 0};
+  // copy streams and events of the pipelined gk_gemm_host (created on first use)
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  std::vector<cudaEvent_t> events;
 };
