@@ -516,12 +516,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)
         const uint32_t t_col = t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c);
-        if (!(p.debug & 64)) {
 #pragma unroll
-          for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_col + pl * p.bn, v[pl]);
-          tmem_ld_wait();
-        }
-        if (p.debug & 32) continue;
+        for (int pl = 0; pl < PLANES; ++pl) tmem_ld_32x32(t_col + pl * p.bn, v[pl]);
+        tmem_ld_wait();
         const int ncols = p.N - (n0 + c);  // columns of this chunk inside the matrix (may be <= 0)
         if (!m_ok || ncols <= 0) continue;
         const int n_in = (n0 + c) % p.n_div, n_out = (n0 + c) / p.n_div;  // a chunk never straddles n_div

@@ -119,7 +119,9 @@ typedef struct gk_gemm_desc {
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t raster_group; /* T of the tiled rasters */
   int32_t max_ctas;     /* cap on the persistent grid */
-  int32_t reserved[3];
+  int32_t reserved[3];  /* [0]: diagnostic bits, 0 in production (1 no TMA, 2 no MMA, 4 idle producers: lets the
+                           bounded waits run out, 8 per-role cycle counters into the workspace, 16 progress
+                           marks for gk_debug_marks); [1]: gk_gemm_host chunk size in MiB (0 = 32); [2]: 0 */
 } gk_gemm_desc;
 
 typedef struct gk_epilogue_desc {
