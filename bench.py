@@ -120,7 +120,19 @@ class ClockSampler:
             import pynvml
             pynvml.nvmlInit()
             self.nv = pynvml
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.h = None
+            try:
+                # NVML numbers all GPUs of the machine; CUDA only the visible ones: match by UUID
+                import torch
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+                try:
+                    self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+                except Exception:
+                    self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = None
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self.nv = None
