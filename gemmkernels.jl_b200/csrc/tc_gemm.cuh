@@ -145,39 +145,84 @@ __device__ __forceinline__ float tc_activation(float v, int32_t act) {
 // Epilogue of one full 32-column chunk with the element types fixed at compile time (DTC < 0: no C
 // operand).  All loads of C are issued before the first use, so their latencies overlap; the
 // arithmetic is the same expression, in the same order, as the element-wise path for ragged chunks.
+template <int DT> struct TcElem { using type = float; };
+template <> struct TcElem<TC_F16> { using type = __half; };
+template <> struct TcElem<TC_BF16> { using type = __nv_bfloat16; };
+__device__ __forceinline__ float tc_to_float(float x) { return x; }
+__device__ __forceinline__ float tc_to_float(__half x) { return __half2float(x); }
+__device__ __forceinline__ float tc_to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T tc_from_float(float x);
+template <> __device__ __forceinline__ float tc_from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half tc_from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 tc_from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
 template <int PLANES, int DTC, int DTD>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint32_t (&v)[PLANES][32], int64_t ci,
                                                   int64_t di, float bias_row, int col0) {
+  // The work is arranged as passes over the 32 register values, each pass a straight run of one kind
+  // of instruction with its warp-uniform decision taken once per chunk, not once per element.
+  using TC = typename TcElem<(DTC >= 0 ? DTC : TC_F32)>::type;
+  using TD = typename TcElem<DTD>::type;
   const bool c_pairs = PLANES == 2 && p.c_plane == 0;
   const bool d_pairs = PLANES == 2 && p.d_plane == 0;
-  float cv[PLANES][32];
+  float x[PLANES][32];
   if constexpr (DTC >= 0) {
+    TC cv[PLANES][32];
 #pragma unroll
     for (int pl = 0; pl < PLANES; ++pl) {
-      const int64_t base = c_pairs ? 2 * ci + pl : pl * p.c_plane + ci;
+      const TC* cp = static_cast<const TC*>(p.C) + (c_pairs ? 2 * ci + pl : pl * p.c_plane + ci);
       const int64_t step = c_pairs ? 2 * p.c_sn0 : p.c_sn0;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) cv[pl][j] = tc_load_elem(p.C, base + j * step, DTC);
+      for (int j = 0; j < 32; ++j) cv[pl][j] = cp[j * step];
     }
-  }
-  const float* bias_col = p.bias_axis == TC_BIAS_COL ? p.bias + col0 : nullptr;
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const float bias = bias_col ? bias_col[j] : bias_row;
-    float out[PLANES];
 #pragma unroll
     for (int pl = 0; pl < PLANES; ++pl) {
-      float x = p.alpha * __uint_as_float(v[pl][j]);
-      if constexpr (DTC >= 0) x += p.beta * cv[pl][j];
-      if (pl == 0) x += bias;
-      out[pl] = tc_activation(x, p.act);
-    }
-    const int64_t dj = di + j * p.d_sn0;
-    if (DTD == TC_F32 && d_pairs) {
-      reinterpret_cast<float2*>(p.D)[dj] = make_float2(out[0], out[PLANES - 1]);
-    } else {
 #pragma unroll
-      for (int pl = 0; pl < PLANES; ++pl) tc_store_elem(p.D, d_pairs ? 2 * dj + pl : pl * p.d_plane + dj, DTD, out[pl]);
+      for (int j = 0; j < 32; ++j) {
+        float t = p.alpha * __uint_as_float(v[pl][j]);
+        t += p.beta * tc_to_float(cv[pl][j]);
+        x[pl][j] = t;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[pl][j] = p.alpha * __uint_as_float(v[pl][j]);
+    }
+  }
+  if (p.bias_axis == TC_BIAS_COL) {
+    const float* bias_col = p.bias + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[0][j] += bias_col[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[0][j] += bias_row;
+  }
+  if (p.act == TC_ACT_RELU) {
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[pl][j] = fmaxf(x[pl][j], 0.0f);
+    }
+  } else if (p.act == TC_ACT_GELU) {
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[pl][j] = tc_activation(x[pl][j], TC_ACT_GELU);
+    }
+  }
+  if (DTD == TC_F32 && d_pairs) {
+    float2* dp = reinterpret_cast<float2*>(p.D) + di;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dp[j * p.d_sn0] = make_float2(x[0][j], x[PLANES - 1][j]);
+  } else {
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+      TD* dp = static_cast<TD*>(p.D) + (d_pairs ? 2 * di + pl : pl * p.d_plane + di);
+      const int64_t step = d_pairs ? 2 * p.d_sn0 : p.d_sn0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dp[j * step] = tc_from_float<TD>(x[pl][j]);
     }
   }
 }
@@ -487,6 +532,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     const bool fast_store = PLANES == 1 && p.dtype_d == TC_F32 && p.beta == 0.0f &&
                             p.bias_axis != TC_BIAS_COL && p.act != TC_ACT_GELU;
     const bool has_c = p.beta != 0.0f;
+    // plain matrices only (a contraction's C is addressed through two-level strides), planar or real
+    const bool prefetch_c = has_c && p.m_div >= p.M && p.n_div >= p.N && p.c_sm0 == 1 && (PLANES == 1 || p.c_plane != 0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;
       tc_tile_coords(p, t, tm, tn);
@@ -494,6 +541,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const int n0 = tn * bn_tile;
       const uint32_t as = two_acc ? (acc_it & 1u) : 0u;
       const uint32_t aph = (two_acc ? (acc_it >> 1) : acc_it) & 1u;
+      if (prefetch_c) {
+        // While the main loop of this tile runs, pull the tile's part of C into L2: one request per
+        // 128-byte line (this warp's 32 rows of one column), columns dealt out to the lanes.
+        const int m0 = m - lane;
+        if (m0 < p.M) {
+          const size_t es_c = p.dtype_c == TC_F32 ? 4 : 2;
+          const char* c_line = static_cast<const char*>(p.C) + static_cast<size_t>(m0) * es_c;
+          for (int c = lane; c < bn_tile && n0 + c < p.N; c += 32) {
+#pragma unroll
+            for (int pl = 0; pl < PLANES; ++pl)
+              prefetch_l2(c_line + (static_cast<size_t>(pl) * p.c_plane + static_cast<size_t>(n0 + c) * p.c_sn0) * es_c);
+          }
+        }
+      }
       // all-or-nothing per warp: the TMEM loads below are warp-collective
       const long long e0 = (p.debug & 8) ? clock64() : 0;
       const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);

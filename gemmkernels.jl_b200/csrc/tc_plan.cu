@@ -201,7 +201,12 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
     const int64_t waves = (tm * tn + slots - 1) / slots;
     // a single accumulator stage exposes the epilogue: worth it only when the main loop is long
     double eff = c.eff;
-    if (c.n_sub * planes * c.bn > 256) eff = pr.K >= 1024 ? kWideEff : 0.5;
+    if (c.n_sub * planes * c.bn > 256) {
+      // an epilogue that also reads C (or writes through the general path) is several times
+      // longer; exposed, it eats the gain
+      const bool light = pr.C == nullptr || pr.beta == 0.0;
+      eff = pr.K >= 1024 ? (light ? kWideEff : 0.85) : 0.5;
+    }
     const double t = static_cast<double>(waves) * c.bn * c.n_sub / eff;
     if (t < best) { best = t; bcg = c.cg; bbn = c.bn; bns = c.n_sub; }
   }
