@@ -374,7 +374,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     tc_problem_from_gemm(*desc, epi, nullptr, nullptr, nullptr, nullptr, &pr);
     s = tc_plan(h, pr, false, &L);
     if (s != GK_OK) return s;
-    plan->grid = L.grid; plan->block = kTcThreads; plan->cluster = L.cg;
+    plan->grid = L.grid; plan->block = tc_threads(L.planes); plan->cluster = L.cg;
     plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;

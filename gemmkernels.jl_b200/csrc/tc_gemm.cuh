@@ -24,7 +24,11 @@
 
 namespace gk {
 
-constexpr int kTcThreads = 256;
+// 4 role warps + the epilogue warps: 8 of them for the one-plane kernels (two per TMEM lane quarter,
+// taking alternate 32-column chunks), 4 for the two-plane kernels, whose epilogue needs more
+// registers per thread than a 384-thread CTA leaves.
+__host__ __device__ constexpr int tc_epilogue_warps(int planes) { return planes == 1 ? 8 : 4; }
+__host__ __device__ constexpr int tc_threads(int planes) { return 128 + 32 * tc_epilogue_warps(planes); }
 constexpr int kTcTileM = 128;              // rows per CTA (TMEM lanes)
 constexpr int kTcKBytes = 128;             // bytes of K per k-block row (= swizzle span)
 constexpr int kTcMmaPerKBlock = 4;         // each MMA consumes 32 bytes of K
@@ -241,7 +245,7 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm
 }
 
 template <int CG, int PLANES, bool TF32, bool RANK5>
-__global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+__global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes and the pattern is a function of the address.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8u * a, 1);
-      mbar_init(bar_tempty + 8u * a, 4 * CG);  // one arrival per epilogue warp per CTA
+      mbar_init(bar_tempty + 8u * a, tc_epilogue_warps(PLANES) * CG);  // one arrival per epilogue warp per CTA
     }
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -525,7 +529,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int chunk_step = 32 * (tc_epilogue_warps(PLANES) / 4);
+    const int chunk_first = 32 * ((warp - 4) >> 2);
     const uint32_t tempty_leader = (CG == 2) ? map_to_cta(bar_tempty, 0) : bar_tempty;
     uint32_t acc_it = 0;
     bool ok = true;
@@ -548,7 +554,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
         if (m0 < p.M) {
           const size_t es_c = p.dtype_c == TC_F32 ? 4 : 2;
           const char* c_line = static_cast<const char*>(p.C) + static_cast<size_t>(m0) * es_c;
-          for (int c = lane; c < bn_tile && n0 + c < p.N; c += 32) {
+          for (int c = lane + chunk_first; c < bn_tile && n0 + c < p.N; c += chunk_step) {
 #pragma unroll
             for (int pl = 0; pl < PLANES; ++pl)
               prefetch_l2(c_line + (static_cast<size_t>(pl) * p.c_plane + static_cast<size_t>(n0 + c) * p.c_sn0) * es_c);
@@ -573,7 +579,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_gemm_kernel(const __grid_con
       const int m_in = m % p.m_div, m_out = m / p.m_div;
       const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1;
-      for (int c = 0; c < bn_tile; c += 32) {
+      for (int c = chunk_first; c < bn_tile; c += chunk_step) {
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)
         const uint32_t t_col = t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c);

@@ -469,7 +469,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
       if (cached == 0) {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * (h->sm_count / 2));
-        cfg.blockDim = dim3(kTcThreads);
+        cfg.blockDim = dim3(tc_threads(planes));
         cfg.dynamicSmemBytes = kSmemBudget;
         cudaLaunchAttribute at{};
         at.id = cudaLaunchAttributeClusterDimension;
@@ -505,7 +505,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
 gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(L.grid);
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(tc_threads(L.planes));
   cfg.dynamicSmemBytes = L.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute at{};
