@@ -448,9 +448,18 @@ def run_side(args):
     elif bound == "hbm":
         peak, src = peaks["hbm_gbs"], f"{peaks['source']} copy bandwidth"
     else:
+        import ctypes as C
+        from gemmkernels_b200 import _lib as L
         sm = torch.cuda.get_device_properties(0).multi_processor_count
         mhz = clocks.get("sm_max_mhz") or 1965
-        peak, src = sm * 128 * 2 * mhz * 1e6 / 1e12, f"nominal: {sm} SMs x 128 FMA lanes x 2 x {mhz} MHz"
+        nominal = sm * 128 * 2 * mhz * 1e6 / 1e12
+        measured = C.c_double(0.0)
+        st = L.lib.gk_measure_fp32_fma(GK.handle(0), C.byref(measured), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if st != 0:
+            raise SystemExit(f"FMA peak measurement failed: {L.lib.gk_last_error_message()}")
+        peak = measured.value
+        src = (f"measured here: register-only packed-FMA kernel (gk_measure_fp32_fma); "
+               f"nominal {nominal:.1f} = {sm} SMs x 128 FMA lanes x 2 x {mhz} MHz")
     print(json.dumps({
         "metric": f"{unit} ({name})", "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

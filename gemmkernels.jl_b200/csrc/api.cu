@@ -276,6 +276,24 @@ static gk_status launch_simt(const gk_gemm_desc& d, const gk_epilogue_desc* epi,
 
 using namespace gk;
 
+// Register-only FP32 FMA throughput probe: kFmaPeakChains independent packed-FMA chains per thread.
+constexpr int kFmaPeakChains = 16;
+__global__ void __launch_bounds__(256) fma_peak_kernel(float* sink, int iters, float seed) {
+  float2 acc[kFmaPeakChains];
+#pragma unroll
+  for (int i = 0; i < kFmaPeakChains; ++i) acc[i] = make_float2(seed + i, seed - i);
+  const float2 a = make_float2(1.0f + 1e-7f * threadIdx.x, 1.0f - 1e-7f * threadIdx.x);
+  const float2 b = make_float2(1e-9f, -1e-9f);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int i = 0; i < kFmaPeakChains; ++i) acc[i] = __ffma2_rn(acc[i], a, b);
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kFmaPeakChains; ++i) s += acc[i].x + acc[i].y;
+  if (s == 12345.678f) *sink = s;   // keeps the chains alive; practically never true
+}
+
 extern "C" {
 
 int32_t gk_version(void) { return GK_VERSION_MAJOR * 1000 + GK_VERSION_MINOR; }
@@ -348,6 +366,37 @@ gk_status gk_debug_marks(gk_handle h, int32_t* out16) {
   clear_error();
   if (!h || !out16) return set_error(GK_ERR_INVALID_ARGUMENT, "handle or output is NULL");
   for (int i = 0; i < 16; ++i) out16[i] = reinterpret_cast<volatile int32_t*>(h->status_host)[i];
+  return GK_OK;
+}
+
+gk_status gk_measure_fp32_fma(gk_handle h, double* tflops, gk_stream stream) {
+  clear_error();
+  if (!h || !tflops) return set_error(GK_ERR_INVALID_ARGUMENT, "handle or output is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* sink = nullptr;
+  GK_CUDA_CHECK(cudaMalloc(&sink, sizeof(float)));
+  cudaEvent_t e0, e1;
+  GK_CUDA_CHECK(cudaEventCreate(&e0));
+  GK_CUDA_CHECK(cudaEventCreate(&e1));
+  const int blocks = h->sm_count * 8, threads = 256, iters = 4096;
+  fma_peak_kernel<<<blocks, threads, 0, st>>>(sink, iters, 1.0f);   // warm-up (clocks, instruction cache)
+  double best_ms = 1e30;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(e0, st);
+    fma_peak_kernel<<<blocks, threads, 0, st>>>(sink, iters, 1.0f);
+    cudaEventRecord(e1, st);
+    cudaError_t e = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    if (e != cudaSuccess) {
+      cudaEventDestroy(e0); cudaEventDestroy(e1); cudaFree(sink);
+      return set_error(GK_ERR_CUDA, "FMA measurement failed: %s", cudaGetErrorString(e));
+    }
+    best_ms = std::min(best_ms, static_cast<double>(ms));
+  }
+  cudaEventDestroy(e0); cudaEventDestroy(e1); cudaFree(sink);
+  const double fmas = static_cast<double>(blocks) * threads * iters * kFmaPeakChains * 2;   // 2 lanes per packed FMA
+  *tflops = 2.0 * fmas / (best_ms * 1e-3) / 1e12;
   return GK_OK;
 }
 

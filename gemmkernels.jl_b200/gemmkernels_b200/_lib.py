@@ -26,7 +26,7 @@ GK_RASTER_AUTO, GK_RASTER_IDENTITY, GK_RASTER_HORIZONTAL, GK_RASTER_VERTICAL, GK
 
 EXPORTS = (
     "gk_version", "gk_last_error_message", "gk_create", "gk_destroy", "gk_poll_status",
-    "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks",
+    "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks", "gk_measure_fp32_fma",
     "gk_contract_static",
 )
 GK_MAX_MODES = 8
@@ -119,6 +119,8 @@ def _load() -> C.CDLL:
     lib.gk_gemm_host.restype = C.c_int
     lib.gk_gemm_host.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p]
+    lib.gk_measure_fp32_fma.restype = C.c_int
+    lib.gk_measure_fp32_fma.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.c_void_p]
     lib.gk_debug_marks.restype = C.c_int
     lib.gk_debug_marks.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
     lib.gk_contract_query.restype = C.c_int

@@ -161,6 +161,12 @@ GK_API gk_status gk_poll_status(gk_handle h, int32_t* raw_code);
  * (how far each role got).  Reads host memory only: usable even after the context has failed. */
 GK_API gk_status gk_debug_marks(gk_handle h, int32_t* out16);
 
+/* Measures what the FP32 FMA pipe of this GPU sustains: a register-only kernel of independent packed
+ * FMA chains on every SM, timed with CUDA events on `stream` (synchronises it).  *tflops gets
+ * 2 flop per FMA / time.  The denominator for rooflines of the FPU operator, for which no library
+ * GEMM figure exists.  No counterpart in the reference. */
+GK_API gk_status gk_measure_fp32_fma(gk_handle h, double* tflops, gk_stream stream);
+
 /* Fills *plan with what gk_gemm would launch for this descriptor; launches nothing. */
 GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
                         gk_gemm_plan* plan);

@@ -328,6 +328,17 @@ def test_beta_with_aliased_c_and_d_and_fp16_output():
     assert O.isapprox_elementwise(want, GK.to_numpy(c), "Float16")
 
 
+def test_fp32_fma_rate_measurement_is_plausible():
+    """gk_measure_fp32_fma: between half of and a little above the nominal 148 x 128 x 2 x clock."""
+    import ctypes as C
+    from gemmkernels_b200 import _lib as L
+    out = C.c_double(0.0)
+    assert L.lib.gk_measure_fp32_fma(GK.handle(), C.byref(out), C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    props = torch.cuda.get_device_properties(0)
+    nominal = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    assert 0.5 * nominal < out.value < 1.1 * nominal, out.value
+
+
 def test_bound_matmul_replays_the_same_gemm():
     """GK.bind lowers once; each call of the object enqueues the same GEMM (here in place: D = A*B + D)."""
     rng = np.random.default_rng(22)
