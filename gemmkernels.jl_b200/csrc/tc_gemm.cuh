@@ -59,7 +59,9 @@ struct TcParams {
   int32_t M, N, K;
   int32_t tiles_m, tiles_n;  // cluster tiles: (128*CG) x (n_sub*bn)
   int32_t k_blocks;
-  int32_t raster_group;      // cluster tiles along M walked before stepping along N
+  int32_t raster_group;      // cluster tiles along M (N for the horizontal raster) walked before stepping on
+  int32_t raster_kind;       // 0 = bands down M, 1 = bands along N, 2 = Z-order (power-of-two tile grids)
+  int32_t z_bits;            // Z-order: low bits interleaved per dimension (min of the two log2 extents)
   int32_t bn;                // columns per MMA (multiple of 32; per-CTA B rows = bn/CG)
   int32_t n_sub;             // a cluster tile is n_sub (1 or 2) such column blocks that share A
   int32_t acc_stages;        // accumulator stages in TMEM: 2, or 1 when one tile fills all 512 columns
@@ -231,17 +233,43 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint3
   }
 }
 
-// Cluster tile index -> (tile_m, tile_n): walk `raster_group` tiles down M, then step along N,
-// so that the tiles in flight at any time share A rows and B columns in L2.
+// Even-position bits of x packed together (bit 0, 2, 4, ... -> bit 0, 1, 2, ...).
+__device__ __forceinline__ uint32_t tc_even_bits(uint32_t x) {
+  x &= 0x55555555u;
+  x = (x | (x >> 1)) & 0x33333333u;
+  x = (x | (x >> 2)) & 0x0F0F0F0Fu;
+  x = (x | (x >> 4)) & 0x00FF00FFu;
+  x = (x | (x >> 8)) & 0x0000FFFFu;
+  return x;
+}
+
+// Cluster tile index -> (tile_m, tile_n).  Default: walk `raster_group` tiles down M, then step along
+// N, so that the tiles in flight at any time share A rows and B columns in L2 (the reference's
+// VerticallyTiled{T} grouping); kind 1 swaps the roles of M and N (HorizontallyTiled{T}); kind 2 is
+// the Z-order curve of LebesgueCurve (M takes the even bits), the excess of the longer dimension
+// continuing in its high bits.
 __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm, int& tn) {
+  if (p.raster_kind == 2) {
+    const uint32_t low = static_cast<uint32_t>(t) & ((1u << (2 * p.z_bits)) - 1u);
+    const int rest = t >> (2 * p.z_bits);
+    tm = static_cast<int>(tc_even_bits(low));
+    tn = static_cast<int>(tc_even_bits(low >> 1));
+    if (p.tiles_m >= p.tiles_n) tm += rest << p.z_bits;
+    else tn += rest << p.z_bits;
+    return;
+  }
+  const bool along_n = p.raster_kind == 1;
+  const int major = along_n ? p.tiles_n : p.tiles_m;   // the dimension the bands cut
+  const int minor = along_n ? p.tiles_m : p.tiles_n;
   const int g = p.raster_group;
-  const int band = g * p.tiles_n;
+  const int band = g * minor;
   const int band_id = t / band;
-  const int first_m = band_id * g;
-  const int rows = min(g, p.tiles_m - first_m);
+  const int first = band_id * g;
+  const int rows = min(g, major - first);
   const int r = t - band_id * band;
-  tm = first_m + r % rows;
-  tn = r / rows;
+  const int a = first + r % rows, b = r / rows;
+  tm = along_n ? b : a;
+  tn = along_n ? a : b;
 }
 
 template <int CG, int PLANES, bool TF32, bool RANK5>

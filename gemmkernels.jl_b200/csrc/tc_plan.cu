@@ -418,6 +418,16 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   if (group <= 0)
     group = static_cast<int>(std::lround(std::sqrt(static_cast<double>(slots_guess) * bn * n_sub / (kTcTileM * cg))));
   p.raster_group = std::max(1, std::min(group, p.tiles_m));
+  p.raster_kind = 0;
+  if (pr.raster == GK_RASTER_HORIZONTAL) {
+    p.raster_kind = 1;
+    p.raster_group = std::max(1, std::min(pr.raster_group > 0 ? pr.raster_group : group, p.tiles_n));
+  } else if (pr.raster == GK_RASTER_LEBESGUE) {
+    // the Z-order curve needs power-of-two extents in tiles; other grids keep the band raster
+    auto log2_exact = [](int x) { int b = 0; while ((1 << b) < x) ++b; return (1 << b) == x ? b : -1; };
+    const int bm = log2_exact(p.tiles_m), bnn = log2_exact(p.tiles_n);
+    if (bm >= 0 && bnn >= 0) { p.raster_kind = 2; p.z_bits = std::min(bm, bnn); }
+  }
 
   // epilogue
   if (pr.n_ext0 < pr.N && pr.n_ext0 % 32 != 0)

@@ -51,16 +51,43 @@ def number_of_blocks(swizzle, block_shape, matmul_shape):
     return (_cld(matmul_shape["M"], block_shape["M"]), _cld(matmul_shape["N"], block_shape["N"]))
 
 
+def _even_bits(x: int) -> int:
+    out, bit = 0, 0
+    while x:
+        out |= (x & 1) << bit
+        x >>= 2
+        bit += 1
+    return out
+
+
+def tile_of(swizzle, t: int, tiles_m: int, tiles_n: int, group: int = 0):
+    """(tile_m, tile_n) the persistent scheduler visits at step t: the host mirror of the kernel's
+    tile walk.  Tiled swizzles walk bands of T tiles (down M for VerticallyTiled and by default, along
+    N for HorizontallyTiled); LebesgueCurve follows the Z-order curve (M takes the even bits,
+    src/cta-swizzle.jl:155-158) on power-of-two grids and the default bands elsewhere."""
+    pow2 = lambda x: x > 0 and x & (x - 1) == 0
+    if isinstance(swizzle, LebesgueCurve) and pow2(tiles_m) and pow2(tiles_n):
+        zb = min(tiles_m.bit_length(), tiles_n.bit_length()) - 1
+        low, rest = t & ((1 << (2 * zb)) - 1), t >> (2 * zb)
+        tm, tn = _even_bits(low), _even_bits(low >> 1)
+        return (tm + (rest << zb), tn) if tiles_m >= tiles_n else (tm, tn + (rest << zb))
+    along_n = isinstance(swizzle, HorizontallyTiled)
+    major, minor = (tiles_n, tiles_m) if along_n else (tiles_m, tiles_n)
+    g = major if isinstance(swizzle, Identity) else (getattr(swizzle, "tile", 0) or group or 8)
+    g = max(1, min(g, major))
+    band = g * minor
+    band_id = t // band
+    first = band_id * g
+    rows = min(g, major - first)
+    r = t - band_id * band
+    a, b = first + r % rows, r // rows
+    return (b, a) if along_n else (a, b)
+
+
 def visualise_cta_swizzle(swizzle, tiles_m: int, tiles_n: int):
     """tiles_m x tiles_n table of the order in which the persistent scheduler visits tiles."""
-    group = tiles_m if isinstance(swizzle, Identity) else (getattr(swizzle, "tile", 0) or 8)
-    group = max(1, min(group, tiles_m))
-    order = [[0] * tiles_n for _ in range(tiles_m)]
+    order = [[-1] * tiles_n for _ in range(tiles_m)]
     for t in range(tiles_m * tiles_n):
-        band = group * tiles_n
-        band_id = t // band
-        first_m = band_id * group
-        rows = min(group, tiles_m - first_m)
-        r = t - band_id * band
-        order[first_m + r % rows][r // rows] = t
+        tm, tn = tile_of(swizzle, t, tiles_m, tiles_n)
+        order[tm][tn] = t
     return order

@@ -169,9 +169,12 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
     sw = conf.cta_swizzle
     if isinstance(sw, (CTASwizzle.HorizontallyTiled, CTASwizzle.VerticallyTiled)):
         desc.raster, desc.raster_group = sw.raster, sw.tile
+    elif isinstance(sw, CTASwizzle.LebesgueCurve):
+        desc.raster, desc.raster_group = sw.raster, conf.raster_group
     else:
-        # Identity / LebesgueCurve only fix the order of block indices in the reference; which tiles
-        # run together is up to the scheduler there too, so the engine keeps its own raster.
+        # Identity only fixes the order of block indices in the reference (it is the default of every
+        # configuration); which tiles run together is up to the hardware scheduler there, so the
+        # persistent scheduler keeps its own band raster.
         desc.raster, desc.raster_group = L.GK_RASTER_AUTO, conf.raster_group
 
     def operand(arr, layout, rows, cols, name):

@@ -70,7 +70,8 @@ op_kind(::Type{<:Operator.FPUOp{M, N, K, mb, nb, kb, CT, AT}}) where {M, N, K, m
 layout_kind(l) = Layout.is_zero(l) ? Int32(1) : Layout.is_diagonal(l) ? Int32(2) : Int32(0)
 raster(::Type{CTASwizzle.HorizontallyTiled{T}}) where {T} = (Int32(2), Int32(T))
 raster(::Type{CTASwizzle.VerticallyTiled{T}}) where {T} = (Int32(3), Int32(T))
-raster(::Type) = (Int32(0), Int32(0))     # Identity / LebesgueCurve: the scheduler keeps its own raster
+raster(::Type{CTASwizzle.LebesgueCurve}) = (Int32(4), Int32(0))
+raster(::Type) = (Int32(0), Int32(0))     # Identity: the persistent scheduler keeps its own band raster
 
 # Folding of the eight hooks (src/matmul.jl:8-15) into alpha, beta and an activation.  Net math of the
 # reference: D = g_d( r_d( sum s_a(g_a(A)) s_b(g_b(B)) + s_c(g_c(C)) ) + bias ).

@@ -16,7 +16,7 @@ import pytest
 import torch
 
 import gemmkernels_b200 as GK
-from gemmkernels_b200 import _lib as L
+from gemmkernels_b200 import CTASwizzle, _lib as L
 from gemmkernels_b200 import Epilogue, Kernel, Layout, Operator, Transform
 from oracle import gemm_oracle as O
 
@@ -261,6 +261,22 @@ def test_tile_shapes_and_transposes_exact(ta, tb, cg, bn):
                la=la, lb=lb, lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32],
                block_shape=(128, 128, 64), cta_group=cg, tile_n=bn)
     assert np.array_equal(GK.to_numpy(d), O.gemm(A, B, trans_a=bool(ta), trans_b=bool(tb)))
+
+
+@pytest.mark.parametrize("swizzle", [CTASwizzle.Identity(), CTASwizzle.HorizontallyTiled[2], CTASwizzle.HorizontallyTiled[8],
+                                     CTASwizzle.VerticallyTiled[3], CTASwizzle.LebesgueCurve()])
+@pytest.mark.parametrize("M,N", [(2048, 2048), (1024, 4096), (1400, 900)])
+def test_every_cta_swizzle_visits_every_tile(swizzle, M, N):
+    """The raster only changes the order of tiles: results are identical, and exact on integers.
+    2048 x 2048 and 1024 x 4096 are power-of-two tile grids (the Z-order walk), 1400 x 900 is not."""
+    rng = np.random.default_rng(M + N)
+    K = 192
+    A = rng.integers(-2, 3, (M, K)).astype(np.float16); B = rng.integers(-2, 3, (K, N)).astype(np.float16)
+    d = GK.cuarray(GK.Float32, M, N); d.fill_(-1.0)
+    run_matmul(dev(A), dev(B), None, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+               la=Layout.ColMajor[GK.Float16], lb=Layout.ColMajor[GK.Float16], lc=Layout.Zero[GK.Float32],
+               ld=Layout.ColMajor[GK.Float32], block_shape=(128, 128, 64), cta_swizzle=swizzle, tile_n=128, cta_group=1)
+    assert np.array_equal(GK.to_numpy(d), A.astype(np.float32) @ B.astype(np.float32))
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])

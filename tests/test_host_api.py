@@ -183,6 +183,30 @@ def test_swizzle_visualisation_covers_every_tile_once():
     assert CTASwizzle.number_of_blocks(CTASwizzle.Identity(), {"M": 128, "N": 128}, {"M": 1000, "N": 10}) == (8, 1)
 
 
+def test_every_swizzle_is_a_permutation_and_lebesgue_follows_the_z_curve():
+    for sw in (CTASwizzle.Identity(), CTASwizzle.HorizontallyTiled[4], CTASwizzle.VerticallyTiled[3], CTASwizzle.LebesgueCurve()):
+        for tm, tn in ((10, 7), (8, 8), (16, 4), (4, 32), (1, 5)):
+            order = CTASwizzle.visualise_cta_swizzle(sw, tm, tn)
+            assert sorted(v for row in order for v in row) == list(range(tm * tn)), (sw, tm, tn)
+    # HorizontallyTiled{4}: four tiles along N, then the next row (src/cta-swizzle.jl:47-90)
+    h = CTASwizzle.visualise_cta_swizzle(CTASwizzle.HorizontallyTiled[4], 3, 8)
+    assert h[0][:5] == [0, 1, 2, 3, 12] and h[1][0] == 4
+    # LebesgueCurve on 8 x 8: the table of src/cta-swizzle.jl:134-143 (1-based there)
+    z = CTASwizzle.visualise_cta_swizzle(CTASwizzle.LebesgueCurve(), 8, 8)
+    assert [v + 1 for v in z[0]] == [1, 3, 9, 11, 33, 35, 41, 43]
+    assert [row[0] + 1 for row in z] == [1, 2, 5, 6, 17, 18, 21, 22]
+    # rectangular power-of-two grids: the square curve repeats along the longer side
+    r = CTASwizzle.visualise_cta_swizzle(CTASwizzle.LebesgueCurve(), 2, 8)
+    assert r[0] == [0, 2, 4, 6, 8, 10, 12, 14] and r[1][0] == 1
+    conf = GK.get_config(gemm_shape=(1024, 1024, 64), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=Layout.ColMajor[GK.Float16], global_c_layout=Layout.Zero[GK.Float32],
+                         global_d_layout=Layout.ColMajor[GK.Float32], cta_swizzle=CTASwizzle.LebesgueCurve())
+    a = torch.zeros(64, 1024, dtype=torch.float16).T; b = torch.zeros(1024, 64, dtype=torch.float16).T
+    d = torch.zeros(1024, 1024, dtype=torch.float32).T
+    desc, _, _ = GK.lower(conf, a, b, None, d, {}, Epilogue.Default(), Kernel.matmul_singlestage)
+    assert desc.raster == L.GK_RASTER_LEBESGUE
+
+
 def test_column_major_helpers_roundtrip():
     x = np.arange(12, dtype=np.float32).reshape(3, 4)
     t = GK.to_cuarray(x, device="cpu")
