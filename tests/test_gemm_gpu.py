@@ -419,6 +419,21 @@ def test_alpha_zero_and_k_zero_reduce_to_beta_c():
     assert np.allclose(GK.to_numpy(c), 0.5 * Cm, rtol=1e-6)
 
 
+@pytest.mark.parametrize("M,N,K", [(0, 8, 8), (8, 0, 8), (1, 1, 1), (1, 7, 3), (33, 1, 129), (2, 300, 1)])
+def test_empty_and_tiny_products(M, N, K):
+    """Empty outputs are a no-op; sizes far below a tile go through whichever kernel takes them."""
+    rng = np.random.default_rng(M * 100 + N * 10 + K)
+    A = rng.integers(-3, 4, (M, K)).astype(np.float16); B = rng.integers(-3, 4, (K, N)).astype(np.float16)
+    Cm = rng.integers(-3, 4, (M, N)).astype(np.float32)
+    c = dev(Cm) if M * N else GK.cuarray(GK.Float32, M, N)
+    out = GK.matmatmul_(c, "N", "N", dev(A) if M * K else GK.cuarray(GK.Float16, M, K),
+                        dev(B) if K * N else GK.cuarray(GK.Float16, K, N), 2.0, 1.0)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert out is c and tuple(c.shape) == (M, N)
+    if M * N:
+        assert np.array_equal(GK.to_numpy(c), 2.0 * (A.astype(np.float32) @ B.astype(np.float32)) + Cm)
+
+
 def test_unsupported_combinations_raise_config_error():
     a = GK.cuarray(GK.Float64, 128, 128); d = GK.cuarray(GK.Float64, 128, 128)
     conf = GK.get_config(gemm_shape=(128, 128, 128), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
