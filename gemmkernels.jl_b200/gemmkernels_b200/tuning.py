@@ -25,7 +25,7 @@ from dataclasses import asdict, dataclass
 from pathlib import Path
 from typing import Callable, Iterable, Iterator
 
-TILE_N = (64, 128, 192, 256)
+TILE_N = (64, 128, 192, 256, 512)   # 512 = two 256-column accumulators sharing each A stage (CTA pairs only)
 CTA_GROUP = (1, 2)
 STAGES = (0, 3, 4, 6)          # 0 = as many as shared memory holds
 RASTER_GROUP = (0, 4, 8, 16)   # 0 = built-in choice
@@ -63,9 +63,12 @@ def candidates(problem: Problem, tile_n=TILE_N, cta_group=CTA_GROUP, stages=STAG
     for tn, cg, st, rg in itertools.product(tile_n, cta_group, stages, raster_group):
         if cg == 2 and tn % 64:
             continue
+        if tn == 512 and cg != 2:
+            continue
         if tn > max(64, -(-problem.n // 32) * 32):        # wider than the whole matrix: a duplicate
             continue
         yield Candidate(tn, cg, st, rg)
+    yield Candidate(0, 0, 0, 0)                            # the built-in choice, for comparison
 
 
 # ------------------------------------------------------------------------------------------------
@@ -229,7 +232,7 @@ def _config(prob: Problem, cand: Candidate | None):
     extra = {} if cand is None else dict(tile_n=cand.tile_n, cta_group=cand.cta_group, stages=cand.stages,
                                          raster_group=cand.raster_group)
     return get_config(gemm_shape=dict(M=prob.m, N=prob.n, K=prob.k),
-                      operator=Operator.TCGen05Operator[et, eltypes.Float32],
+                      operator=Operator.TCGen05Operator[Operator.TF32 if prob.dtype == "TF32" else et, eltypes.Float32],
                       global_a_layout=la, global_b_layout=lb,
                       global_c_layout=(Layout.UnsafeAlignedColMajor if prob.with_c else Layout.Zero)[eltypes.Float32],
                       global_d_layout=Layout.UnsafeAlignedColMajor[eltypes.Float32], **extra)

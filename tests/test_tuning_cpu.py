@@ -13,9 +13,11 @@ def test_candidates_skip_refused_combinations():
     cs = list(T.candidates(p))
     assert len(set(c.key() for c in cs)) == len(cs)
     assert all(not (c.cta_group == 2 and c.tile_n % 64) for c in cs)
-    assert T.Candidate(256, 2, 0, 0) in cs
+    assert T.Candidate(256, 2, 0, 0) in cs and T.Candidate(512, 2, 0, 0) in cs
+    assert not any(c.tile_n == 512 and c.cta_group == 1 for c in cs)
+    assert cs[-1] == T.Candidate(0, 0, 0, 0)                # the built-in choice is measured too
     narrow = list(T.candidates(T.Problem(4096, 64, 4096)))
-    assert narrow and all(c.tile_n == 64 for c in narrow)
+    assert narrow and all(c.tile_n in (0, 64) for c in narrow)
 
 
 def test_resume_skips_measured_and_ignores_torn_lines(tmp_path):
