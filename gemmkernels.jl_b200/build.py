@@ -12,6 +12,7 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
@@ -19,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libgemmkernels_b200.so"
 
-SOURCES = ["api.cu", "tc_plan.cu", "contract.cu"]
+SOURCES = ["tc_kernels_rank3.cu", "tc_kernels_rank5.cu", "api.cu", "tc_plan.cu", "contract.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -52,8 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not _stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
-    objs = []
-    for src in SOURCES:
+    def compile_one(src: str) -> str:
         obj = LIB_DIR / (Path(src).stem + ".o")
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
@@ -61,7 +61,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             cmd.insert(2, "-v")
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
-        objs.append(str(obj))
+        return str(obj)
+
+    # the translation units are independent: compile them side by side
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
     cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", str(LIB_PATH), *objs,
            "-Xlinker", "--exclude-libs=ALL"]
     if verbose:

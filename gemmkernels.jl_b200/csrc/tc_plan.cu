@@ -136,20 +136,12 @@ static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op,
   return GK_OK;
 }
 
-template <int CG, int PLANES, bool TF32, bool RANK5>
-static const void* tc_kernel_ptr() {
-  return reinterpret_cast<const void*>(&tc_gemm_kernel<CG, PLANES, TF32, RANK5>);
-}
-
+// The kernel instances are compiled in two translation units of their own (tc_kernels_rank3.cu,
+// tc_kernels_rank5.cu), which is what makes the build parallel.
 template <bool RANK5>
-static const void* tc_kernel_select_r(int cg, int planes, bool tf32) {
-  if (cg == 1) {
-    if (planes == 1) return tf32 ? tc_kernel_ptr<1, 1, true, RANK5>() : tc_kernel_ptr<1, 1, false, RANK5>();
-    return tf32 ? tc_kernel_ptr<1, 2, true, RANK5>() : tc_kernel_ptr<1, 2, false, RANK5>();
-  }
-  if (planes == 1) return tf32 ? tc_kernel_ptr<2, 1, true, RANK5>() : tc_kernel_ptr<2, 1, false, RANK5>();
-  return tf32 ? tc_kernel_ptr<2, 2, true, RANK5>() : tc_kernel_ptr<2, 2, false, RANK5>();
-}
+const void* tc_kernel_select_r(int cg, int planes, bool tf32);
+extern template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32);
+extern template const void* tc_kernel_select_r<true>(int cg, int planes, bool tf32);
 
 static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5) {
   return rank5 ? tc_kernel_select_r<true>(cg, planes, tf32) : tc_kernel_select_r<false>(cg, planes, tf32);
