@@ -714,3 +714,59 @@ def test_zoo_bias(ta, tb, n):
                epilogue=Epilogue.Bias(dev(bias.reshape(-1))), block_shape=(128, 128, 64), kernel=Kernel.matmul_pipelined)
     want = O.gemm(A, B, Cm, 1.0, 1.0, bool(ta), bool(tb)) + bias
     assert O.isapprox_elementwise(want, GK.to_numpy(d), "Float16")
+
+
+# ------------------------------------------------------------------------------------------------
+# randomised sweep over shapes, transposes, types, tile overrides and epilogues
+# ------------------------------------------------------------------------------------------------
+def _fuzz_cases(n=48):
+    rng = np.random.default_rng(20240)
+    cases = []
+    for i in range(n):
+        M, N, K = (int(rng.choice([8, 40, 136, 264, 520, 1032, 1544])) + 8 * int(rng.integers(0, 16)) for _ in range(3))
+        cases.append(dict(i=i, M=M, N=N, K=K, ta=bool(rng.integers(2)), tb=bool(rng.integers(2)),
+                          ab=str(rng.choice(["Float16", "BFloat16", "TF32"])), cd=str(rng.choice(["Float32", "same"])),
+                          tile_n=int(rng.choice([0, 0, 64, 128, 256, 512])), cg=int(rng.choice([0, 1, 2])),
+                          beta=float(rng.choice([0.0, 1.0, -0.5])), alpha=float(rng.choice([1.0, 2.0, 0.25])),
+                          bias=str(rng.choice(["none", "row", "col"])), act=str(rng.choice(["none", "relu", "gelu"]))))
+    return cases
+
+
+@pytest.mark.parametrize("cs", _fuzz_cases(), ids=lambda c: f"{c['i']}-{c['M']}x{c['N']}x{c['K']}-{c['ab']}")
+def test_randomised_shapes_types_tiles_and_epilogues(cs):
+    rng = np.random.default_rng(1000 + cs["i"])
+    M, N, K, ta, tb = cs["M"], cs["N"], cs["K"], cs["ta"], cs["tb"]
+    tf32 = cs["ab"] == "TF32"
+    AB = GK.Float32 if tf32 else getattr(GK, cs["ab"])
+    CD = GK.Float32 if (cs["cd"] == "Float32" or tf32) else AB
+    # multiples of 1/8 in [-1, 1]: exact in every input type, so the only rounding is the output's
+    A = (rng.integers(-8, 9, (K, M) if ta else (M, K)) / 8).astype(np.float32)
+    B = (rng.integers(-8, 9, (N, K) if tb else (K, N)) / 8).astype(np.float32)
+    Cm = (rng.integers(-8, 9, (M, N)) / 8).astype(np.float32)
+    bias = (rng.integers(-8, 9, M if cs["bias"] == "row" else N) / 8).astype(np.float32) if cs["bias"] != "none" else None
+    if cs["tile_n"] == 512 and cs["cg"] == 1:
+        cs = dict(cs, cg=2)
+    kw = {}
+    if cs["tile_n"]:
+        kw["tile_n"] = cs["tile_n"]
+    if cs["cg"]:
+        kw["cta_group"] = cs["cg"]
+    la = (Layout.RowMajor if ta else Layout.ColMajor)[AB]; lb = (Layout.RowMajor if tb else Layout.ColMajor)[AB]
+    has_c = cs["beta"] != 0.0
+    c = dev(Cm, CD) if has_c else None
+    d = GK.cuarray(CD, M, N)
+    opct = Operator.TF32 if tf32 else AB
+    act = {"none": None, "relu": Transform.ReLU(), "gelu": Transform.GELU()}[cs["act"]]
+    epi = Epilogue.Bias(torch.from_numpy(bias).cuda(), axis=cs["bias"]) if bias is not None else None
+    try:
+        run_matmul(dev(A, AB), dev(B, AB), c, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[opct, GK.Float32], la=la, lb=lb,
+                   lc=(Layout.ColMajor if has_c else Layout.Zero)[CD], ld=Layout.ColMajor[CD],
+                   alpha=cs["alpha"], beta=cs["beta"] if has_c else 1.0, epilogue=epi, act=act, **kw)
+    except GK.ConfigError as e:
+        pytest.skip(f"engine refuses this combination, as the reference's tests allow: {e}")
+    want = cs["alpha"] * (( A.T if ta else A).astype(np.float64) @ (B.T if tb else B).astype(np.float64))
+    if has_c:
+        want = want + cs["beta"] * GK.to_numpy(c).astype(np.float64)
+    want = O.epilogue(want, bias, cs["bias"] if bias is not None else "col", None if cs["act"] == "none" else cs["act"])
+    tol = {"Float32": 2e-6, "Float16": 1e-3, "BFloat16": 8e-3}[CD.name]
+    assert O.normwise_error(GK.to_numpy(d).astype(np.float64), want) <= tol
