@@ -258,8 +258,10 @@ GK_API gk_status gk_contract_static(const gk_contract_desc* desc, const void* a,
  * `CuArray`s; the reference has no such method — CUDA.jl users would `CuArray(A)` first, which is
  * what this call does internally): copies a, b (and c, and the bias named by epi) to device
  * staging buffers kept in the handle, runs gk_gemm, copies D back to d_host and returns once
- * d_host is complete (it synchronises `stream`).  Pinned host memory makes the copies faster but
- * is not required.  Calls on one handle are serialised. */
+ * d_host is complete (it synchronises `stream`).  Large real products are cut into blocks (row chunks
+ * of A by column chunks of B) whose uploads, kernels and downloads overlap on two copy streams owned by
+ * the handle; small ones run copy, compute, copy on `stream`.  Pinned host memory makes the copies
+ * faster (and is what lets them overlap) but is not required.  Calls on one handle are serialised. */
 GK_API gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host,
                               const void* b_host, const void* c_host, void* d_host,
                               const gk_epilogue_desc* epi, gk_stream stream);
