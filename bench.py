@@ -286,13 +286,21 @@ def run_gpu(args):
 
     # end to end: same GEMM from pinned host buffers through gk_gemm_host (H2D of A and B, D2H of D
     # inside the timed region, every step)
+    if world > 1:
+        # sharded host path: rank 0 uploads A, NVLink carries it to the others, every rank uploads its own
+        # block of B and downloads its block of D
+        def e2e_step():
+            multigpu.colshard_matmul_host(conf, a_pin if rank == 0 else None, a, b_pin, d_pin, src=0, device_index=local)
+    else:
+        def e2e_step():
+            GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
     for _ in range(2):
-        GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
+        e2e_step()
     barrier()
     e2e_steps = min(args.steps, 100)   # ~10 ms per step over PCIe: bounded so the default run stays short
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
+        e2e_step()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
     if rank == 0:
@@ -300,7 +308,7 @@ def run_gpu(args):
         if not err <= 1e-3:
             raise SystemExit(f"end-to-end result is wrong: normwise error {err}")
     e2e_value = flops_total / (e2e_ms * 1e-3) / 1e12
-    h2d = a_pin.numel() * 2 + b_pin.numel() * 2
+    h2d = a_pin.numel() * 2 + b_pin.numel() * 2      # rank 0; with several ranks the others upload only their B block
     d2h = d_pin.numel() * 4
 
     if rank != 0:

@@ -527,7 +527,7 @@ static cudaError_t copy_block(void* dst, const void* src, int64_t ld, size_t es,
 // Returns GK_ERR_UNSUPPORTED (without setting the error text) when the problem is too small to cut.
 static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const void* a_host, const void* b_host,
                                      const void* c_host, void* d_host, const gk_epilogue_desc* epi, bool read_c,
-                                     size_t a_bytes, size_t b_bytes, cudaStream_t st) {
+                                     size_t a_bytes, size_t b_bytes, bool a_resident, cudaStream_t st) {
   // chunk size: reserved[1] megabytes when set (a tuning aid), else 32 MiB
   const size_t target = static_cast<size_t>(d.reserved[1] > 0 ? d.reserved[1] : 32) << 20;
   auto chunks = [target](size_t bytes) {
@@ -535,7 +535,8 @@ static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const v
     return std::max(1, std::min(n, 8));
   };
   auto ceil_div = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
-  const int64_t mr = ceil_div(ceil_div(d.m, chunks(a_bytes)), 256) * 256;   // rows per chunk
+  // A already on the device: nothing of it to upload, so only the columns are cut
+  const int64_t mr = a_resident ? ceil_div(d.m, 256) * 256 : ceil_div(ceil_div(d.m, chunks(a_bytes)), 256) * 256;
   const int64_t nc = ceil_div(ceil_div(d.n, chunks(b_bytes)), 512) * 512;   // columns per chunk
   const int R = static_cast<int>(ceil_div(d.m, mr)), Cn = static_cast<int>(ceil_div(d.n, nc));
   if (R * Cn <= 1) return GK_ERR_UNSUPPORTED;
@@ -549,14 +550,16 @@ static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const v
   }
   const size_t es_a = dtype_size(d.dtype_a), es_b = dtype_size(d.dtype_b), es_c = dtype_size(d.dtype_c),
                es_d = dtype_size(d.dtype_d);
-  char* a_dev = static_cast<char*>(h->stage_dev[0]);
+  char* a_dev = a_resident ? static_cast<char*>(const_cast<void*>(a_host)) : static_cast<char*>(h->stage_dev[0]);
   char* b_dev = static_cast<char*>(h->stage_dev[1]);
   char* c_dev = static_cast<char*>(h->stage_dev[2]);
   char* d_dev = static_cast<char*>(h->stage_dev[3]);
   size_t ev = 0;
-  // the copy streams start after whatever the caller queued before this call
+  // The copy streams start after whatever the caller queued before this call — except that with A
+  // resident the uploads of B do not wait for the caller's stream (where A may still be arriving from a
+  // broadcast): the kernels run on that stream and are ordered after it anyway.
   GK_CUDA_CHECK(cudaEventRecord(h->events[ev], st));
-  GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_in, h->events[ev], 0));
+  if (!a_resident) GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_in, h->events[ev], 0));
   GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_out, h->events[ev], 0));
   ++ev;
   gk_epilogue_desc epi_blk;
@@ -566,6 +569,7 @@ static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const v
     GK_CUDA_CHECK(cudaMemcpyAsync(h->stage_dev[4], epi->bias, bias_bytes, cudaMemcpyHostToDevice, h->copy_in));
   }
   auto load_a = [&](int i) -> cudaError_t {
+    if (a_resident) return cudaSuccess;
     const int64_t i0 = i * mr, mi = std::min<int64_t>(mr, d.m - i0);
     return d.trans_a ? copy_block(a_dev, a_host, d.lda, es_a, 0, d.k, i0, mi, cudaMemcpyHostToDevice, h->copy_in)
                      : copy_block(a_dev, a_host, d.lda, es_a, i0, mi, 0, d.k, cudaMemcpyHostToDevice, h->copy_in);
@@ -640,7 +644,8 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
   const gk_gemm_desc& d = *desc;
   const bool read_ab = d.layout_a == GK_LAYOUT_DENSE && d.layout_b == GK_LAYOUT_DENSE;
   const bool read_c = c_host != nullptr && d.layout_c == GK_LAYOUT_DENSE && d.beta != 0.0;
-  const size_t a_bytes = read_ab ? operand_bytes(d.lda, d.trans_a ? d.m : d.k, d.plane_a, d.number, d.dtype_a) : 0;
+  const bool a_resident = (d.reserved[2] & 1) != 0 && read_ab;   // `a_host` is a device pointer: A stays where it is
+  const size_t a_bytes = read_ab && !a_resident ? operand_bytes(d.lda, d.trans_a ? d.m : d.k, d.plane_a, d.number, d.dtype_a) : 0;
   const size_t b_bytes = read_ab ? operand_bytes(d.ldb, d.trans_b ? d.k : d.n, d.plane_b, d.number, d.dtype_b) : 0;
   const size_t c_bytes = read_c ? operand_bytes(d.ldc, d.n, d.plane_c, d.number, d.dtype_c) : 0;
   const size_t d_bytes = operand_bytes(d.ldd, d.n, d.plane_d, d.number, d.dtype_d);
@@ -652,7 +657,7 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
   for (int i = 0; i < 5; ++i)
     if (need[i] && (s = stage_reserve(h, i, need[i])) != GK_OK) return s;
   if (d.number == GK_REAL && read_ab && d.m > 0 && d.n > 0 && d.k > 0 && a_bytes + b_bytes + d_bytes >= (64u << 20)) {
-    s = gemm_host_pipelined(h, d, a_host, b_host, c_host, d_host, epi, read_c, a_bytes, b_bytes, st);
+    s = gemm_host_pipelined(h, d, a_host, b_host, c_host, d_host, epi, read_c, a_bytes, b_bytes, a_resident, st);
     if (s == GK_OK) {
       int32_t code = 0;
       return gk_poll_status(h, &code);
@@ -670,8 +675,8 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
     epi_dev.bias = static_cast<const float*>(h->stage_dev[4]);
     epi_use = &epi_dev;
   }
-  s = gk_gemm(h, desc, h->stage_dev[0], h->stage_dev[1], read_c ? h->stage_dev[2] : nullptr, h->stage_dev[3],
-              epi_use, nullptr, stream);
+  s = gk_gemm(h, desc, a_resident ? a_host : h->stage_dev[0], h->stage_dev[1], read_c ? h->stage_dev[2] : nullptr,
+              h->stage_dev[3], epi_use, nullptr, stream);
   if (s != GK_OK) return s;
   if (d_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(d_host, h->stage_dev[3], d_bytes, cudaMemcpyDeviceToHost, st));
   GK_CUDA_CHECK(cudaStreamSynchronize(st));

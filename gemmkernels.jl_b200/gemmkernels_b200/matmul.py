@@ -315,14 +315,18 @@ def bind(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_single
 
 
 def matmul_host(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, stream=None,
-                device_index=None, **transforms):
+                device_index=None, a_on_device=False, **transforms):
     """`matmul` for matrices in host memory (column-major CPU tensors, ideally pinned): copies the
     operands to the device, runs the GEMM and copies D back into `d`; returns when `d` is complete.
+    With `a_on_device=True`, `a` is a device array that is used where it is (the sharded path: A is
+    uploaded by one rank and broadcast over NVLink, every rank uploads only its block of B).
     Julia counterpart: calling the shim's `matmul` with `Array`s instead of `CuArray`s."""
     import torch
     hooks = {k.replace("transform_", ""): v for k, v in transforms.items()}
     epilogue = epilogue or Epilogue.Default()
     desc, epi, (pa, pb, pc, pd) = lower(conf, a, b, c, d, hooks, epilogue, kernel)
+    if a_on_device:
+        desc.reserved[2] |= 1          # A is a device array already (resident or just broadcast): used in place
     dev = device_index if device_index is not None else torch.cuda.current_device()
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):

@@ -62,6 +62,22 @@ def colshard_matmul(local_product, a_storage, b_block, d_block, *, src: int = 0,
     return d_block
 
 
+def colshard_matmul_host(conf, a_host, a_dev, b_host_block, d_host_block, *, src: int = 0, group=None, device_index=None):
+    """The sharded product with operands and result in host memory.  Rank `src` uploads A (its
+    `a_host`; other ranks pass None) into its `a_dev`, A goes to every rank over NVLink (NCCL
+    broadcast into each rank's `a_dev`), and every rank runs the host-path GEMM on its own column
+    block of B and D with A used in place — so A crosses PCIe once per job instead of once per rank."""
+    import torch
+    from .matmul import matmul_host
+    import torch.distributed as dist
+    if a_host is not None:
+        a_dev.copy_(a_host, non_blocking=True)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        broadcast_a(a_dev.T, src, group)            # a_dev.T is the contiguous storage of the column-major array
+    matmul_host(conf, a_dev, b_host_block, None, d_host_block, device_index=device_index, a_on_device=True)
+    return d_host_block
+
+
 def gather_columns(d_block, shard: ColumnShard, group=None):
     """Assembles the full D on every rank from the column blocks (outside any timed region; used by
     tests and by callers that want D in one place).  `d_block` is the contiguous storage of the

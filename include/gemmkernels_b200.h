@@ -121,7 +121,9 @@ typedef struct gk_gemm_desc {
   int32_t max_ctas;     /* cap on the persistent grid */
   int32_t reserved[3];  /* [0]: diagnostic bits, 0 in production (1 no TMA, 2 no MMA, 4 idle producers: lets the
                            bounded waits run out, 8 per-role cycle counters into the workspace, 16 progress
-                           marks for gk_debug_marks); [1]: gk_gemm_host chunk size in MiB (0 = 32); [2]: 0 */
+                           marks for gk_debug_marks); [1]: gk_gemm_host chunk size in MiB (0 = 32);
+                           [2]: gk_gemm_host only, bit 0: `a_host` is a device pointer (A already resident,
+                           e.g. after a broadcast from another rank) and is used in place */
 } gk_gemm_desc;
 
 typedef struct gk_epilogue_desc {

@@ -55,3 +55,23 @@ def test_matmul_host_matches_oracle(M, N, K, ta, tb, with_c):
                   "transform_shared_to_global_d": Transform.Elementwise(Transform.ReLU())} if with_c else {}))
     torch.cuda.synchronize(); GK.poll_status()
     assert torch.equal(dd.cpu(), d)
+
+
+def test_matmul_host_with_a_resident_on_the_device():
+    """a_on_device: A is a device array used in place (the sharded path after a broadcast); B, D in host memory.
+    Large enough for the column-chunk pipeline (D alone is 128 MiB)."""
+    M, N, K = 4096, 8192, 2048
+    rng = np.random.default_rng(99)
+    A = rng.integers(-2, 3, (M, K)).astype(np.float32); B = rng.integers(-2, 3, (K, N)).astype(np.float32)
+    a_dev = GK.to_cuarray(A, GK.Float16)
+    b = host_colmajor(B, torch.float16)
+    d = torch.zeros(N, M, dtype=torch.float32).pin_memory().T
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=Layout.ColMajor[GK.Float16], global_c_layout=Layout.Zero[GK.Float32],
+                         global_d_layout=Layout.ColMajor[GK.Float32])
+    for _ in range(2):
+        d.zero_()
+        GK.matmul_host(conf, a_dev, b, None, d, a_on_device=True)
+    rows = np.sort(rng.choice(M, 32, replace=False))
+    assert np.array_equal(d.numpy()[rows], A[rows] @ B)
+    assert float(d.abs().sum()) == float(np.abs(A @ B).sum())
