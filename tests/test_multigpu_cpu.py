@@ -63,6 +63,25 @@ def _worker(rank, world, port, n, k, m, out_dir):
         assert torch.equal(a_store, torch.from_numpy(np.ascontiguousarray(A.T)))       # A arrived everywhere
         # second step with A resident: no broadcast, new B block
         multigpu.colshard_matmul(local_product, a_store, b_block * 2, d_block, a_is_resident=True)
+        # the host-path variant: only rank 0 holds A in host memory; the per-rank host GEMM is replaced by
+        # the same stand-in (there is no CUDA here), which must find A in place and be told so
+        import importlib
+        mm = importlib.import_module("gemmkernels_b200.matmul")     # the package re-exports a function of that name
+        seen = {}
+
+        def fake_matmul_host(conf, a, b, c, d, *, device_index=None, a_on_device=False, **kw):
+            seen["a_on_device"] = a_on_device
+            local_product(a.T, b.T, d.T)
+        real, mm.matmul_host = mm.matmul_host, fake_matmul_host
+        try:
+            a_dev = torch.zeros(k, m).T                        # column-major (m, k) "device" array
+            d_host = torch.zeros(shard.count, m).T
+            multigpu.colshard_matmul_host(None, torch.from_numpy(np.ascontiguousarray(A.T)).T if rank == 0 else None,
+                                          a_dev, (b_block * 2).T, d_host)
+        finally:
+            mm.matmul_host = real
+        assert seen["a_on_device"] is True and torch.equal(a_dev.T, torch.from_numpy(np.ascontiguousarray(A.T)))
+        assert torch.equal(d_host.T, d_block)
         full = multigpu.gather_columns(d_block, shard)
         want = 2 * (A @ B)
         err = np.linalg.norm(full.numpy().T - want) / np.linalg.norm(want)
