@@ -8,6 +8,7 @@
 #include "diag_gemm.cuh"
 #include "fpu_gemm.cuh"
 #include "simt_gemm.cuh"
+#include "splitk_reduce.cuh"
 #include "split_planes.cuh"
 #include "tc_plan.h"
 
@@ -428,6 +429,10 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
+    if (!(sp.a || sp.b)) {
+      const int splits = tc_choose_k_split(pr, L, h->sm_count);
+      if (splits > 1) plan->workspace_bytes = static_cast<int64_t>(splits) * desc->m * desc->n * 4;   // optional: enables split-K
+    }
   } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {
     plan->kernel = 2;
     plan->grid = static_cast<int32_t>((desc->m / kFpuBM) * (desc->n / kFpuBN));
@@ -486,6 +491,40 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     if (L.params.debug & 8) {
       if (!workspace) return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace");
       L.params.dbg_out = static_cast<long long*>(workspace);
+      return tc_launch(L, st);
+    }
+    // Few tiles and a long K: cut K into runs that fill the idle SMs, partial sums in the workspace
+    // (only when the caller passed one: gk_gemm_query reports the size), then one reduction pass.
+    const int splits = (workspace && !(sp.a || sp.b)) ? tc_choose_k_split(pr, L, h->sm_count) : 1;
+    if (splits > 1) {
+      if (reinterpret_cast<uintptr_t>(workspace) & 255)
+        return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
+      TcProblem ps = pr;
+      ps.C = nullptr; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
+      ps.c_sn[0] = desc->m; ps.d_sn[0] = desc->m;
+      ps.alpha = 1.0; ps.beta = 0.0; ps.epi = nullptr;
+      ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg;     // same tile as planned
+      ps.k_split = splits; ps.split_stride = desc->m * desc->n;
+      TcLaunch Ls;
+      s = tc_plan(h, ps, true, &Ls);
+      if (s != GK_OK) return s;
+      s = tc_launch(Ls, st);
+      if (s != GK_OK) return s;
+      SplitKReduceParams r{};
+      r.partial = static_cast<const float*>(workspace); r.splits = Ls.params.k_split; r.stride = ps.split_stride;
+      r.M = static_cast<int>(desc->m); r.N = static_cast<int>(desc->n);
+      r.alpha = static_cast<float>(desc->alpha);
+      r.beta = (pr.C != nullptr) ? static_cast<float>(desc->beta) : 0.0f;
+      r.C = pr.C; r.ldc = desc->ldc; r.dtype_c = (desc->dtype_c == GK_F16 ? 0 : desc->dtype_c == GK_BF16 ? 1 : 2);
+      r.D = d; r.ldd = desc->ldd; r.dtype_d = (desc->dtype_d == GK_F16 ? 0 : desc->dtype_d == GK_BF16 ? 1 : 2);
+      if (epi) { r.bias = epi->bias; r.bias_axis = epi->bias_axis; r.act = epi->activation; }
+      const bool vec = desc->m % 4 == 0;
+      const int64_t units = (vec ? desc->m / 4 : desc->m) * desc->n;
+      const int blocks = static_cast<int>(std::min<int64_t>((units + 255) / 256, 8 * h->sm_count));
+      if (vec) splitk_reduce_kernel<true><<<blocks, 256, 0, st>>>(r);
+      else splitk_reduce_kernel<false><<<blocks, 256, 0, st>>>(r);
+      GK_CUDA_CHECK(cudaGetLastError());
+      return GK_OK;
     }
     return tc_launch(L, st);
   }

@@ -59,6 +59,11 @@ struct TcParams {
   int32_t M, N, K;
   int32_t tiles_m, tiles_n;  // cluster tiles: (128*CG) x (n_sub*bn)
   int32_t k_blocks;
+  // Split-K (few tiles, long K): the k-blocks are dealt out in k_split contiguous runs of kb_per_split,
+  // work unit t = tile * k_split + run; every run writes its raw FP32 partial sums to plane `run` of a
+  // workspace (split_stride elements apart) and a second kernel adds the planes and applies the epilogue.
+  int32_t k_split, kb_per_split;
+  int64_t split_stride;
   int32_t raster_group;      // cluster tiles along M (N for the horizontal raster) walked before stepping on
   int32_t raster_kind;       // 0 = bands down M, 1 = bands along N, 2 = Z-order (power-of-two tile grids)
   int32_t z_bits;            // Z-order: low bits interleaved per dimension (min of the two log2 extents)
@@ -326,7 +331,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const uint32_t tmem_base = *tmem_slot_gen;
   if (threadIdx.x == 0) tc_mark(p.status, p.debug, 1, 1);   // set-up done, TMEM allocated
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.k_split;   // work units
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
   const int bn_cta = p.bn / CG;
@@ -376,11 +381,12 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
       for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
         int tm, tn;
-        tc_tile_coords(p, t, tm, tn);
+        tc_tile_coords(p, t / p.k_split, tm, tn);
+        const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
         const int n_cta = tn * bn_tile + static_cast<int>(rank) * bn_cta;
         const int mn = (is_a ? m_cta : n_cta) + mn_add;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (prof) pt0 = clock64();
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
@@ -499,7 +505,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         }
         tc_fence_after_sync();
         const uint32_t d_base = tmem_base + as * acc_cols;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (prof) t0 = clock64();
           const bool fgot = mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs);
           if (prof) { t1 = clock64(); mw += t1 - t0; }
@@ -509,7 +516,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             break;
           }
           tc_fence_after_sync();
-          if (kb == 0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 1);   // first stage landed
+          if (kb == kb0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 1);   // first stage landed
 #pragma unroll
           for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
 #pragma unroll
@@ -520,7 +527,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
                   if (ti < n_terms) {
                     const uint64_t da = smem_desc(s16 + t_a[ti] + ks * a_k16, hi_a);
                     const uint64_t db = smem_desc(s16 + t_b[ti] + nb * b_sub16 + ks * b_k16, hi_b);
-                    const uint32_t acc = (kb | ks) ? 1u : t_keep[ti];
+                    const uint32_t acc = ((kb - kb0) | ks) ? 1u : t_keep[ti];
                     if (elected) umma<CG, TF32>(d_base + nb * sub_cols + t_d[ti], da, db, t_id[ti], acc);
                   }
                 }
@@ -528,7 +535,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             }
           }
           if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
-          if (kb == 0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
+          if (kb == kb0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
           if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }
           if (prof) mi += clock64() - t1;
@@ -570,7 +577,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
     const bool prefetch_c = has_c && p.m_div >= p.M && p.n_div >= p.N && p.c_sm0 == 1 && (PLANES == 1 || p.c_plane != 0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;
-      tc_tile_coords(p, t, tm, tn);
+      tc_tile_coords(p, t / p.k_split, tm, tn);
+      const int64_t split_off = static_cast<int64_t>(t % p.k_split) * p.split_stride;
       const int m = (tm * CG + static_cast<int>(rank)) * kTcTileM + q * 32 + lane;
       const int n0 = tn * bn_tile;
       const uint32_t as = two_acc ? (acc_it & 1u) : 0u;
@@ -620,7 +628,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         if (fast_store) {
           // FP32 output, no C, no per-column bias: one FMA (+ max) and one coalesced store per
           // column; a warp writes 32 consecutive rows = 128 bytes of a column of D.
-          float* dp = static_cast<float*>(p.D) + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
+          float* dp = static_cast<float*>(p.D) + split_off + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
           if (ncols >= 32) {
             if (p.act == TC_ACT_RELU) {
 #pragma unroll

@@ -265,6 +265,14 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   p.acc_stages = acc_stages;
   p.bk = kTcKBytes / es;
   p.k_blocks = (p.K + p.bk - 1) / p.bk;
+  p.k_split = 1; p.kb_per_split = std::max(1, p.k_blocks); p.split_stride = 0;
+  if (pr.k_split > 1) {
+    if (planes != 1 || pr.rank5 || pr.dtype_d != GK_F32 || pr.C != nullptr || pr.epi != nullptr || pr.alpha != 1.0)
+      return set_error(GK_ERR_INVALID_ARGUMENT, "split-K takes a plain real product into an FP32 workspace");
+    p.kb_per_split = (p.k_blocks + pr.k_split - 1) / pr.k_split;
+    p.k_split = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;   // no empty runs
+    p.split_stride = pr.split_stride;
+  }
   p.tiles_m = (p.M + kTcTileM * cg - 1) / (kTcTileM * cg);
   p.tiles_n = (p.N + bn * n_sub - 1) / (bn * n_sub);
   p.a_planes = p.b_planes = planes;
@@ -455,7 +463,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   out->kernel = tc_kernel_select(cg, planes, tf32, pr.rank5);
 
   // persistent grid
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.k_split;
   int slots;
   {
     std::lock_guard<std::mutex> lock(h->mu);
@@ -502,6 +510,18 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
     if (s != GK_OK) return s;
   }
   return GK_OK;
+}
+
+int tc_choose_k_split(const TcProblem& pr, const TcLaunch& L, int sm_count) {
+  const TcParams& p = L.params;
+  if (L.planes != 1 || L.rank5 || p.k_split != 1) return 1;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int slots = std::max(1, sm_count / L.cg);
+  if (tiles * 2 > slots || p.k_blocks < 16) return 1;
+  // as many runs as there are idle slots per tile, each at least 8 k-blocks long, 16 at most
+  const int s = std::min({16, slots / tiles, p.k_blocks / 8});
+  (void)pr;
+  return s >= 2 ? s : 1;
 }
 
 gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {

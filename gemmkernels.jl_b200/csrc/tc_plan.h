@@ -34,7 +34,16 @@ struct TcProblem {
   double alpha = 1.0, beta = 0.0;
   const gk_epilogue_desc* epi = nullptr;
   int32_t tile_n = 0, cta_group = 0, stages = 0, raster = 0, raster_group = 0, max_ctas = 0, debug = 0;
+  // split-K: number of contiguous runs the k-blocks are cut into (0 or 1 = none); with k_split > 1, D must be an
+  // FP32 workspace of k_split planes, split_stride elements apart, and C, bias and activation are left out
+  int32_t k_split = 0;
+  int64_t split_stride = 0;
 };
+
+// How many runs to cut K into for this problem on this GPU: 1 unless the tiles fill less than half of the
+// CTA slots and K is long.  `L` is the plan without splitting.
+struct TcLaunch;
+int tc_choose_k_split(const TcProblem& pr, const TcLaunch& L, int sm_count);
 
 struct TcLaunch {
   TcParams params;

@@ -239,6 +239,26 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
     return desc, epi, (a_ptr, b_ptr, c_ptr, d_ptr)
 
 
+def _wants_workspace(desc) -> bool:
+    """Cases in which the library can use a workspace: interleaved complex / dual operands (split into
+    planes first) and real products with few output tiles and a long K (split-K)."""
+    if desc.number != L.GK_REAL:
+        return desc.plane_a == 0 or desc.plane_b == 0
+    return desc.m * desc.n <= (1 << 22) and desc.k >= 2048
+
+
+def _auto_workspace(h, desc, epi, like):
+    """A torch-allocated workspace of the size gk_gemm_query reports, or None."""
+    import torch
+    plan = L.GemmPlan()
+    st = L.lib.gk_gemm_query(h, C.byref(desc), C.byref(epi), C.byref(plan))
+    if st != L.GK_OK:
+        _raise(st)
+    if plan.workspace_bytes:
+        return torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=like.device)
+    return None
+
+
 def matmul(conf: Config, a, b, c, d, *,
            transform_global_to_shared_a=None, transform_global_to_shared_b=None,
            transform_global_to_shared_c=None, transform_shared_to_global_d=None,
@@ -259,14 +279,8 @@ def matmul(conf: Config, a, b, c, d, *,
     dev = d.device.index if d.device.index is not None else torch.cuda.current_device()
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
-        if workspace is None and desc.number != L.GK_REAL and (desc.plane_a == 0 or desc.plane_b == 0):
-            # interleaved complex / dual operands: the library splits them into planes in a workspace
-            plan = L.GemmPlan()
-            st = L.lib.gk_gemm_query(handle(dev), C.byref(desc), C.byref(epi), C.byref(plan))
-            if st != L.GK_OK:
-                _raise(st)
-            if plan.workspace_bytes:
-                workspace = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=d.device)
+        if workspace is None and _wants_workspace(desc):
+            workspace = _auto_workspace(handle(dev), desc, epi, d)
         ws = workspace.data_ptr() if workspace is not None else None
         st = L.lib.gk_gemm(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), ws, C.c_void_p(s))
     if st != L.GK_OK:
@@ -287,14 +301,9 @@ class BoundMatmul:
         self.device = d.device.index if d.device.index is not None else torch.cuda.current_device()
         with torch.cuda.device(self.device):
             self.handle = handle(self.device)
-            if workspace is None and self.desc.number != L.GK_REAL and (self.desc.plane_a == 0 or self.desc.plane_b == 0):
-                plan = L.GemmPlan()
-                st = L.lib.gk_gemm_query(self.handle, C.byref(self.desc), C.byref(self.epi), C.byref(plan))
-                if st != L.GK_OK:
-                    _raise(st)
-                if plan.workspace_bytes:
-                    workspace = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=d.device)
-                    self._keep += (workspace,)
+            if workspace is None and _wants_workspace(self.desc):
+                workspace = _auto_workspace(self.handle, self.desc, self.epi, d)
+                self._keep += (workspace,)
         self.ws = workspace.data_ptr() if workspace is not None else None
         self._torch = torch
 

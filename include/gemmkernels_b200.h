@@ -175,9 +175,12 @@ GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_e
 
 /* Enqueues one GEMM on `stream`.  a, b, c, d are device pointers (c may be NULL when beta == 0 or
  * layout_c is ZERO; c == d is allowed).  epi may be NULL.  workspace is a 256-byte aligned device
- * buffer of at least plan.workspace_bytes bytes (NULL when that is 0); it is needed only when
- * complex / dual A or B are interleaved (plane_a / plane_b == 0): they are split into planes there
- * first, on the same stream. */
+ * buffer of at least plan.workspace_bytes bytes (NULL when that is 0).  It is REQUIRED when complex /
+ * dual A or B are interleaved (plane_a / plane_b == 0): they are split into planes there first, on the
+ * same stream.  It is OPTIONAL for real tensor-core products with few output tiles and a long K, for
+ * which gk_gemm_query also reports a size: given the buffer, K is cut into runs over the otherwise
+ * idle SMs (split-K: FP32 partial sums in the workspace, one reduction pass that applies alpha, beta,
+ * bias and activation); with NULL the same product runs unsplit. */
 GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
                   gk_stream stream);

@@ -434,6 +434,53 @@ def test_empty_and_tiny_products(M, N, K):
         assert np.array_equal(GK.to_numpy(c), 2.0 * (A.astype(np.float32) @ B.astype(np.float32)) + Cm)
 
 
+@pytest.mark.parametrize("M,N,K,ta,cd,beta,bias_axis,act", [
+    (256, 256, 16384, False, "Float32", 0.0, None, None),
+    (384, 520, 8192, False, "Float32", 0.5, "col", Transform.ReLU()),
+    (130, 264, 4096, True, "Float16", 1.0, "row", None),    # M not a multiple of 4 (A stored transposed): scalar reduction pass
+])
+def test_split_k_for_few_tiles_and_long_k(M, N, K, ta, cd, beta, bias_axis, act):
+    """Few output tiles, long K: the product is cut along K over the idle SMs (partial sums in a
+    workspace the Python layer allocates from gk_gemm_query's figure) and reduced in a second pass."""
+    rng = np.random.default_rng(M + K)
+    CD = getattr(GK, cd)
+    A = rng.integers(-2, 3, (M, K)).astype(np.float16); B = rng.integers(-2, 3, (K, N)).astype(np.float16)
+    Cm = rng.integers(-8, 9, (M, N)).astype(np.float32)
+    bias = rng.integers(-4, 5, M if bias_axis == "row" else N).astype(np.float32) if bias_axis else None
+    c = dev(Cm, CD) if beta else None
+    d = GK.cuarray(CD, M, N)
+    epi = Epilogue.Bias(torch.from_numpy(bias).cuda(), axis=bias_axis) if bias_axis else None
+    a_dev = dev(A.T.copy() if ta else A)
+    conf = run_matmul(a_dev, dev(B), c, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                      la=(Layout.RowMajor if ta else Layout.ColMajor)[GK.Float16], lb=Layout.ColMajor[GK.Float16],
+                      lc=(Layout.ColMajor if beta else Layout.Zero)[CD], ld=Layout.ColMajor[CD],
+                      beta=beta if beta else 1.0, epilogue=epi, act=act)
+    plan = GK.query(conf, a_dev, dev(B), c, d, epilogue=epi)
+    assert plan.kernel == 1 and plan.workspace_bytes >= 2 * 4 * M * N          # at least two partial planes
+    want = A.astype(np.float64) @ B.astype(np.float64)
+    if beta:
+        want = want + beta * Cm
+    want = O.epilogue(want, bias, bias_axis or "col", "relu" if act is not None else None)
+    got = GK.to_numpy(d).astype(np.float64)
+    if cd == "Float32":
+        assert np.array_equal(got, want)                   # small integers: exact whatever the summation order
+    else:
+        assert O.normwise_error(got, want) <= 1e-3
+    # without a workspace the same call runs unsplit and gives the same numbers
+    d2 = GK.cuarray(CD, M, N)
+    hooks = {}
+    if beta not in (0.0, 1.0):
+        hooks["shared_to_regs_c"] = Transform.Elementwise(Transform.Scale(beta))
+    if act is not None:
+        hooks["shared_to_global_d"] = Transform.Elementwise(act)
+    desc, epi_desc, (pa, pb, pc, _) = GK.lower(conf, a_dev, dev(B), c, d2, hooks, epi or Epilogue.Default(), Kernel.matmul_singlestage)
+    B_d = dev(B)
+    assert L.lib.gk_gemm(GK.handle(), C.byref(desc), a_dev.data_ptr(), B_d.data_ptr(), pc, d2.data_ptr(), C.byref(epi_desc), None,
+                         C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize(); GK.poll_status()
+    assert torch.equal(d2, d) if cd == "Float32" else O.normwise_error(GK.to_numpy(d2).astype(np.float64), want) <= 1e-3
+
+
 def test_unsupported_combinations_raise_config_error():
     a = GK.cuarray(GK.Float64, 128, 128); d = GK.cuarray(GK.Float64, 128, 128)
     conf = GK.get_config(gemm_shape=(128, 128, 128), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
