@@ -277,6 +277,26 @@ static gk_status launch_simt(const gk_gemm_desc& d, const gk_epilogue_desc* epi,
 
 using namespace gk;
 
+// Split-K decision for a planned product: the plan's own tiles if they leave at least half of the CTA
+// slots idle; otherwise, when the tile shape was left to the library, 256 x 256 pair tiles cut along K
+// (small tiles were chosen to fill the SMs in one round, which a long K makes slow: every tile then
+// streams all of K with little operand reuse).  Returns the number of runs (1 = no split) and may
+// replace *pr's tile choice.
+static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
+  if (pr->tile_n == 0 && pr->cta_group == 0) {
+    TcProblem alt = *pr;
+    alt.tile_n = 256; alt.cta_group = 2;
+    TcLaunch La;
+    if (tc_plan(h, alt, false, &La) == GK_OK) {
+      const int splits = tc_choose_k_split(alt, La, h->sm_count);
+      if (splits > 1) { pr->tile_n = 256; pr->cta_group = 2; return splits; }
+    } else {
+      clear_error();
+    }
+  }
+  return tc_choose_k_split(*pr, L, h->sm_count);
+}
+
 // Register-only FP32 FMA throughput probe: kFmaPeakChains independent packed-FMA chains per thread.
 constexpr int kFmaPeakChains = 16;
 __global__ void __launch_bounds__(256) fma_peak_kernel(float* sink, int iters, float seed) {
@@ -430,7 +450,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
     if (!(sp.a || sp.b)) {
-      const int splits = tc_choose_k_split(pr, L, h->sm_count);
+      const int splits = plan_k_split(h, &pr, L);
       if (splits > 1) plan->workspace_bytes = static_cast<int64_t>(splits) * desc->m * desc->n * 4;   // optional: enables split-K
     }
   } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {
@@ -495,7 +515,7 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     }
     // Few tiles and a long K: cut K into runs that fill the idle SMs, partial sums in the workspace
     // (only when the caller passed one: gk_gemm_query reports the size), then one reduction pass.
-    const int splits = (workspace && !(sp.a || sp.b)) ? tc_choose_k_split(pr, L, h->sm_count) : 1;
+    const int splits = (workspace && !(sp.a || sp.b)) ? plan_k_split(h, &pr, L) : 1;
     if (splits > 1) {
       if (reinterpret_cast<uintptr_t>(workspace) & 255)
         return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
@@ -503,7 +523,7 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
       ps.C = nullptr; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
       ps.c_sn[0] = desc->m; ps.d_sn[0] = desc->m;
       ps.alpha = 1.0; ps.beta = 0.0; ps.epi = nullptr;
-      ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg;     // same tile as planned
+      if (pr.tile_n == 0) { ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg; }   // same tile as planned
       ps.k_split = splits; ps.split_stride = desc->m * desc->n;
       TcLaunch Ls;
       s = tc_plan(h, ps, true, &Ls);

@@ -518,8 +518,8 @@ int tc_choose_k_split(const TcProblem& pr, const TcLaunch& L, int sm_count) {
   const int tiles = p.tiles_m * p.tiles_n;
   const int slots = std::max(1, sm_count / L.cg);
   if (tiles * 2 > slots || p.k_blocks < 16) return 1;
-  // as many runs as there are idle slots per tile, each at least 8 k-blocks long, 16 at most
-  const int s = std::min({16, slots / tiles, p.k_blocks / 8});
+  // as many runs as there are idle slots per tile, each at least 8 k-blocks long, 64 at most
+  const int s = std::min({64, slots / tiles, p.k_blocks / 8});
   (void)pr;
   return s >= 2 ? s : 1;
 }
