@@ -140,6 +140,16 @@ function matmul(conf::Config, a, b, c, d;
                       conf.tile_n, conf.cta_group, conf.stages, rg == 0 ? conf.raster_group : rg, 0, (0, 0, 0))
     epi = GkEpilogueDesc(sizeof(GkEpilogueDesc), has_bias ? (epilogue.axis === :row ? 1 : 2) : 0,
                          has_bias ? reinterpret(CuPtr{Float32}, epilogue.bias_pointer) : CuPtr{Float32}(0), act, (0, 0, 0))
+    # Interleaved complex / dual operands need a workspace (they are split into planes first); real products
+    # with few output tiles and a long K can use one (split-K).  gk_gemm_query reports the size.
+    wants = Operator.number(conf.operator) != 0 ? (desc.plane_a == 0 || desc.plane_b == 0) :
+            (desc.m * desc.n <= 1 << 22 && desc.k >= 2048)
+    if workspace === nothing && wants
+        plan = Ref(GkGemmPlan(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0))
+        gk_check(ccall((:gk_gemm_query, libgk), Cint, (Ptr{Cvoid}, Ref{GkGemmDesc}, Ref{GkEpilogueDesc}, Ref{GkGemmPlan}),
+                       gk_handle(), desc, epi, plan))
+        plan[].workspace_bytes > 0 && (workspace = CuArray{UInt8}(undef, plan[].workspace_bytes))
+    end
     ws = workspace === nothing ? CU_NULL : reinterpret(CuPtr{Cvoid}, pointer(workspace))
     gk_check(ccall((:gk_gemm, libgk), Cint,
                    (Ptr{Cvoid}, Ref{GkGemmDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid},
