@@ -572,6 +572,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
     bool ok = true;
     const bool fast_store = PLANES == 1 && p.dtype_d == TC_F32 && p.beta == 0.0f &&
                             p.bias_axis != TC_BIAS_COL && p.act != TC_ACT_GELU;
+    const bool fast_store16 = PLANES == 1 && p.dtype_d != TC_F32 && p.beta == 0.0f && p.bias_axis != TC_BIAS_COL &&
+                              p.act != TC_ACT_GELU;
     const bool has_c = p.beta != 0.0f;
     // plain matrices only (a contraction's C is addressed through two-level strides), planar or real
     const bool prefetch_c = has_c && p.m_div >= p.M && p.n_div >= p.N && p.c_sm0 == 1 && (PLANES == 1 || p.c_plane != 0);
@@ -646,6 +648,26 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
                 const float x = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
                 dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
               }
+            }
+          }
+        } else if (fast_store16 && ncols >= 32) {
+          // 16-bit output, no C, no per-column bias: the same two instructions per element as above
+          const int64_t di = d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
+          if (p.dtype_d == TC_F16) {
+            __half* dp = static_cast<__half*>(p.D) + di;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
+              if (p.act == TC_ACT_RELU) x = fmaxf(x, 0.0f);
+              dp[j * p.d_sn0] = __float2half_rn(x);
+            }
+          } else {
+            __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(p.D) + di;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = fmaf(p.alpha, __uint_as_float(v[0][j]), bias_row);
+              if (p.act == TC_ACT_RELU) x = fmaxf(x, 0.0f);
+              dp[j * p.d_sn0] = __float2bfloat16_rn(x);
             }
           }
         } else {
