@@ -7,12 +7,15 @@
 // TMA with the 128-byte swizzle and are consumed by tcgen05.mma straight from there; accumulators
 // live in tensor memory, double-buffered so the epilogue of one tile overlaps the main loop of the
 // next (single-buffered for the widest tiles, which fill all 512 columns: n_sub == 2 makes one tile
-// of two column blocks that reuse the same A stage, halving A's share of the shared-memory feed).  With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of
-// A and its own half of B's columns (no multicast), and the pair leader issues the MMAs for both.
+// of two column blocks that reuse the same A stage, halving A's share of the shared-memory feed).
+// With CG == 2 two CTAs of a cluster form one 256-row tile: each loads its own 128 rows of A and its
+// own half of B's columns (no multicast), and the pair leader issues the MMAs for both.  With
+// k_split > 1 a work unit is one run of k-blocks of a tile and writes partial sums to a workspace.
 //
-// Warp roles (256 threads): warp 0 = TMA producer for A, warp 1 = MMA issuer, warp 2 = TMEM
-// allocator, warp 3 = TMA producer for B, warps 4..7 = epilogue (warp w reads TMEM lanes
-// 32*(w%4)..+31).
+// Warp roles: warp 0 = TMA producer for A, warp 1 = MMA issuer, warp 2 = TMEM allocator, warp 3 =
+// TMA producer for B, warps 4.. = epilogue (warp w reads TMEM lanes 32*(w%4)..+31; the one-plane
+// kernels run eight epilogue warps, 384 threads, two per lane quarter taking alternate 32-column
+// chunks; the two-plane kernels four, 256 threads).
 //
 // Every barrier wait is bounded (ptx.cuh: mbar_wait).  When a wait gives up, the CTA raises a
 // shared abort flag, all roles leave their loops, in-flight copies and MMAs are drained with
