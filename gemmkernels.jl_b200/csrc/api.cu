@@ -1,5 +1,6 @@
 // C ABI of the library (include/gemmkernels_b200.h): handle, dispatch, error reporting.
 #include <algorithm>
+#include <type_traits>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -226,13 +227,26 @@ static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, st
 // ------------------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, typename TAcc>
 static gk_status launch_simt_typed(const SimtParams& p, bool tropical, cudaStream_t stream) {
-  dim3 grid(static_cast<unsigned>((p.M + kSimtTile - 1) / kSimtTile),
-            static_cast<unsigned>((p.N + kSimtTile - 1) / kSimtTile));
+  // 128 x 128 tiles (8 x 8 outputs per thread) for FP32 accumulation once there are enough of them to fill
+  // the GPU; 64 x 64 tiles otherwise (measured: the larger tile gains 8 % on Float16 -> Float32, nothing
+  // on Int32, and loses on Int16)
+  constexpr bool kFloatAcc = std::is_same<TAcc, float>::value;
+  const bool big = kFloatAcc && ((p.M + 127) / 128) * ((p.N + 127) / 128) >= 96;
+  const int tile = big ? 128 : kSimtTile;
+  dim3 grid(static_cast<unsigned>((p.M + tile - 1) / tile), static_cast<unsigned>((p.N + tile - 1) / tile));
   if (grid.y > 65535u) return set_error(GK_ERR_INVALID_CONFIG, "N too large for the generic kernel");
+  if constexpr (kFloatAcc) {
+    if (big) {
+      if (tropical) simt_gemm_kernel<TIn, TOut, TAcc, true, 8><<<grid, kSimtThreads, 0, stream>>>(p);
+      else simt_gemm_kernel<TIn, TOut, TAcc, false, 8><<<grid, kSimtThreads, 0, stream>>>(p);
+      GK_CUDA_CHECK(cudaGetLastError());
+      return GK_OK;
+    }
+  }
   if (tropical)
-    simt_gemm_kernel<TIn, TOut, TAcc, true><<<grid, kSimtThreads, 0, stream>>>(p);
+    simt_gemm_kernel<TIn, TOut, TAcc, true, 4><<<grid, kSimtThreads, 0, stream>>>(p);
   else
-    simt_gemm_kernel<TIn, TOut, TAcc, false><<<grid, kSimtThreads, 0, stream>>>(p);
+    simt_gemm_kernel<TIn, TOut, TAcc, false, 4><<<grid, kSimtThreads, 0, stream>>>(p);
   GK_CUDA_CHECK(cudaGetLastError());
   return GK_OK;
 }
@@ -460,9 +474,12 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->smem_bytes = 2 * 2 * kFpuBK * (kFpuBM + kFpuPad) * 4;
     plan->tile_m = kFpuBM; plan->tile_n = kFpuBN; plan->tile_k = kFpuBK; plan->stages = 2;
   } else {
-    plan->grid = static_cast<int32_t>(((desc->m + kSimtTile - 1) / kSimtTile) * ((desc->n + kSimtTile - 1) / kSimtTile));
+    // same rule as launch_simt_typed: 128 x 128 tiles for 4-byte accumulators once there are 96 of them
+    const bool float_acc = desc->dtype_d == GK_F32 || desc->dtype_d == GK_F16 || desc->dtype_d == GK_BF16;
+    const int tile = (float_acc && ((desc->m + 127) / 128) * ((desc->n + 127) / 128) >= 96) ? 128 : kSimtTile;
+    plan->grid = static_cast<int32_t>(((desc->m + tile - 1) / tile) * ((desc->n + tile - 1) / tile));
     plan->block = kSimtThreads; plan->cluster = 1;
-    plan->tile_m = kSimtTile; plan->tile_n = kSimtTile; plan->tile_k = kSimtK; plan->stages = 1;
+    plan->tile_m = tile; plan->tile_n = tile; plan->tile_k = kSimtK; plan->stages = 1;
   }
   return GK_OK;
 }

@@ -67,30 +67,33 @@ constexpr int kSimtTile = 64;
 constexpr int kSimtK = 16;
 constexpr int kSimtThreads = 256;
 
-template <typename TIn, typename TOut, typename TAcc, bool TROPICAL>
+// TM x TM outputs per thread, a (16 TM) x (16 TM) tile per CTA: TM = 4 (64 x 64 tiles) for small problems and
+// 8-byte accumulators, TM = 8 (128 x 128 tiles, twice the FMAs per shared-memory load) for large ones.
+template <typename TIn, typename TOut, typename TAcc, bool TROPICAL, int TM>
 __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParams p) {
-  __shared__ TAcc As[kSimtK][kSimtTile + 1];
-  __shared__ TAcc Bs[kSimtK][kSimtTile + 1];
+  constexpr int TILE = 16 * TM;
+  __shared__ TAcc As[kSimtK][TILE + 1];
+  __shared__ TAcc Bs[kSimtK][TILE + 1];
 
   const TIn* A = static_cast<const TIn*>(p.A);
   const TIn* B = static_cast<const TIn*>(p.B);
   const TOut* C = static_cast<const TOut*>(p.C);
   TOut* D = static_cast<TOut*>(p.D);
 
-  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * kSimtTile;
-  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * kSimtTile;
-  const int tx = threadIdx.x & 15;  // 4 rows each
-  const int ty = threadIdx.x >> 4;  // 4 columns each
+  const int64_t m0 = static_cast<int64_t>(blockIdx.x) * TILE;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * TILE;
+  const int tx = threadIdx.x & 15;  // TM rows each, 16 apart
+  const int ty = threadIdx.x >> 4;  // TM columns each, 16 apart
 
   const TAcc alpha = static_cast<TAcc>(p.alpha);
   const TAcc beta = static_cast<TAcc>(p.beta);
   const TAcc ident = TROPICAL ? simt_neg_inf<TAcc>() : TAcc(0);
 
-  TAcc acc[4][4];
+  TAcc acc[TM][TM];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < TM; ++j) {
       const int64_t m = m0 + tx + 16 * i, n = n0 + ty + 16 * j;
       TAcc c = ident;
       if (TROPICAL && p.has_c && m < p.M && n < p.N)
@@ -100,14 +103,14 @@ __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParam
 
   if (!p.a_zero) {
     for (int64_t k0 = 0; k0 < p.K; k0 += kSimtK) {
-      // 64 x 16 elements per operand, 4 per thread
+      // TILE x 16 elements per operand, TM per thread
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
+      for (int r = 0; r < TM; ++r) {
         const int e = threadIdx.x + r * kSimtThreads;
         {
           // A: walk the contiguous index fastest
-          const int mm = (p.a_sm == 1) ? (e & 63) : (e >> 4);
-          const int kk = (p.a_sm == 1) ? (e >> 6) : (e & 15);
+          const int mm = (p.a_sm == 1) ? (e % TILE) : (e >> 4);
+          const int kk = (p.a_sm == 1) ? (e / TILE) : (e & 15);
           const int64_t m = m0 + mm, k = k0 + kk;
           TAcc v = ident;
           if (m < p.M && k < p.K) {
@@ -117,8 +120,8 @@ __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParam
           As[kk][mm] = v;
         }
         {
-          const int nn = (p.b_sn == 1) ? (e & 63) : (e >> 4);
-          const int kk = (p.b_sn == 1) ? (e >> 6) : (e & 15);
+          const int nn = (p.b_sn == 1) ? (e % TILE) : (e >> 4);
+          const int kk = (p.b_sn == 1) ? (e / TILE) : (e & 15);
           const int64_t n = n0 + nn, k = k0 + kk;
           TAcc v = ident;
           if (n < p.N && k < p.K) v = simt_cvt_in<TAcc, TIn>(B[k * p.b_sk + n * p.b_sn]);
@@ -128,15 +131,15 @@ __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParam
       __syncthreads();
 #pragma unroll
       for (int kk = 0; kk < kSimtK; ++kk) {
-        TAcc a[4], b[4];
+        TAcc a[TM], b[TM];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = As[kk][tx + 16 * i];
+        for (int i = 0; i < TM; ++i) a[i] = As[kk][tx + 16 * i];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) b[j] = Bs[kk][ty + 16 * j];
+        for (int j = 0; j < TM; ++j) b[j] = Bs[kk][ty + 16 * j];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < TM; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < TM; ++j) {
             if (TROPICAL) {
               // max-plus: padding holds -inf (floats) or INT_MIN; keep integer sums from wrapping
               const TAcc s = (a[i] == ident || b[j] == ident) ? ident : a[i] + b[j];
@@ -151,9 +154,9 @@ __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParam
   }
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < TM; ++j) {
       const int64_t m = m0 + tx + 16 * i, n = n0 + ty + 16 * j;
       if (m < p.M && n < p.N) {
         TAcc v = acc[i][j];
