@@ -73,8 +73,9 @@ static gk_status validate_desc(const gk_gemm_desc* d, const gk_epilogue_desc* ep
 static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, const void* c, const void* dd,
                          const gk_epilogue_desc* epi) {
   if (d.op == GK_OP_FPU_TROPICAL || d.op == GK_OP_TCGEN05 || d.number != GK_REAL) return false;
-  if (d.dtype_a != GK_F32 || d.dtype_b != GK_F32 || d.dtype_d != GK_F32) return false;
-  if (d.compute != GK_F32) return false;
+  if (d.dtype_a != d.dtype_b || d.dtype_d != GK_F32) return false;
+  if (d.dtype_a != GK_F32 && d.dtype_a != GK_F16 && d.dtype_a != GK_BF16) return false;
+  if (d.compute != GK_F32 && d.compute != d.dtype_a) return false;
   if (d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE) return false;
   const bool has_c = d.layout_c == GK_LAYOUT_DENSE && d.beta != 0.0;
   if (has_c && (d.dtype_c != GK_F32 || d.ldc % 4)) return false;
@@ -91,7 +92,7 @@ static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, co
 static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
                             const void* b, const void* c, void* dd, cudaStream_t stream) {
   FpuParams p{};
-  p.A = static_cast<const float*>(a); p.B = static_cast<const float*>(b);
+  p.A = a; p.B = b;
   p.C = static_cast<const float*>(c); p.D = static_cast<float*>(dd);
   p.M = static_cast<int>(d.m); p.N = static_cast<int>(d.n); p.K = static_cast<int>(d.k);
   p.lda = d.lda; p.ldb = d.ldb; p.ldc = d.ldc; p.ldd = d.ldd;
@@ -107,10 +108,16 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   const dim3 grid(static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n));
   const bool ak = d.trans_a != 0;   // stored K x M: K is the contiguous index of A
   const bool bk = d.trans_b == 0;   // stored K x N: K is the contiguous index of B
-  if (ak && bk) fpu_gemm_kernel<true, true><<<grid, kFpuThreads, 0, stream>>>(p);
-  else if (ak && !bk) fpu_gemm_kernel<true, false><<<grid, kFpuThreads, 0, stream>>>(p);
-  else if (!ak && bk) fpu_gemm_kernel<false, true><<<grid, kFpuThreads, 0, stream>>>(p);
-  else fpu_gemm_kernel<false, false><<<grid, kFpuThreads, 0, stream>>>(p);
+  auto launch = [&](auto tag) {
+    using TIn = decltype(tag);
+    if (ak && bk) fpu_gemm_kernel<true, true, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
+    else if (ak && !bk) fpu_gemm_kernel<true, false, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
+    else if (!ak && bk) fpu_gemm_kernel<false, true, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
+    else fpu_gemm_kernel<false, false, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
+  };
+  if (d.dtype_a == GK_F16) launch(__half{});
+  else if (d.dtype_a == GK_BF16) launch(__nv_bfloat16{});
+  else launch(float{});
   GK_CUDA_CHECK(cudaGetLastError());
   return GK_OK;
 }

@@ -8,9 +8,14 @@
 // k-tile ahead; an operand whose contiguous index is K (a transposed A, an untransposed B) is
 // transposed on its way into shared memory.  Two shared-memory buffers, one barrier per k-tile.
 //
+// A and B may be Float16 or BFloat16 (the FPU operator's Float16 -> Float32 configuration): they are
+// widened to Float32 as they are loaded, the arithmetic is the same FP32 FMA chain.
+//
 // Takes tile-multiple sizes and 16-byte aligned rows only (the reference's UnsafeAligned* layouts,
 // src/layout.jl:192-270); everything else goes to the generic kernel in simt_gemm.cuh.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -19,8 +24,8 @@ namespace gk {
 constexpr int kFpuBM = 128, kFpuBN = 128, kFpuBK = 16, kFpuThreads = 256, kFpuPad = 4;
 
 struct FpuParams {
-  const float* A;
-  const float* B;
+  const void* A;   // Float32, or Float16 / BFloat16 widened to Float32 on the way into shared memory
+  const void* B;
   const float* C;
   float* D;
   int M, N, K;
@@ -36,18 +41,33 @@ struct FpuParams {
 // Global -> registers for one operand tile: 2 float4 per thread.
 //   MN-contiguous: element (x, k) at base[x + k*ld]  (x = m or n): rows of 128 floats per k
 //   K-contiguous : element (x, k) at base[k + x*ld]               : rows of 16 floats per x
-template <bool KMAJOR>
-__device__ __forceinline__ void fpu_load_tile(const float* __restrict__ base, int64_t ld, int x0, int k0,
+// Four consecutive elements as Float32.
+__device__ __forceinline__ float4 fpu_load4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 fpu_load4(const __half* p) {
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+  const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float4 fpu_load4(const __nv_bfloat16* p) {
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+template <bool KMAJOR, typename TIn>
+__device__ __forceinline__ void fpu_load_tile(const TIn* __restrict__ base, int64_t ld, int x0, int k0,
                                               float4 (&r)[2]) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int idx = threadIdx.x + i * kFpuThreads;
     if constexpr (KMAJOR) {
       const int x = idx >> 2, k4 = idx & 3;
-      r[i] = __ldg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(x0 + x) * ld + k0 + k4 * 4));
+      r[i] = fpu_load4(base + static_cast<int64_t>(x0 + x) * ld + k0 + k4 * 4);
     } else {
       const int k = idx >> 5, x4 = idx & 31;
-      r[i] = __ldg(reinterpret_cast<const float4*>(base + static_cast<int64_t>(k0 + k) * ld + x0 + x4 * 4));
+      r[i] = fpu_load4(base + static_cast<int64_t>(k0 + k) * ld + x0 + x4 * 4);
     }
   }
 }
@@ -75,8 +95,10 @@ __device__ __forceinline__ float fpu_act(float v, int act) {
   return v;
 }
 
-template <bool A_KMAJOR, bool B_KMAJOR>
+template <bool A_KMAJOR, bool B_KMAJOR, typename TIn>
 __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParams p) {
+  const TIn* gA = static_cast<const TIn*>(p.A);
+  const TIn* gB = static_cast<const TIn*>(p.B);
   __shared__ __align__(16) float As[2][kFpuBK][kFpuBM + kFpuPad];
   __shared__ __align__(16) float Bs[2][kFpuBK][kFpuBN + kFpuPad];
 
@@ -104,8 +126,8 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
 
   float4 ra[2], rb[2];
   const int kt_count = p.K / kFpuBK;
-  fpu_load_tile<A_KMAJOR>(p.A, p.lda, m0, 0, ra);
-  fpu_load_tile<B_KMAJOR>(p.B, p.ldb, n0, 0, rb);
+  fpu_load_tile<A_KMAJOR>(gA, p.lda, m0, 0, ra);
+  fpu_load_tile<B_KMAJOR>(gB, p.ldb, n0, 0, rb);
   // alpha scales A on its way in, as the reference's shared_to_regs_a transform does
   fpu_store_tile<A_KMAJOR>(As[0], ra, p.alpha);
   fpu_store_tile<B_KMAJOR>(Bs[0], rb, 1.0f);
@@ -115,8 +137,8 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
     const int cur = kt & 1;
     const bool more = kt + 1 < kt_count;
     if (more) {
-      fpu_load_tile<A_KMAJOR>(p.A, p.lda, m0, (kt + 1) * kFpuBK, ra);
-      fpu_load_tile<B_KMAJOR>(p.B, p.ldb, n0, (kt + 1) * kFpuBK, rb);
+      fpu_load_tile<A_KMAJOR>(gA, p.lda, m0, (kt + 1) * kFpuBK, ra);
+      fpu_load_tile<B_KMAJOR>(gB, p.ldb, n0, (kt + 1) * kFpuBK, rb);
     }
 #pragma unroll
     for (int k = 0; k < kFpuBK; ++k) {
