@@ -7,6 +7,7 @@
 // This is the correctness backstop for shapes the fast kernels do not take (unaligned leading
 // dimensions, integer and FP64 types).  The FP32 fast path is fpu_gemm.cuh.
 #pragma once
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -142,7 +143,9 @@ __global__ void __launch_bounds__(kSimtThreads) simt_gemm_kernel(const SimtParam
           for (int j = 0; j < TM; ++j) {
             if (TROPICAL) {
               // max-plus: padding holds -inf (floats) or INT_MIN; keep integer sums from wrapping
-              const TAcc s = (a[i] == ident || b[j] == ident) ? ident : a[i] + b[j];
+              TAcc s;
+              if constexpr (std::is_floating_point<TAcc>::value) s = a[i] + b[j];   // -inf + x stays -inf
+              else s = (a[i] == ident || b[j] == ident) ? ident : a[i] + b[j];
               acc[i][j] = s > acc[i][j] ? s : acc[i][j];
             } else {
               acc[i][j] = simt_fma<TAcc>(a[i], b[j], acc[i][j]);
