@@ -120,6 +120,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 // ----------------------------------------------------------------------------------------------
 // TMA
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start
+// while its predecessor in the stream is still running; it must not touch global memory the
+// predecessor may still write (or write what it may still read) before pdl_wait() returns.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }

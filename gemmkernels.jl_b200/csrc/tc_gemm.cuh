@@ -308,6 +308,9 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       reinterpret_cast<volatile uint32_t*>(ctrl_gen + 16 * p.stages + 40);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(ctrl_gen + 16 * p.stages + 44);
 
+  // Let the next kernel of the stream begin its own set-up as SMs free up (it waits, as this one does
+  // below, before touching global memory).
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(bar_full + 8u * s, 1);
@@ -382,6 +385,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       bool ok = true;
       const bool prof = (p.debug & 8) != 0;
       long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
+      pdl_wait();           // operands may be the previous kernel's output
       for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
         int tm, tn;
         tc_tile_coords(p, t / p.k_split, tm, tn);
@@ -579,6 +583,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
                               p.act != TC_ACT_GELU;
     const bool has_c = p.beta != 0.0f;
     // plain matrices only (a contraction's C is addressed through two-level strides), planar or real
+    pdl_wait();             // D (and C) may still be in use by the previous kernel
     const bool prefetch_c = has_c && p.m_div >= p.M && p.n_div >= p.N && p.c_sm0 == 1 && (PLANES == 1 || p.c_plane != 0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;

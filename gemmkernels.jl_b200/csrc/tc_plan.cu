@@ -530,12 +530,19 @@ gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {
   cfg.blockDim = dim3(tc_threads(L.planes));
   cfg.dynamicSmemBytes = L.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute at{};
+  cudaLaunchAttribute at[2]{};
+  int n_at = 0;
   if (L.cg == 2) {
-    at.id = cudaLaunchAttributeClusterDimension;
-    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-    cfg.attrs = &at; cfg.numAttrs = 1;
+    at[n_at].id = cudaLaunchAttributeClusterDimension;
+    at[n_at].val.clusterDim.x = 2; at[n_at].val.clusterDim.y = 1; at[n_at].val.clusterDim.z = 1;
+    ++n_at;
   }
+  // programmatic dependent launch: the kernel's set-up may overlap the tail of the kernel before it in the
+  // stream; its producers and epilogue wait (griddepcontrol.wait) before their first global access
+  at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[n_at].val.programmaticStreamSerializationAllowed = 1;
+  ++n_at;
+  cfg.attrs = at; cfg.numAttrs = n_at;
   void* args[1] = {const_cast<TcParams*>(&L.params)};
   GK_CUDA_CHECK(cudaLaunchKernelExC(&cfg, L.kernel, args));
   return GK_OK;
