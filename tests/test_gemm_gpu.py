@@ -481,6 +481,35 @@ def test_split_k_for_few_tiles_and_long_k(M, N, K, ta, cd, beta, bias_axis, act)
     assert torch.equal(d2, d) if cd == "Float32" else O.normwise_error(GK.to_numpy(d2).astype(np.float64), want) <= 1e-3
 
 
+def test_chained_products_without_host_synchronisation():
+    """Y = (A*B)*C with the first product's Float16 output feeding the second, ten chains enqueued back to back:
+    the second kernel may start its set-up while the first is still running (programmatic dependent launch) but
+    must not read X before the first has finished; every chain must give the exact result."""
+    n = 2048
+    rng = np.random.default_rng(404)
+    A = (rng.random((n, n)) < 1 / 64).astype(np.float16); B = (rng.random((n, n)) < 1 / 64).astype(np.float16)
+    Cm = rng.integers(-1, 2, (n, n)).astype(np.float16)
+    X = A.astype(np.float32) @ B.astype(np.float32)
+    assert X.max() <= 2048                                   # exactly representable in Float16
+    want = X @ Cm.astype(np.float32)
+    a, b, c = dev(A), dev(B), dev(Cm)
+    x = GK.cuarray(GK.Float16, n, n); y = GK.cuarray(GK.Float32, n, n)
+    lay16, lay32 = Layout.UnsafeAlignedColMajor[GK.Float16], Layout.UnsafeAlignedColMajor[GK.Float32]
+    conf1 = GK.get_config(gemm_shape=(n, n, n), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                          global_a_layout=lay16, global_c_layout=Layout.Zero[GK.Float16], global_d_layout=lay16)
+    conf2 = GK.get_config(gemm_shape=(n, n, n), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                          global_a_layout=lay16, global_c_layout=Layout.Zero[GK.Float32], global_d_layout=lay32)
+    first, second = GK.bind(conf1, a, b, None, x), GK.bind(conf2, x, c, None, y)
+    for i in range(10):
+        x.zero_(); y.zero_()                                  # stale data would show
+        first(); second()
+        if i % 3 == 0:
+            torch.cuda.synchronize()
+            assert np.array_equal(GK.to_numpy(y), want), i
+    torch.cuda.synchronize(); GK.poll_status()
+    assert np.array_equal(GK.to_numpy(y), want)
+
+
 def test_unsupported_combinations_raise_config_error():
     a = GK.cuarray(GK.Float64, 128, 128); d = GK.cuarray(GK.Float64, 128, 128)
     conf = GK.get_config(gemm_shape=(128, 128, 128), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
