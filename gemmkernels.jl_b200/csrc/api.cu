@@ -198,9 +198,9 @@ static gk_status launch_diag(gk_handle h, const gk_gemm_desc& d, const gk_epilog
     return GK_OK;
   }
   if (d.m == 0 || d.n == 0) return GK_OK;
-  if (!vec) diag_gemm_scalar_kernel<<<grid, 256, 0, stream>>>(p);
-  else if (d.dtype_a == GK_F16) diag_gemm_vec_kernel<__half><<<grid, 256, 0, stream>>>(p);
-  else diag_gemm_vec_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  void (*kern)(const DiagParams) = !vec ? diag_gemm_scalar_kernel
+                                        : (d.dtype_a == GK_F16 ? diag_gemm_vec_kernel<__half> : diag_gemm_vec_kernel<__nv_bfloat16>);
+  GK_CUDA_CHECK(launch_dependent(kern, dim3(grid), dim3(256), 0, stream, p));
   GK_CUDA_CHECK(cudaGetLastError());
   return GK_OK;
 }
@@ -565,9 +565,8 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
       const bool vec = desc->m % 4 == 0;
       const int64_t units = (vec ? desc->m / 4 : desc->m) * desc->n;
       const int blocks = static_cast<int>(std::min<int64_t>((units + 255) / 256, 8 * h->sm_count));
-      if (vec) splitk_reduce_kernel<true><<<blocks, 256, 0, st>>>(r);
-      else splitk_reduce_kernel<false><<<blocks, 256, 0, st>>>(r);
-      GK_CUDA_CHECK(cudaGetLastError());
+      GK_CUDA_CHECK(launch_dependent(vec ? splitk_reduce_kernel<true> : splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0,
+                                     st, r));
       return GK_OK;
     }
     return tc_launch(L, st);

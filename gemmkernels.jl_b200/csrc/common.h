@@ -53,6 +53,20 @@ inline const char* dtype_name(int32_t dt) {
                            cudaGetErrorString(_e), __FILE__, __LINE__);                  \
   } while (0)
 
+// Launch with programmatic stream serialisation: the kernel may begin while its predecessor in the
+// stream drains; it must execute griddepcontrol.wait before its first global access (ptx.cuh: pdl_wait).
+template <typename P>
+inline cudaError_t launch_dependent(void (*kernel)(const P), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    const P& params) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at{};
+  at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 }  // namespace gk
 
 struct gk_handle_s {

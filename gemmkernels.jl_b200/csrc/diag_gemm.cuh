@@ -50,6 +50,8 @@ __device__ __forceinline__ float diag_act(float x, int act) {
 
 // Scalar path: any strides, any of the three element types.
 __global__ void __launch_bounds__(256) diag_gemm_scalar_kernel(const DiagParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // launched with stream serialisation: see launch_dependent
   const int64_t total = p.M * p.N;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -65,6 +67,8 @@ __global__ void __launch_bounds__(256) diag_gemm_scalar_kernel(const DiagParams 
 // Vector path: 16-bit v and B (column-major), FP32 C and D, M a multiple of 8, aligned columns.
 template <typename T16>
 __global__ void __launch_bounds__(256) diag_gemm_vec_kernel(const DiagParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t m8 = p.M / 8;
   const int64_t total = m8 * p.N;
   const T16* v = static_cast<const T16*>(p.v);

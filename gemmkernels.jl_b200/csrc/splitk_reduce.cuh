@@ -47,6 +47,8 @@ __device__ __forceinline__ float splitk_finish(const SplitKReduceParams& p, floa
 
 template <bool VEC4>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitKReduceParams p) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // the partial sums come from the kernel before this one
   const int rows = VEC4 ? p.M / 4 : p.M;          // units along M
   const int64_t units = static_cast<int64_t>(rows) * p.N;
   for (int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; u < units;
