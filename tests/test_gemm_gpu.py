@@ -846,3 +846,40 @@ def test_randomised_shapes_types_tiles_and_epilogues(cs):
     want = O.epilogue(want, bias, cs["bias"] if bias is not None else "col", None if cs["act"] == "none" else cs["act"])
     tol = {"Float32": 2e-6, "Float16": 1e-3, "BFloat16": 8e-3}[CD.name]
     assert O.normwise_error(GK.to_numpy(d).astype(np.float64), want) <= tol
+
+
+# ------------------------------------------------------------------------------------------------
+# randomised contractions: mode orders, extents, both paths
+# ------------------------------------------------------------------------------------------------
+def _contraction_cases(n=24):
+    rng = np.random.default_rng(777)
+    cases = []
+    for i in range(n):
+        n_m, n_n, n_k = (int(rng.integers(1, 3)) for _ in range(3))        # 1-2 modes per group
+        names = iter("abcdefgh")
+        m_modes = [next(names) for _ in range(n_m)]; n_modes = [next(names) for _ in range(n_n)]
+        k_modes = [next(names) for _ in range(n_k)]
+        ext = {ch: int(rng.choice([8, 16, 32, 64])) for ch in m_modes + n_modes + k_modes}
+        perm = lambda xs: "".join(rng.permutation(xs))
+        cases.append(dict(i=i, a=perm(m_modes + k_modes), b=perm(k_modes + n_modes), d=perm(m_modes + n_modes), ext=ext,
+                          alpha=float(rng.choice([1.0, 0.5])), beta=float(rng.choice([0.0, 1.0])),
+                          force_gather=bool(rng.integers(0, 4) == 0)))
+    return cases
+
+
+@pytest.mark.parametrize("cs", _contraction_cases(), ids=lambda c: f"{c['i']}-{c['d']}={c['a']}*{c['b']}")
+def test_randomised_contractions(cs):
+    rng = np.random.default_rng(5000 + cs["i"])
+    shape = lambda modes: tuple(cs["ext"][ch] for ch in modes)
+    A = rng.integers(-2, 3, shape(cs["a"])).astype(np.float16)
+    B = rng.integers(-2, 3, shape(cs["b"])).astype(np.float16)
+    Cm = rng.integers(-4, 5, shape(cs["d"])).astype(np.float32)
+    d = _julia_tensor(Cm)
+    plan = GK.contract_query(d, cs["d"], _julia_tensor(A), cs["a"], _julia_tensor(B), cs["b"], cs["alpha"], cs["beta"],
+                             force_gather=cs["force_gather"])
+    assert plan.kernel in (1, 5) and (plan.kernel == 5 or not cs["force_gather"])
+    GK.contract_(d, cs["d"], _julia_tensor(A), cs["a"], _julia_tensor(B), cs["b"], cs["alpha"], cs["beta"],
+                 force_gather=cs["force_gather"])
+    torch.cuda.synchronize(); GK.poll_status()
+    want = O.contract(A, cs["a"], B, cs["b"], cs["d"], cs["alpha"], cs["beta"], Cm)
+    assert np.array_equal(GK.to_numpy(d), want.astype(np.float32))        # small integers, alpha a power of two: exact
