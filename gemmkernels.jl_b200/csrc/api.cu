@@ -59,6 +59,18 @@ static gk_status validate_desc(const gk_gemm_desc* d, const gk_epilogue_desc* ep
     return set_error(GK_ERR_UNSUPPORTED, "unknown element type in descriptor");
   if (d->number < GK_REAL || d->number > GK_DUAL)
     return set_error(GK_ERR_INVALID_CONFIG, "unknown number system %d", d->number);
+  if (d->batch > 1) {
+    if (d->number != GK_REAL)
+      return set_error(GK_ERR_INVALID_CONFIG, "batched products are real products (number = %d)", d->number);
+    if (d->layout_a == GK_LAYOUT_DIAGONAL)
+      return set_error(GK_ERR_INVALID_CONFIG, "batched products do not take a Diagonal A");
+    if (d->batch_stride_a < 0 || d->batch_stride_b < 0 || d->batch_stride_c < 0 || d->batch_stride_d < 0)
+      return set_error(GK_ERR_DIMENSION_MISMATCH, "Dimensions do not match: negative batch stride");
+    if (d->m > 0 && d->n > 0 && d->batch_stride_d < d->ldd * (d->n - 1) + d->m)
+      return set_error(GK_ERR_DIMENSION_MISMATCH,
+                       "Dimensions do not match: batch_stride_d = %lld makes the outputs of the batch overlap",
+                       (long long)d->batch_stride_d);
+  }
   if (epi) {
     if (epi->bias_axis < GK_BIAS_NONE || epi->bias_axis > GK_BIAS_COL)
       return set_error(GK_ERR_UNSUPPORTED, "bias axis %d is not none/row/column", epi->bias_axis);
@@ -470,7 +482,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
-    if (!(sp.a || sp.b)) {
+    if (!(sp.a || sp.b) && desc->batch <= 1) {
       const int splits = plan_k_split(h, &pr, L);
       if (splits > 1) plan->workspace_bytes = static_cast<int64_t>(splits) * desc->m * desc->n * 4;   // optional: enables split-K
     }
@@ -491,23 +503,56 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
   return GK_OK;
 }
 
+// Host-side checks of the pointers a launch would dereference: a caller's mistake must come back as a
+// status code, not as a device fault.
+static gk_status check_pointers(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
+                                const void* c, const void* dd) {
+  if (d.m == 0 || d.n == 0) return GK_OK;
+  if (!dd) return set_error(GK_ERR_INVALID_ARGUMENT, "D is NULL");
+  const bool product = d.k > 0 && d.alpha != 0.0 && d.layout_a != GK_LAYOUT_ZERO && d.layout_b != GK_LAYOUT_ZERO;
+  if (product && !a) return set_error(GK_ERR_INVALID_ARGUMENT, "A is NULL but its layout is not Zero");
+  if (product && !b) return set_error(GK_ERR_INVALID_ARGUMENT, "B is NULL but its layout is not Zero");
+  if (d.layout_c != GK_LAYOUT_ZERO && d.beta != 0.0 && !c)
+    return set_error(GK_ERR_INVALID_ARGUMENT, "beta = %g but C is NULL (pass C, or beta = 0 / layout_c = ZERO)", d.beta);
+  if (epi && epi->bias_axis != GK_BIAS_NONE && !epi->bias)
+    return set_error(GK_ERR_INVALID_ARGUMENT, "bias axis set but bias pointer is NULL");
+  return GK_OK;
+}
+
+// One product of a batch (or the only one) on the kernels that have no batch index of their own.
+static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b, const void* c,
+                             void* d, const gk_epilogue_desc* epi, void* workspace, int64_t workspace_bytes,
+                             cudaStream_t st);
+
 gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
-                  gk_stream stream) {
+                  int64_t workspace_bytes, gk_stream stream) {
   clear_error();
-  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  // argument checks first (they need no device), so that a caller's mistake is reported as such
   gk_status s = validate_desc(desc, epi);
   if (s != GK_OK) return s;
-  if (!d && desc->m > 0 && desc->n > 0) return set_error(GK_ERR_INVALID_ARGUMENT, "D is NULL");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((s = check_pointers(*desc, epi, a, b, c, d)) != GK_OK) return s;
+  if (workspace_bytes < 0 || (workspace_bytes > 0 && !workspace))
+    return set_error(GK_ERR_INVALID_ARGUMENT, "workspace_bytes = %lld with a %s workspace", (long long)workspace_bytes,
+                     workspace ? "non-NULL" : "NULL");
+  if (!workspace) workspace_bytes = 0;
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  return gemm_single(h, desc, a, b, c, d, epi, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b, const void* c,
+                             void* d, const gk_epilogue_desc* epi, void* workspace, int64_t workspace_bytes,
+                             cudaStream_t st) {
+  gk_status s = GK_OK;
   std::string why;
   gk_gemm_desc planar = *desc;
   const SplitPlan sp = plan_split(*desc);
   if (sp.a || sp.b) {
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || workspace_bytes < sp.a_bytes + sp.b_bytes)
       return set_error(GK_ERR_INVALID_ARGUMENT,
                        "interleaved complex/dual operands are split into planes first: pass a 256-byte aligned "
-                       "workspace of %lld bytes (gk_gemm_query reports it)", (long long)(sp.a_bytes + sp.b_bytes));
+                       "workspace of %lld bytes (gk_gemm_query reports it); got %lld bytes",
+                       (long long)(sp.a_bytes + sp.b_bytes), (long long)workspace_bytes);
     char* ws = static_cast<char*>(workspace);
     if (sp.a) {
       s = launch_split(desc->dtype_a, a, ws, sp.a_rows, sp.a_cols, desc->lda, sp.a_ld, h->sm_count, st);
@@ -526,6 +571,7 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
   if (fam == 4) return launch_diag(h, *desc, epi, a, b, c, d, st, nullptr);
   if (desc->m == 0 || desc->n == 0) return GK_OK;
   if (fam == 1 && (desc->k == 0 || desc->alpha == 0.0)) fam = 3;  // nothing to multiply
+  const int batch = desc->batch > 1 ? desc->batch : 1;
   if (fam == 1) {
     TcLaunch L;
     TcProblem pr;
@@ -533,13 +579,19 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     s = tc_plan(h, pr, true, &L);
     if (s != GK_OK) return s;
     if (L.params.debug & 8) {
-      if (!workspace) return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace");
+      if (!workspace || workspace_bytes < static_cast<int64_t>(L.grid) * 16 * 8)
+        return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace of %lld bytes",
+                         (long long)L.grid * 16 * 8);
       L.params.dbg_out = static_cast<long long*>(workspace);
       return tc_launch(L, st);
     }
     // Few tiles and a long K: cut K into runs that fill the idle SMs, partial sums in the workspace
-    // (only when the caller passed one: gk_gemm_query reports the size), then one reduction pass.
-    const int splits = (workspace && !(sp.a || sp.b)) ? plan_k_split(h, &pr, L) : 1;
+    // (only when the caller passed one that is large enough: gk_gemm_query reports the size), then
+    // one reduction pass.
+    const int64_t plane_bytes = desc->m * desc->n * 4;
+    int splits = (workspace && !(sp.a || sp.b) && batch == 1) ? plan_k_split(h, &pr, L) : 1;
+    if (splits > 1 && static_cast<int64_t>(splits) * plane_bytes > workspace_bytes)
+      splits = static_cast<int>(workspace_bytes / plane_bytes);      // as many runs as the buffer holds
     if (splits > 1) {
       if (reinterpret_cast<uintptr_t>(workspace) & 255)
         return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
@@ -571,9 +623,24 @@ gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const vo
     }
     return tc_launch(L, st);
   }
-  if (desc->k > 0 && desc->alpha != 0.0 && fpu_eligible(*desc, a, b, c, d, epi))
-    return launch_fpu(h, *desc, epi, a, b, c, d, st);
-  return launch_simt(*desc, epi, a, b, c, d, st);
+  // The SIMT families have no batch index: one launch per product of the batch.
+  // (the FFMA kernel's vector loads need every product of a batch 16-byte aligned like the first)
+  auto stride_ok = [&](int64_t stride, int dtype) { return batch == 1 || (stride * dtype_size(dtype)) % 16 == 0; };
+  const bool fpu = desc->k > 0 && desc->alpha != 0.0 && fpu_eligible(*desc, a, b, c, d, epi) &&
+                   stride_ok(desc->batch_stride_a, desc->dtype_a) && stride_ok(desc->batch_stride_b, desc->dtype_b) &&
+                   stride_ok(desc->batch_stride_c, desc->dtype_c) && stride_ok(desc->batch_stride_d, desc->dtype_d);
+  for (int i = 0; i < batch; ++i) {
+    auto at = [i](const void* p, int64_t stride, int dtype) -> const void* {
+      return p ? static_cast<const char*>(p) + static_cast<size_t>(i) * stride * dtype_size(dtype) : nullptr;
+    };
+    const void* ai = at(a, desc->batch_stride_a, desc->dtype_a);
+    const void* bi = at(b, desc->batch_stride_b, desc->dtype_b);
+    const void* ci = at(c, desc->batch_stride_c, desc->dtype_c);
+    void* di = const_cast<void*>(at(d, desc->batch_stride_d, desc->dtype_d));
+    s = fpu ? launch_fpu(h, *desc, epi, ai, bi, ci, di, st) : launch_simt(*desc, epi, ai, bi, ci, di, st);
+    if (s != GK_OK) return s;
+  }
+  return GK_OK;
 }
 
 // Bytes an operand occupies, from its first to its last addressed element.
@@ -610,8 +677,8 @@ static cudaError_t copy_block(void* dst, const void* src, int64_t ld, size_t es,
 static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const void* a_host, const void* b_host,
                                      const void* c_host, void* d_host, const gk_epilogue_desc* epi, bool read_c,
                                      size_t a_bytes, size_t b_bytes, bool a_resident, cudaStream_t st) {
-  // chunk size: reserved[1] megabytes when set (a tuning aid), else 32 MiB
-  const size_t target = static_cast<size_t>(d.reserved[1] > 0 ? d.reserved[1] : 32) << 20;
+  // chunk size: host_chunk_mib megabytes when set (a tuning aid), else 32 MiB
+  const size_t target = static_cast<size_t>(d.host_chunk_mib > 0 ? d.host_chunk_mib : 32) << 20;
   auto chunks = [target](size_t bytes) {
     const int n = static_cast<int>((bytes + target / 2) / target);
     return std::max(1, std::min(n, 8));
@@ -678,7 +745,7 @@ static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const v
     const size_t c_off = (static_cast<size_t>(j0) * d.ldc + i0) * es_c;
     const size_t d_off = (static_cast<size_t>(j0) * d.ldd + i0) * es_d;
     const gk_status s = gk_gemm(h, &blk, a_dev + a_off, b_dev + b_off, read_c ? c_dev + c_off : nullptr, d_dev + d_off,
-                                epi ? &epi_blk : nullptr, nullptr, st);
+                                epi ? &epi_blk : nullptr, nullptr, 0, st);
     if (s != GK_OK) return s;
     GK_CUDA_CHECK(cudaEventRecord(h->events[ev], st));
     GK_CUDA_CHECK(cudaStreamWaitEvent(h->copy_out, h->events[ev], 0));
@@ -719,14 +786,16 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
                        const void* c_host, void* d_host, const gk_epilogue_desc* epi,
                        gk_stream stream) {
   clear_error();
-  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
   gk_status s = validate_desc(desc, epi);
   if (s != GK_OK) return s;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const gk_gemm_desc& d = *desc;
+  if ((s = check_pointers(d, epi, a_host, b_host, c_host, d_host)) != GK_OK) return s;
+  if (d.batch > 1) return set_error(GK_ERR_INVALID_CONFIG, "gk_gemm_host takes single products (batch = %d)", d.batch);
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
   const bool read_ab = d.layout_a == GK_LAYOUT_DENSE && d.layout_b == GK_LAYOUT_DENSE;
   const bool read_c = c_host != nullptr && d.layout_c == GK_LAYOUT_DENSE && d.beta != 0.0;
-  const bool a_resident = (d.reserved[2] & 1) != 0 && read_ab;   // `a_host` is a device pointer: A stays where it is
+  const bool a_resident = d.a_resident != 0 && read_ab;   // `a_host` is a device pointer: A stays where it is
   const size_t a_bytes = read_ab && !a_resident ? operand_bytes(d.lda, d.trans_a ? d.m : d.k, d.plane_a, d.number, d.dtype_a) : 0;
   const size_t b_bytes = read_ab ? operand_bytes(d.ldb, d.trans_b ? d.k : d.n, d.plane_b, d.number, d.dtype_b) : 0;
   const size_t c_bytes = read_c ? operand_bytes(d.ldc, d.n, d.plane_c, d.number, d.dtype_c) : 0;
@@ -758,7 +827,7 @@ gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host
     epi_use = &epi_dev;
   }
   s = gk_gemm(h, desc, a_resident ? a_host : h->stage_dev[0], h->stage_dev[1], read_c ? h->stage_dev[2] : nullptr,
-              h->stage_dev[3], epi_use, nullptr, stream);
+              h->stage_dev[3], epi_use, nullptr, 0, stream);
   if (s != GK_OK) return s;
   if (d_bytes) GK_CUDA_CHECK(cudaMemcpyAsync(d_host, h->stage_dev[3], d_bytes, cudaMemcpyDeviceToHost, st));
   GK_CUDA_CHECK(cudaStreamSynchronize(st));

@@ -174,7 +174,7 @@ static bool build_tc_problem(const gk_contract_desc& d, Groups g, const void* a,
   if (g.n.size() > 1 && g.n[0].extent % 32) return no("inner N mode is not a multiple of 32");
   pr->alpha = d.alpha; pr->beta = d.beta;
   pr->tile_n = d.tile_n; pr->cta_group = d.cta_group; pr->stages = d.stages;
-  pr->debug = d.reserved[0];
+  pr->debug = d.debug;
   return true;
 }
 
@@ -408,6 +408,8 @@ gk_status gk_contract(gk_handle h, const gk_contract_desc* desc, const void* a, 
                       void* d, void* workspace, int64_t workspace_bytes, gk_stream stream) {
   clear_error();
   if (!a || !b || !d) return set_error(GK_ERR_INVALID_ARGUMENT, "A, B or D is NULL");
+  if (desc && desc->beta != 0.0 && !c)
+    return set_error(GK_ERR_INVALID_ARGUMENT, "beta = %g but C is NULL (pass C, or beta = 0)", desc->beta);
   return contract_impl(h, desc, a, b, c, d, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), nullptr);
 }
 
@@ -418,6 +420,8 @@ gk_status gk_contract_static(const gk_contract_desc* desc, const void* a, const 
   if (!desc || desc->struct_size != sizeof(gk_contract_desc))
     return set_error(GK_ERR_INVALID_ARGUMENT, "gk_contract_desc.struct_size does not match this library (%zu)",
                      sizeof(gk_contract_desc));
+  if (desc->beta != 0.0 && !c)
+    return set_error(GK_ERR_INVALID_ARGUMENT, "beta = %g but C is NULL (pass C, or beta = 0)", desc->beta);
   if (desc->compute == GK_TF32)
     return set_error(GK_ERR_INVALID_CONFIG, "gk_contract_static runs the gather kernel only; TF32 needs the tensor cores");
   Groups g;

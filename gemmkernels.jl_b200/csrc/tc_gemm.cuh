@@ -67,6 +67,10 @@ struct TcParams {
   // workspace (split_stride elements apart) and a second kernel adds the planes and applies the epilogue.
   int32_t k_split, kb_per_split;
   int64_t split_stride;
+  // Strided-batched real products: work units run over (product, tile, k-run); an operand whose tensor
+  // map lists the batch as its third mode has x_batched = 1 (0: shared by all products).
+  int32_t batch, a_batched, b_batched;
+  int64_t c_batch, d_batch;  // elements between the C / D of consecutive products
   int32_t raster_group;      // cluster tiles along M (N for the horizontal raster) walked before stepping on
   int32_t raster_kind;       // 0 = bands down M, 1 = bands along N, 2 = Z-order (power-of-two tile grids)
   int32_t z_bits;            // Z-order: low bits interleaved per dimension (min of the two log2 extents)
@@ -337,7 +341,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const uint32_t tmem_base = *tmem_slot_gen;
   if (threadIdx.x == 0) tc_mark(p.status, p.debug, 1, 1);   // set-up done, TMEM allocated
 
-  const int num_tiles = p.tiles_m * p.tiles_n * p.k_split;   // work units
+  const int units_per_product = p.tiles_m * p.tiles_n * p.k_split;
+  const int num_tiles = units_per_product * p.batch;         // work units
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
   const int bn_cta = p.bn / CG;
@@ -388,8 +393,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       pdl_wait();           // operands may be the previous kernel's output
       for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
         int tm, tn;
-        tc_tile_coords(p, t / p.k_split, tm, tn);
+        const int bt = t / units_per_product;                 // which product of the batch
+        tc_tile_coords(p, (t - bt * units_per_product) / p.k_split, tm, tn);
         const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        [[maybe_unused]] const int c2 = pl + bt * (is_a ? p.a_batched : p.b_batched);   // plane, or product of a batch
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
         const int n_cta = tn * bn_tile + static_cast<int>(rank) * bn_cta;
         const int mn = (is_a ? m_cta : n_cta) + mn_add;
@@ -429,8 +436,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
               } else {
                 const int c0 = mn_major ? mn : k0;
                 const int c1 = mn_major ? k0 : mn;
-                if constexpr (CG == 2) tma_load_3d_pair(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
-                else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, pl);
+                if constexpr (CG == 2) tma_load_3d_pair(dst, tmap, full0_signal + 8u * s, c0, c1, c2);
+                else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, c2);
               }
             }
           }
@@ -587,7 +594,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
     const bool prefetch_c = has_c && p.m_div >= p.M && p.n_div >= p.N && p.c_sm0 == 1 && (PLANES == 1 || p.c_plane != 0);
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
       int tm, tn;
-      tc_tile_coords(p, t / p.k_split, tm, tn);
+      const int bt = t / units_per_product;
+      tc_tile_coords(p, (t - bt * units_per_product) / p.k_split, tm, tn);
       const int64_t split_off = static_cast<int64_t>(t % p.k_split) * p.split_stride;
       const int m = (tm * CG + static_cast<int>(rank)) * kTcTileM + q * 32 + lane;
       const int n0 = tn * bn_tile;
@@ -599,7 +607,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         const int m0 = m - lane;
         if (m0 < p.M) {
           const size_t es_c = p.dtype_c == TC_F32 ? 4 : 2;
-          const char* c_line = static_cast<const char*>(p.C) + static_cast<size_t>(m0) * es_c;
+          const char* c_line = static_cast<const char*>(p.C) + (static_cast<size_t>(m0) + static_cast<size_t>(bt) * p.c_batch) * es_c;
           for (int c = lane + chunk_first; c < bn_tile && n0 + c < p.N; c += chunk_step) {
 #pragma unroll
             for (int pl = 0; pl < PLANES; ++pl)
@@ -623,8 +631,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       float bias_row = 0.0f;
       if (p.bias_axis == TC_BIAS_ROW && m_ok) bias_row = p.bias[m];
       const int m_in = m % p.m_div, m_out = m / p.m_div;
-      const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1;
-      const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1;
+      const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch;
+      const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1 + bt * p.c_batch;
       for (int c = chunk_first; c < bn_tile; c += chunk_step) {
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)

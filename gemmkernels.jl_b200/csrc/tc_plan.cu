@@ -37,6 +37,8 @@ bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::strin
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
     return no("operand base address is not 16-byte aligned");
   if ((d.lda * es) % 16 || (d.ldb * es) % 16) return no("leading dimension is not a multiple of 16 bytes");
+  if (d.batch > 1 && ((d.batch_stride_a * es) % 16 || (d.batch_stride_b * es) % 16))
+    return no("batch stride is not a multiple of 16 bytes");
   if (d.number != GK_REAL) {
     if (d.plane_a == 0 || d.plane_b == 0) return no("interleaved complex operands need the split pre-pass");
     if ((d.plane_a * es) % 16 || (d.plane_b * es) % 16) return no("plane stride is not a multiple of 16 bytes");
@@ -46,7 +48,7 @@ bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::strin
 
 // Plain matrix operand -> 3-D tensor map {contiguous, strided, plane}.
 static gk_status encode_plain(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, int box_contig,
-                              int box_other, CUtensorMapSwizzle swizzle) {
+                              int box_other, CUtensorMapSwizzle swizzle, int batch = 1, int64_t batch_stride = 0) {
   const int es = dtype_size(op.dtype);
   CUtensorMapDataType tdt = op.dtype == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                             : op.dtype == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -58,6 +60,10 @@ static gk_status encode_plain(gk_handle h, CUtensorMap* tm, const TcOperand& op,
   cuuint64_t strides[2];
   strides[0] = static_cast<cuuint64_t>(o_str) * es;
   strides[1] = planes > 1 ? static_cast<cuuint64_t>(op.plane_stride) * es : strides[0] * dims[1];
+  if (planes == 1 && batch > 1 && batch_stride > 0) {   // the third mode walks the products of a batch
+    dims[2] = static_cast<cuuint64_t>(batch);
+    strides[1] = static_cast<cuuint64_t>(batch_stride) * es;
+  }
   cuuint32_t box[3] = {static_cast<cuuint32_t>(box_contig), static_cast<cuuint32_t>(box_other), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = h->encode_tiled(tm, tdt, 3, const_cast<void*>(op.ptr), dims, strides, box, estr,
@@ -190,7 +196,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
     const int64_t tm = (pr.M + 128 * c.cg - 1) / (128 * c.cg);
     const int64_t tn = (pr.N + c.bn * c.n_sub - 1) / (c.bn * c.n_sub);
     const int64_t slots = std::max(1, sm_count / c.cg);
-    const int64_t waves = (tm * tn + slots - 1) / slots;
+    const int64_t waves = (tm * tn * std::max(1, pr.batch) + slots - 1) / slots;
     // a single accumulator stage exposes the epilogue: worth it only when the main loop is long
     double eff = c.eff;
     if (c.n_sub * planes * c.bn > 256) {
@@ -232,7 +238,11 @@ void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, co
   pr.c_plane = d.plane_c; pr.d_plane = d.plane_d;
   pr.alpha = d.alpha; pr.beta = d.beta; pr.epi = epi;
   pr.tile_n = d.tile_n; pr.cta_group = d.cta_group; pr.stages = d.stages; pr.raster = d.raster;
-  pr.raster_group = d.raster_group; pr.max_ctas = d.max_ctas; pr.debug = d.reserved[0];
+  pr.raster_group = d.raster_group; pr.max_ctas = d.max_ctas; pr.debug = d.debug;
+  if (d.batch > 1) {
+    pr.batch = d.batch;
+    pr.batch_a = d.batch_stride_a; pr.batch_b = d.batch_stride_b; pr.batch_c = d.batch_stride_c; pr.batch_d = d.batch_stride_d;
+  }
 }
 
 static int32_t clamp_div(int64_t ext0, int64_t ext1) {
@@ -272,6 +282,14 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
     p.kb_per_split = (p.k_blocks + pr.k_split - 1) / pr.k_split;
     p.k_split = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;   // no empty runs
     p.split_stride = pr.split_stride;
+  }
+  p.batch = 1;
+  if (pr.batch > 1) {
+    if (planes != 1 || pr.rank5 || pr.k_split > 1)
+      return set_error(GK_ERR_INVALID_CONFIG, "batched products are plain real products without split-K");
+    p.batch = pr.batch;
+    p.a_batched = pr.batch_a > 0 ? 1 : 0; p.b_batched = pr.batch_b > 0 ? 1 : 0;
+    p.c_batch = pr.batch_c; p.d_batch = pr.batch_d;
   }
   p.tiles_m = (p.M + kTcTileM * cg - 1) / (kTcTileM * cg);
   p.tiles_n = (p.N + bn * n_sub - 1) / (bn * n_sub);
@@ -463,7 +481,9 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
   out->kernel = tc_kernel_select(cg, planes, tf32, pr.rank5);
 
   // persistent grid
-  const int tiles = p.tiles_m * p.tiles_n * p.k_split;
+  const int64_t tiles64 = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.k_split * p.batch;
+  if (tiles64 > INT32_MAX) return set_error(GK_ERR_INVALID_CONFIG, "too many work units (%lld)", (long long)tiles64);
+  const int tiles = static_cast<int>(tiles64);
   int slots;
   {
     std::lock_guard<std::mutex> lock(h->mu);
@@ -503,9 +523,11 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) 
       if (s != GK_OK) return s;
       s = encode_modes(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, b_row_mode, b_rows, b_tma);
     } else {
-      s = encode_plain(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, p.a_mn_major ? p.bk : kTcTileM, a_tma);
+      s = encode_plain(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, p.a_mn_major ? p.bk : kTcTileM, a_tma,
+                       pr.batch, pr.batch_a);
       if (s != GK_OK) return s;
-      s = encode_plain(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, p.b_mn_major ? p.bk : bn_cta, b_tma);
+      s = encode_plain(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, p.b_mn_major ? p.bk : bn_cta, b_tma,
+                       pr.batch, pr.batch_b);
     }
     if (s != GK_OK) return s;
   }

@@ -38,6 +38,9 @@ struct TcProblem {
   // FP32 workspace of k_split planes, split_stride elements apart, and C, bias and activation are left out
   int32_t k_split = 0;
   int64_t split_stride = 0;
+  // strided-batched real products (plain matrices only): operand strides in elements, 0 = shared
+  int32_t batch = 1;
+  int64_t batch_a = 0, batch_b = 0, batch_c = 0, batch_d = 0;
 };
 
 // How many runs to cut K into for this problem on this GPU: 1 unless the tiles fill less than half of the

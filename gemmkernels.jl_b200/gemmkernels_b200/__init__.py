@@ -25,12 +25,12 @@ from .contract import BoundContraction, bind_contract, contract_, contract_query
 from .config import Config, ConfigError, DimensionMismatch, get_config, heuristic_block_shape
 from .eltypes import (BFloat16, ComplexF16, ComplexF32, Float16, Float32, Float64, Int16, Int32, Int64)
 from .matmul import (BoundMatmul, DeviceTimeout, GemmKernelsError, bind, create_config, handle, lower, matmatmul_,
-                     matmul, matmul_host, mul_, poll_status, query)
+                     matmul, matmul_batched, matmul_host, mul_, poll_status, query)
 
 __all__ = [
     "CTASwizzle", "Epilogue", "Kernel", "Layout", "Operator", "Transform",
     "Config", "ConfigError", "DimensionMismatch", "get_config", "heuristic_block_shape",
-    "contract_", "contract_query", "bind_contract", "BoundContraction", "matmul", "bind", "BoundMatmul", "matmul_host", "matmatmul_", "mul_", "query", "lower", "create_config", "handle", "poll_status",
+    "contract_", "contract_query", "bind_contract", "BoundContraction", "matmul", "matmul_batched", "bind", "BoundMatmul", "matmul_host", "matmatmul_", "mul_", "query", "lower", "create_config", "handle", "poll_status",
     "cuarray", "to_cuarray", "to_numpy",
     "Float16", "BFloat16", "Float32", "Float64", "Int16", "Int32", "Int64", "ComplexF16", "ComplexF32",
     "GemmKernelsError", "DeviceTimeout",

@@ -47,7 +47,10 @@ class GemmDesc(C.Structure):
         ("alpha", C.c_double), ("beta", C.c_double),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32),
         ("raster_group", C.c_int32), ("max_ctas", C.c_int32),
-        ("reserved", C.c_int32 * 3),
+        ("debug", C.c_int32), ("host_chunk_mib", C.c_int32), ("a_resident", C.c_int32),
+        ("batch", C.c_int32),
+        ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_c", C.c_int64),
+        ("batch_stride_d", C.c_int64),
     ]
 
     def __init__(self, **kw):
@@ -87,7 +90,7 @@ class ContractDesc(C.Structure):
         ("compute", C.c_int32), ("force_gather", C.c_int32),
         ("alpha", C.c_double), ("beta", C.c_double),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32),
-        ("reserved", C.c_int32 * 3),
+        ("debug", C.c_int32), ("reserved", C.c_int32 * 2),
     ]
 
     def __init__(self, **kw):
@@ -115,7 +118,7 @@ def _load() -> C.CDLL:
     lib.gk_gemm_query.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(EpilogueDesc), C.POINTER(GemmPlan)]
     lib.gk_gemm.restype = C.c_int
     lib.gk_gemm.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
-                            C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p, C.c_void_p]
+                            C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p, C.c_int64, C.c_void_p]
     lib.gk_gemm_host.restype = C.c_int
     lib.gk_gemm_host.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p]

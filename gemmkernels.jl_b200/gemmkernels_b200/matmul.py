@@ -247,16 +247,54 @@ def _wants_workspace(desc) -> bool:
     return desc.m * desc.n <= (1 << 22) and desc.k >= 2048
 
 
-def _auto_workspace(h, desc, epi, like):
-    """A torch-allocated workspace of the size gk_gemm_query reports, or None."""
+# Scratch buffers the package lends to gk_gemm when the caller passes none: one per (device, stream),
+# allocated on first need, replaced only by a larger one, never per call.  Kernels that use a buffer
+# are ordered by the stream it belongs to, so successive calls on that stream may share it.
+_workspaces: dict = {}
+_workspaces_lock = threading.Lock()
+
+
+def _workspace_bytes(ws) -> int:
+    return 0 if ws is None else ws.numel() * ws.element_size()
+
+
+def _check_user_workspace(h, desc, epi, workspace):
+    """A workspace the caller supplies must cover what gk_gemm_query reports when the library cannot
+    do without it (interleaved operands); for the optional uses the library itself falls back."""
+    import torch
+    if desc.number != L.GK_REAL and (desc.plane_a == 0 or desc.plane_b == 0):
+        plan = L.GemmPlan()
+        st = L.lib.gk_gemm_query(h, C.byref(desc), C.byref(epi), C.byref(plan))
+        if st != L.GK_OK:
+            _raise(st)
+        if _workspace_bytes(workspace) < plan.workspace_bytes:
+            raise GemmKernelsError(f"workspace holds {_workspace_bytes(workspace)} bytes, this product needs {plan.workspace_bytes}")
+    if workspace.data_ptr() % 256:
+        raise GemmKernelsError("workspace must be 256-byte aligned")
+
+
+def _auto_workspace(h, desc, epi, like, stream: int):
+    """The lent workspace of (device, stream), grown to the size gk_gemm_query reports, or None."""
     import torch
     plan = L.GemmPlan()
     st = L.lib.gk_gemm_query(h, C.byref(desc), C.byref(epi), C.byref(plan))
     if st != L.GK_OK:
         _raise(st)
-    if plan.workspace_bytes:
-        return torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=like.device)
-    return None
+    if not plan.workspace_bytes:
+        return None
+    key = (like.device.index, int(stream))
+    with _workspaces_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < plan.workspace_bytes:
+            # allocate under the caller's stream so the caching allocator ties the block to it
+            size = max(plan.workspace_bytes, 2 * (ws.numel() if ws is not None else 0))
+            if int(stream) == torch.cuda.current_stream(like.device).cuda_stream:
+                ws = torch.empty(size, dtype=torch.uint8, device=like.device)
+            else:
+                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream), device=like.device)):
+                    ws = torch.empty(size, dtype=torch.uint8, device=like.device)
+            _workspaces[key] = ws
+    return ws
 
 
 def matmul(conf: Config, a, b, c, d, *,
@@ -279,10 +317,48 @@ def matmul(conf: Config, a, b, c, d, *,
     dev = d.device.index if d.device.index is not None else torch.cuda.current_device()
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
-        if workspace is None and _wants_workspace(desc):
-            workspace = _auto_workspace(handle(dev), desc, epi, d)
+        if workspace is not None:
+            _check_user_workspace(handle(dev), desc, epi, workspace)
+        elif _wants_workspace(desc):
+            workspace = _auto_workspace(handle(dev), desc, epi, d, s)
         ws = workspace.data_ptr() if workspace is not None else None
-        st = L.lib.gk_gemm(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), ws, C.c_void_p(s))
+        st = L.lib.gk_gemm(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), ws, _workspace_bytes(workspace),
+                           C.c_void_p(s))
+    if st != L.GK_OK:
+        _raise(st)
+    return None
+
+
+def matmul_batched(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul_singlestage, stream=None,
+                   **transforms):
+    """`batch` independent products of one shape in one launch: D[:, :, i] = epilogue(A[:, :, i] * B[:, :, i]
+    + C[:, :, i]).  `d` is a 3-D column-major array (M, N, batch); `a`, `b` and `c` are 3-D with the same
+    last extent, or 2-D to share one matrix between all products (`c` may be None).  `conf` describes
+    one product.  The reference has no batched entry point; on the tensor-core path the persistent
+    scheduler walks (product, tile) pairs, so small products fill the GPU together."""
+    import torch
+    if d.dim() != 3:
+        raise DimensionMismatch("matmul_batched: D must be (M, N, batch)")
+    nb = d.shape[2]
+    if nb == 0:
+        return None
+
+    def first(x, name):
+        if x is None or x.dim() == 2:
+            return x, 0
+        if x.dim() != 3 or x.shape[2] != nb:
+            raise DimensionMismatch(f"matmul_batched: {name} has shape {tuple(x.shape)}, expected a last extent of {nb}")
+        return x[:, :, 0], (x.stride(2) if nb > 1 else 0)
+
+    (a0, sa), (b0, sb), (c0, sc), (d0, sd) = first(a, "A"), first(b, "B"), first(c, "C"), first(d, "D")
+    hooks = {k.replace("transform_", ""): v for k, v in transforms.items()}
+    desc, epi, (pa, pb, pc, pd) = lower(conf, a0, b0, c0, d0, hooks, epilogue or Epilogue.Default(), kernel)
+    desc.batch = nb
+    desc.batch_stride_a, desc.batch_stride_b, desc.batch_stride_c, desc.batch_stride_d = sa, sb, sc, sd
+    dev = d.device.index if d.device.index is not None else torch.cuda.current_device()
+    s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        st = L.lib.gk_gemm(handle(dev), C.byref(desc), pa, pb, pc, pd, C.byref(epi), None, 0, C.c_void_p(s))
     if st != L.GK_OK:
         _raise(st)
     return None
@@ -301,10 +377,19 @@ class BoundMatmul:
         self.device = d.device.index if d.device.index is not None else torch.cuda.current_device()
         with torch.cuda.device(self.device):
             self.handle = handle(self.device)
-            if workspace is None and _wants_workspace(self.desc):
-                workspace = _auto_workspace(self.handle, self.desc, self.epi, d)
-                self._keep += (workspace,)
+            if workspace is not None:
+                _check_user_workspace(self.handle, self.desc, self.epi, workspace)
+            elif _wants_workspace(self.desc):
+                # a bound product owns its scratch: it may be replayed on any stream
+                plan = L.GemmPlan()
+                st = L.lib.gk_gemm_query(self.handle, C.byref(self.desc), C.byref(self.epi), C.byref(plan))
+                if st != L.GK_OK:
+                    _raise(st)
+                if plan.workspace_bytes:
+                    workspace = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=d.device)
+                    self._keep += (workspace,)
         self.ws = workspace.data_ptr() if workspace is not None else None
+        self.ws_bytes = _workspace_bytes(workspace)
         self._torch = torch
 
     def __call__(self, stream=None):
@@ -312,7 +397,8 @@ class BoundMatmul:
         device that holds D; that device must be current."""
         s = stream if stream is not None else self._torch.cuda.current_stream(self.device).cuda_stream
         pa, pb, pc, pd = self.ptrs
-        st = L.lib.gk_gemm(self.handle, C.byref(self.desc), pa, pb, pc, pd, C.byref(self.epi), self.ws, C.c_void_p(s))
+        st = L.lib.gk_gemm(self.handle, C.byref(self.desc), pa, pb, pc, pd, C.byref(self.epi), self.ws, self.ws_bytes,
+                           C.c_void_p(s))
         if st != L.GK_OK:
             _raise(st)
 
@@ -335,7 +421,7 @@ def matmul_host(conf: Config, a, b, c, d, *, epilogue=None, kernel=Kernel.matmul
     epilogue = epilogue or Epilogue.Default()
     desc, epi, (pa, pb, pc, pd) = lower(conf, a, b, c, d, hooks, epilogue, kernel)
     if a_on_device:
-        desc.reserved[2] |= 1          # A is a device array already (resident or just broadcast): used in place
+        desc.a_resident = 1            # A is a device array already (resident or just broadcast): used in place
     dev = device_index if device_index is not None else torch.cuda.current_device()
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):

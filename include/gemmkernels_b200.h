@@ -30,7 +30,7 @@ extern "C" {
 #endif
 
 #define GK_VERSION_MAJOR 0
-#define GK_VERSION_MINOR 1
+#define GK_VERSION_MINOR 2
 
 typedef struct gk_handle_s* gk_handle;
 typedef void* gk_stream; /* a CUstream / cudaStream_t; NULL = the legacy default stream */
@@ -119,11 +119,18 @@ typedef struct gk_gemm_desc {
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t raster_group; /* T of the tiled rasters */
   int32_t max_ctas;     /* cap on the persistent grid */
-  int32_t reserved[3];  /* [0]: diagnostic bits, 0 in production (1 no TMA, 2 no MMA, 4 idle producers: lets the
-                           bounded waits run out, 8 per-role cycle counters into the workspace, 16 progress
-                           marks for gk_debug_marks); [1]: gk_gemm_host chunk size in MiB (0 = 32);
-                           [2]: gk_gemm_host only, bit 0: `a_host` is a device pointer (A already resident,
-                           e.g. after a broadcast from another rank) and is used in place */
+  int32_t debug;        /* diagnostic bits, 0 in production: 1 no TMA, 2 no MMA, 4 idle producers (lets the
+                           bounded waits run out), 8 per-role cycle counters into the workspace, 16 progress
+                           marks for gk_debug_marks */
+  int32_t host_chunk_mib; /* gk_gemm_host only: size of the upload / download chunks in MiB (0 = 32) */
+  int32_t a_resident;   /* gk_gemm_host only: 1 = `a_host` is a DEVICE pointer (A is already resident, e.g.
+                           after a broadcast from another rank) and is used in place, not uploaded */
+  /* Strided-batched products: `batch` independent GEMMs of the same shape, operand x of product i at
+   * x + i * batch_stride_x elements (batch_stride_a / _b = 0 shares that operand between the products).
+   * batch <= 1 is the single product.  Real number system only; tensor-core operands need batch
+   * strides that are multiples of 16 bytes.  The reference has no batched entry point. */
+  int32_t batch;
+  int64_t batch_stride_a, batch_stride_b, batch_stride_c, batch_stride_d;
 } gk_gemm_desc;
 
 typedef struct gk_epilogue_desc {
@@ -175,15 +182,17 @@ GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_e
 
 /* Enqueues one GEMM on `stream`.  a, b, c, d are device pointers (c may be NULL when beta == 0 or
  * layout_c is ZERO; c == d is allowed).  epi may be NULL.  workspace is a 256-byte aligned device
- * buffer of at least plan.workspace_bytes bytes (NULL when that is 0).  It is REQUIRED when complex /
- * dual A or B are interleaved (plane_a / plane_b == 0): they are split into planes there first, on the
- * same stream.  It is OPTIONAL for real tensor-core products with few output tiles and a long K, for
- * which gk_gemm_query also reports a size: given the buffer, K is cut into runs over the otherwise
- * idle SMs (split-K: FP32 partial sums in the workspace, one reduction pass that applies alpha, beta,
- * bias and activation); with NULL the same product runs unsplit. */
+ * buffer of workspace_bytes bytes (NULL / 0 when there is none); gk_gemm_query reports in
+ * plan.workspace_bytes how much the descriptor can use.  It is REQUIRED when complex / dual A or B
+ * are interleaved (plane_a / plane_b == 0): they are split into planes there first, on the same
+ * stream; a buffer that is too small is refused with GK_ERR_INVALID_ARGUMENT.  It is OPTIONAL for
+ * tensor-core products with few output tiles and a long K: given enough room, K is cut into runs over
+ * the otherwise idle SMs (split-K: FP32 partial sums in the workspace, one reduction pass that
+ * applies alpha, beta, bias and activation); with NULL, or with a buffer smaller than the partial
+ * sums need, the same product runs unsplit.  Nothing is ever written beyond workspace_bytes. */
 GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
-                  gk_stream stream);
+                  int64_t workspace_bytes, gk_stream stream);
 
 /*
  * Tensor contraction (GETT): D[modes_c] = alpha * sum over contracted modes of A[modes_a] * B[modes_b]
@@ -212,7 +221,8 @@ typedef struct gk_contract_desc {
   int32_t force_gather; /* 1 = always use the gather kernel (testing) */
   double alpha, beta;
   int32_t tile_n, cta_group, stages; /* tuning overrides, 0 = choose */
-  int32_t reserved[3];
+  int32_t debug;        /* diagnostic bits as in gk_gemm_desc.debug, 0 in production */
+  int32_t reserved[2];
 } gk_contract_desc;
 
 GK_API gk_status gk_contract_query(gk_handle h, const gk_contract_desc* desc, gk_gemm_plan* plan);

@@ -8,6 +8,7 @@ sqrt(eps(T)) (test/blas.jl:36,65).  Integer results must be bit-exact.
 """
 import ctypes as C
 import importlib.util
+import itertools
 import math
 from pathlib import Path
 
@@ -172,9 +173,9 @@ BLAS_TYPES = [("Float16", "Float32", True, 128), ("Float16", "Float16", True, 25
 def test_blas_matmatmul(ab, cd, wmma, min_dim, ta, tb):
     rng = np.random.default_rng(hash((ab, cd, ta, tb)) % 2 ** 32)
     AB, CD = getattr(GK, ab), getattr(GK, cd)
-    sizes = [(10, 10, 10), (min_dim, min_dim, min_dim), (1000, 1000, 1000), (10, min_dim, 1000), (1000, 10, min_dim),
-             (min_dim, 1000, 10)]
-    for (M, N, K) in sizes:
+    # all 27 combinations of test/blas.jl:19-21
+    dims = (10, min_dim, 1000)
+    for (M, N, K) in itertools.product(dims, dims, dims):
         alpha, beta = float(rng.random()), float(rng.random())
         A = (rng.random((K, M) if ta == "T" else (M, K)) / math.sqrt(K)).astype(AB.np_dtype)
         B = (rng.random((N, K) if tb == "T" else (K, N)) / math.sqrt(K)).astype(AB.np_dtype)
@@ -475,10 +476,84 @@ def test_split_k_for_few_tiles_and_long_k(M, N, K, ta, cd, beta, bias_axis, act)
         hooks["shared_to_global_d"] = Transform.Elementwise(act)
     desc, epi_desc, (pa, pb, pc, _) = GK.lower(conf, a_dev, dev(B), c, d2, hooks, epi or Epilogue.Default(), Kernel.matmul_singlestage)
     B_d = dev(B)
-    assert L.lib.gk_gemm(GK.handle(), C.byref(desc), a_dev.data_ptr(), B_d.data_ptr(), pc, d2.data_ptr(), C.byref(epi_desc), None,
+    assert L.lib.gk_gemm(GK.handle(), C.byref(desc), a_dev.data_ptr(), B_d.data_ptr(), pc, d2.data_ptr(), C.byref(epi_desc), None, 0,
                          C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
     torch.cuda.synchronize(); GK.poll_status()
     assert torch.equal(d2, d) if cd == "Float32" else O.normwise_error(GK.to_numpy(d2).astype(np.float64), want) <= 1e-3
+
+
+def test_split_k_never_writes_past_a_small_workspace():
+    """A workspace smaller than the partial sums need is used for as many K-runs as it holds (or not
+    at all); a canary directly behind it must survive, and the result is the same product."""
+    M, N, K = 256, 256, 16384
+    rng = np.random.default_rng(9)
+    A = rng.integers(-2, 3, (M, K)).astype(np.float16); B = rng.integers(-2, 3, (K, N)).astype(np.float16)
+    a, b = dev(A), dev(B)
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                         global_a_layout=Layout.ColMajor[GK.Float16], global_c_layout=Layout.Zero[GK.Float32],
+                         global_d_layout=Layout.ColMajor[GK.Float32])
+    want = O.gemm(A, B)
+    full = GK.query(conf, a, b, None, GK.cuarray(GK.Float32, M, N)).workspace_bytes
+    assert full >= 2 * M * N * 4
+    for ws_bytes in (full, 3 * M * N * 4, M * N * 4 + 4096, 4096):
+        buf = torch.zeros(ws_bytes + 4096, dtype=torch.uint8, device="cuda")
+        buf[ws_bytes:] = 0xA5
+        d = GK.cuarray(GK.Float32, M, N)
+        desc, epi_desc, (pa, pb, pc, pd) = GK.lower(conf, a, b, None, d, {}, Epilogue.Default(), Kernel.matmul_singlestage)
+        st = L.lib.gk_gemm(GK.handle(), C.byref(desc), pa, pb, pc, pd, C.byref(epi_desc), buf.data_ptr(), ws_bytes,
+                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert st == L.GK_OK, L.last_error()
+        torch.cuda.synchronize(); GK.poll_status()
+        assert torch.all(buf[ws_bytes:] == 0xA5), ws_bytes
+        assert np.array_equal(GK.to_numpy(d), want), ws_bytes
+
+
+@pytest.mark.parametrize("ab,op", [("Float16", "tc"), ("Float32", "fpu"), ("Int32", "simt")])
+@pytest.mark.parametrize("share_b", [False, True])
+def test_strided_batched_products(ab, op, share_b):
+    """`batch` products in one call: tensor cores walk (product, tile) pairs in one launch, the SIMT
+    families launch once per product.  Operands padded between the products; B optionally shared."""
+    M, N, K, nb = 384, 320, 192, 5
+    if op == "fpu":
+        M, N, K = 256, 128, 64
+    rng = np.random.default_rng(11)
+    ET = getattr(GK, ab); CD = GK.Int32 if ab == "Int32" else GK.Float32
+    A = rng.integers(-3, 4, (nb, M, K)).astype(ET.np_dtype)
+    B = rng.integers(-3, 4, (1 if share_b else nb, K, N)).astype(ET.np_dtype)
+    Cm = rng.integers(-5, 6, (nb, M, N)).astype(CD.np_dtype)
+
+    def batched(x, pad):
+        # (nb, r, c) numpy -> device (r, c, nb) with `pad` unused elements between the matrices
+        nbx, r, c = x.shape
+        store = torch.zeros(nbx, r * c + pad, dtype=torch.from_numpy(x[:1]).dtype, device="cuda")
+        store[:, : r * c] = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 1))).reshape(nbx, r * c).cuda()
+        return store[:, : r * c].view(nbx, c, r).permute(2, 1, 0), store
+
+    a, _ = batched(A, 64)
+    b, _ = batched(B, 128)
+    if share_b:
+        b = b[:, :, 0]
+    c, _ = batched(Cm, 32)
+    d, d_store = batched(np.zeros_like(Cm), 96)
+    if op == "tc":
+        oper = Operator.TCGen05Operator[ET, CD]
+    else:
+        oper = Operator.FPUOp[8, 8, 1, 4, 8, 1, ET, CD]
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=oper, global_a_layout=Layout.ColMajor[ET],
+                         global_b_layout=Layout.ColMajor[ET], global_c_layout=Layout.ColMajor[CD],
+                         global_d_layout=Layout.ColMajor[CD], **({"block_shape": (64, 64, 32)} if op != "tc" else {}))
+    GK.matmul_batched(conf, a, b, c, d, transform_shared_to_regs_a=Transform.Elementwise(Transform.Scale(2)))
+    torch.cuda.synchronize(); GK.poll_status()
+    got = GK.to_numpy(d)
+    for i in range(nb):
+        Bi = B[0 if share_b else i]
+        if ab == "Int32":
+            want = O.integer_gemm(A[i], Bi, Cm[i], 2, 1)
+        else:
+            want = O.gemm(A[i], Bi, Cm[i], 2.0, 1.0)
+        assert np.array_equal(got[:, :, i], want), i        # small integers: exact
+    # the padding between the outputs is untouched
+    assert torch.all(d_store[:, M * N:] == 0)
 
 
 def test_chained_products_without_host_synchronisation():
@@ -530,9 +605,9 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     d = GK.cuarray(GK.Float32, n, n)
     desc = L.GemmDesc(number=0, m=n, n=n, k=n, dtype_a=L.GK_F16, dtype_b=L.GK_F16, dtype_c=L.GK_F32, dtype_d=L.GK_F32,
                       compute=L.GK_F16, op=L.GK_OP_TCGEN05, lda=n, ldb=n, ldc=n, ldd=n, alpha=1.0, cta_group=1, tile_n=128)
-    desc.reserved[0] = 4          # measurement/test aid: producers skip their copies
+    desc.debug = 4                # measurement/test aid: producers skip their copies
     h = GK.handle()
-    st = L.lib.gk_gemm(h, C.byref(desc), a.data_ptr(), a.data_ptr(), None, d.data_ptr(), None, None,
+    st = L.lib.gk_gemm(h, C.byref(desc), a.data_ptr(), a.data_ptr(), None, d.data_ptr(), None, None, 0,
                        C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == L.GK_OK
     torch.cuda.synchronize()

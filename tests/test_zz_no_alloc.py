@@ -74,6 +74,21 @@ def test_static_contraction_refuses_sizes_beyond_its_array():
     assert st == L.GK_ERR_INVALID_CONFIG
     msg = L.last_error()
     assert "36864" in msg and str(L.GK_STATIC_TABLE_ENTRIES) in msg and "gk_contract" in msg
-    # the largest square case that fits does run
-    n = 4096
-    assert 8 * n == L.GK_STATIC_TABLE_ENTRIES
+
+
+def test_static_contraction_runs_when_the_tables_fill_the_array_exactly():
+    """3*M + 3*N + 2*K == GK_STATIC_TABLE_ENTRIES: the largest case the fixed array holds is launched
+    (a short K keeps it cheap) and must agree with gk_contract and with the oracle."""
+    M = N = 5456
+    K = 16
+    assert 3 * M + 3 * N + 2 * K == L.GK_STATIC_TABLE_ENTRIES
+    rng = np.random.default_rng(43)
+    A = (rng.random((M, K)) * 2 - 1).astype(np.float16)
+    B = (rng.random((K, N)) * 2 - 1).astype(np.float16)
+    got, ref = _run_both(A, "ik", B, "kj", "ij", (M, N))
+    assert O.normwise_error(got, ref) <= TOL
+    assert O.normwise_error(got, O.gemm(A, B)) <= TOL
+    # one entry more is refused
+    a = GK.cuarray(GK.Float16, M + 1, K); b = GK.cuarray(GK.Float16, K, N); d = GK.cuarray(GK.Float32, M + 1, N)
+    desc = _desc(d, "ij", a, "ik", b, "kj", 1.0, 0.0, None, None, False, 0, 0)
+    assert L.lib.gk_contract_static(C.byref(desc), a.data_ptr(), b.data_ptr(), None, d.data_ptr(), _stream()) == L.GK_ERR_INVALID_CONFIG
