@@ -28,6 +28,11 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+if "reference" in sys.argv:
+    # the CPU arm uses every host core: torchrun exports OMP_NUM_THREADS=1 to its workers, which would
+    # pin the BLAS pool to one thread before numpy is even imported
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
 sys.path.insert(0, str(ROOT / "gemmkernels.jl_b200"))
 
 import numpy as np  # noqa: E402
@@ -49,17 +54,14 @@ def measured_peaks():
     return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-def workload_config(n_gpus: int, workload: str = "c0") -> dict:
-    if workload == "c5":
-        n = 16384
-        return {"workload": f"c5: C=A*B, A,B BFloat16 N(0,0.02) {n}x{n} col-major, C Float32; column blocks of B,C over "
-                            f"{n_gpus} rank(s) ({n // n_gpus} columns each), A broadcast once (NCCL), resident",
-                "m": n, "n_total": n, "k": n, "operator": "TCGen05Operator{BFloat16,Float32}",
-                "l2": "operands and output per GPU are larger than L2; no flush between steps"}
+def workload_config(n_gpus: int) -> dict:
+    cols = N_DIM // n_gpus
     return {"workload": f"c0: C=A*B, A,B Float16 U[0,1) {N_DIM}x{N_DIM} col-major, C Float32, alpha=1 beta=0"
-                        + (f"; column blocks of B,C over {n_gpus} ranks, A broadcast once (NCCL), resident" if n_gpus > 1 else ""),
-            "m": N_DIM, "n_per_gpu": N_DIM, "k": N_DIM, "operator": "TCGen05Operator{Float16,Float32}",
-            "l2": "inputs and output (512 MiB per GPU) are larger than L2; no flush between steps"}
+                        + (f"; split by column blocks of B,C over {n_gpus} ranks ({cols} columns each), A resident on every rank "
+                           "(broadcast once through the library, timed separately)" if n_gpus > 1 else ""),
+            "m": N_DIM, "n_total": N_DIM, "n_per_gpu": cols, "k": N_DIM, "operator": "TCGen05Operator{Float16,Float32}",
+            "l2": "inputs and output (512 MiB in all) are larger than L2; no flush between steps"
+                  if n_gpus <= 2 else "per-GPU working set fits L2 at this N (strong scaling of a fixed 8192^3 product); no flush"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -72,19 +74,24 @@ def cpu_sgemm_sample(cols: int, reps: int, warmup: int):
     A, B = O.inputs_fp16_uniform01(0, N_DIM, cols, N_DIM)
     a32, b32 = A.astype(np.float32), B.astype(np.float32)
     threads = os.cpu_count() or 1
+    import contextlib
+    limit = contextlib.nullcontext()
     try:
-        from threadpoolctl import threadpool_info
-        blas = [p for p in threadpool_info() if p.get("user_api") == "blas"]
-        if blas:
-            threads = int(blas[0]["num_threads"])
+        from threadpoolctl import threadpool_info, threadpool_limits
+        limit = threadpool_limits(limits=threads, user_api="blas")      # every core, whatever the environment said
     except Exception:
-        pass
-    for _ in range(warmup):
-        O.gemm(a32, b32)
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        O.gemm(a32, b32)
-    dt = (time.perf_counter() - t0) / max(reps, 1)
+        threadpool_info = None
+    with limit:
+        if threadpool_info is not None:
+            blas = [p for p in threadpool_info() if p.get("user_api") == "blas"]
+            if blas:
+                threads = int(blas[0]["num_threads"])
+        for _ in range(warmup):
+            O.gemm(a32, b32)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            O.gemm(a32, b32)
+        dt = (time.perf_counter() - t0) / max(reps, 1)
     return dt, 2.0 * N_DIM * cols * N_DIM, threads
 
 
@@ -93,11 +100,11 @@ def run_reference(args):
     if rank != 0:
         return 0
     cols = 1024   # one eighth of the columns per step: a bounded sample of the same product
-    dt, flops, threads = cpu_sgemm_sample(cols, args.steps, min(args.warmup, 1))
+    dt, flops, threads = cpu_sgemm_sample(cols, args.steps, max(1, min(args.warmup, 3)))
     tf = flops / dt / 1e12
     line = {"impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "steps": args.steps, "warmup": max(1, min(args.warmup, 3)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args.gpus),
             "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                              "sample": f"{N_DIM}x{cols}x{N_DIM} slice (first {cols} columns of D) of the 8192^3 product per step, "
@@ -173,6 +180,101 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # the GPU arm
 # ------------------------------------------------------------------------------------------------
+def _timed(step, steps, warmup, barrier, max_over_ranks, torch):
+    """W untimed steps, then `steps` steps between CUDA events on the launching stream; barrier and
+    device synchronisation on both sides; max over ranks.  Returns milliseconds per step."""
+    for _ in range(warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+
+def c5_subrecord(args, world, rank, local, barrier, max_over_ranks, peaks):
+    """Configuration 5 (16384^3 BFloat16 -> Float32) sharded by column blocks over the ranks: steady
+    state with A resident, the one-shot time with A broadcast in K-panels under the product, the plain
+    broadcast alone, and — in the same run, on rank 0 — the whole product on one GPU, which gives the
+    strong-scaling efficiency without a second job.  Operands are drawn on the device (N(0, 0.02),
+    seeded); one row of the result is checked against a torch FP32 product."""
+    import torch
+    import gemmkernels_b200 as GK
+    from gemmkernels_b200 import multigpu
+    n = 16384
+    shard = multigpu.column_shard(n, world, rank, 512)
+    n_loc = shard.count
+    g = torch.Generator(device="cuda").manual_seed(1005)
+    a = GK.cuarray(GK.BFloat16, n, n)
+    if rank == 0:
+        a.T.copy_((torch.randn(n, n, device="cuda", generator=g) * 0.02).to(torch.bfloat16))
+    else:
+        a.zero_()
+    gb = torch.Generator(device="cuda").manual_seed(2005 + rank)
+    b = GK.cuarray(GK.BFloat16, n, n_loc)
+    b.T.copy_((torch.randn(n_loc, n, device="cuda", generator=gb) * 0.02).to(torch.bfloat16))
+    d = GK.cuarray(GK.Float32, n, n_loc)
+    conf = GK.get_config(gemm_shape=(n, n_loc, n), operator=GK.Operator.TCGen05Operator[GK.BFloat16, GK.Float32],
+                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[GK.BFloat16],
+                         global_c_layout=GK.Layout.Zero[GK.Float32],
+                         global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
+    steps, warm = min(args.steps, 20), 3
+    rec = {"workload": f"c5: 16384^3 BFloat16 N(0,0.02) -> Float32, column blocks of B,C over {world} rank(s) "
+                       f"({n_loc} columns on rank 0)", "steps": steps, "warmup": warm}
+    if world > 1:
+        # one-shot: A leaves rank 0 in K-panels on the communication stream while the panels that have
+        # arrived are multiplied (first call also pays nothing extra: the communicator is warm by now)
+        def one_shot():
+            multigpu.colshard_matmul_device(conf, a, b, None, d, a_mode="broadcast", root=0)
+        rec["one_shot_broadcast_overlapped_ms"] = _timed(one_shot, 3, 1, barrier, max_over_ranks, torch)
+        rec["a_broadcast_alone_ms"] = _timed(lambda: multigpu.broadcast_a_library(a, root=0), 3, 1, barrier, max_over_ranks, torch)
+    step = GK.bind(conf, a, b, None, d)
+    ms = _timed(step, steps, warm, barrier, max_over_ranks, torch)
+    GK.poll_status()
+    if rank == 0:
+        want = a[11:12].float() @ b.float()
+        err = (torch.linalg.norm(d[11:12].double() - want.double()) / torch.linalg.norm(want.double())).item()
+        if not err <= 1e-3:
+            raise SystemExit(f"c5 result is wrong: normwise error {err}")
+    flops = 2.0 * n ** 3
+    plan = GK.query(conf, a, b, None, d)
+    rec.update({"ms_per_step": ms, "tflops_total": flops / (ms * 1e-3) / 1e12,
+                "tflops_per_gpu": flops / world / (ms * 1e-3) / 1e12,
+                "frac_of_measured_per_gpu": flops / world / (ms * 1e-3) / 1e12 / peaks["tflops"],
+                "tile": [int(plan.tile_m), int(plan.tile_n), int(plan.tile_k)], "grid": int(plan.grid)})
+    if world > 1:
+        del b, d
+        n1_ms = None
+        if rank == 0:
+            b1 = GK.cuarray(GK.BFloat16, n, n); b1.T.copy_((torch.randn(n, n, device="cuda", generator=gb) * 0.02).to(torch.bfloat16))
+            d1 = GK.cuarray(GK.Float32, n, n)
+            conf1 = GK.get_config(gemm_shape=(n, n, n), operator=GK.Operator.TCGen05Operator[GK.BFloat16, GK.Float32],
+                                  global_a_layout=GK.Layout.UnsafeAlignedColMajor[GK.BFloat16],
+                                  global_c_layout=GK.Layout.Zero[GK.Float32],
+                                  global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
+            step1 = GK.bind(conf1, a, b1, None, d1)
+            for _ in range(warm):
+                step1()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step1()
+            e1.record(); torch.cuda.synchronize()
+            n1_ms = e0.elapsed_time(e1) / steps
+            del b1, d1
+        barrier()
+        if rank == 0:
+            rec["n1_ms_per_step_same_run"] = n1_ms
+            rec["efficiency_vs_n1"] = n1_ms / (world * ms)
+    del a
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -193,55 +295,6 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     from gemmkernels_b200 import multigpu
-    # Inputs: A is generated on rank 0 and broadcast (the one exchange of the sharded path);
-    # every rank draws its own column block of B.
-    if args.workload == "c5":
-        # strong scaling: one 16384^3 BFloat16 product, columns of B and C split over the ranks
-        n = m_dim = k_dim = 16384
-        shard = multigpu.column_shard(n, world, rank, 256)
-        n_loc, ET, tdt = shard.count, GK.BFloat16, torch.bfloat16
-        A_host = O.inputs_bf16_normal(5, m_dim, 8, k_dim)[0]
-        B_host = O.bf16_round(np.random.default_rng(2005 + rank).standard_normal((k_dim, n_loc), dtype=np.float32) * np.float32(0.02))
-        flops_total = 2.0 * m_dim * n * k_dim
-        flops_rank = 2.0 * m_dim * n_loc * k_dim
-    else:
-        # weak scaling: every rank owns 8192 columns of an 8192 x (8192 * ranks) product
-        m_dim = k_dim = n_loc = N_DIM
-        ET, tdt = GK.Float16, torch.float16
-        A_host, _ = O.inputs_fp16_uniform01(0, m_dim, 8, k_dim)
-        B_host = np.random.default_rng(2000 + rank).random((k_dim, n_loc), dtype=np.float32).astype(np.float16)
-        flops_total = world * FLOPS_PER_GEMM
-        flops_rank = FLOPS_PER_GEMM
-    a_pin = torch.from_numpy(np.ascontiguousarray(A_host.T)).to(tdt).pin_memory().T      # column-major, pinned
-    b_pin = torch.from_numpy(np.ascontiguousarray(B_host.T)).to(tdt).pin_memory().T
-    d_pin = torch.empty(n_loc, m_dim, dtype=torch.float32).pin_memory().T
-    a = GK.cuarray(ET, m_dim, k_dim)
-    b = GK.cuarray(ET, k_dim, n_loc); b.copy_(b_pin, non_blocking=True)
-    d = GK.cuarray(GK.Float32, m_dim, n_loc)
-    bcast_ms = None
-    if rank == 0:
-        a.copy_(a_pin, non_blocking=True)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-        warm = torch.zeros(1024, device="cuda")
-        dist.broadcast(warm, src=0)     # first collective pays NCCL's lazy set-up; keep it out of the timing
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        multigpu.broadcast_a(a.T, src=0)      # a.T is the contiguous view of the column-major storage
-        e1.record(); torch.cuda.synchronize()
-        bcast_ms = e0.elapsed_time(e1)
-
-    # the call a user makes: GemmKernels.matmul with a Config (TCGen05Operator, aligned layouts)
-    conf = GK.get_config(gemm_shape=(m_dim, n_loc, k_dim), operator=GK.Operator.TCGen05Operator[ET, GK.Float32],
-                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[ET],
-                         global_c_layout=GK.Layout.Zero[GK.Float32],
-                         global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
-    plan = GK.query(conf, a, b, None, d)
-
-    def step():
-        GK.matmul(conf, a, b, None, d, kernel=GK.Kernel.matmul_pipelined)
 
     def barrier():
         if world > 1:
@@ -255,7 +308,49 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(args.warmup, 3)):
+    if world > 1:
+        multigpu.init(device_index=local)       # the library's own communicator (NCCL found by dlopen)
+    peaks = measured_peaks()
+
+    # The metric's product, 8192^3 Float16 -> Float32, split by column blocks of B and C over the ranks
+    # (strong scaling: the problem is fixed, every rank owns 8192 / N columns).  A is the same on every
+    # rank (seeded); every rank draws its own block of B.
+    m_dim = k_dim = n_total = N_DIM
+    shard = multigpu.column_shard(n_total, world, rank, 512)
+    n_loc = shard.count
+    ET, tdt = GK.Float16, torch.float16
+    A_host, _ = O.inputs_fp16_uniform01(0, m_dim, 8, k_dim)
+    B_host = np.random.default_rng(2000 + rank).random((k_dim, n_loc), dtype=np.float32).astype(np.float16)
+    a_pin = torch.from_numpy(np.ascontiguousarray(A_host.T)).to(tdt).pin_memory().T      # column-major, pinned
+    b_pin = torch.from_numpy(np.ascontiguousarray(B_host.T)).to(tdt).pin_memory().T
+    d_pin = torch.empty(n_loc, m_dim, dtype=torch.float32).pin_memory().T
+    a = GK.cuarray(ET, m_dim, k_dim)
+    b = GK.cuarray(ET, k_dim, n_loc); b.copy_(b_pin, non_blocking=True)
+    d = GK.cuarray(GK.Float32, m_dim, n_loc)
+    if rank == 0:
+        a.copy_(a_pin, non_blocking=True)
+    torch.cuda.synchronize()
+
+    # the call a user makes: GemmKernels.matmul with a Config (TCGen05Operator, aligned layouts)
+    conf = GK.get_config(gemm_shape=(m_dim, n_loc, k_dim), operator=GK.Operator.TCGen05Operator[ET, GK.Float32],
+                         global_a_layout=GK.Layout.UnsafeAlignedColMajor[ET],
+                         global_c_layout=GK.Layout.Zero[GK.Float32],
+                         global_d_layout=GK.Layout.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64))
+    plan = GK.query(conf, a, b, None, d)
+    one_shot_ms = bcast_ms = None
+    if world > 1:
+        barrier()
+        # A reaches the other ranks through the library: broadcast in K-panels overlapped with the product
+        multigpu.colshard_matmul_device(conf, a, b, None, d, a_mode="broadcast", root=0)      # warm: NCCL's lazy set-up
+        one_shot_ms = _timed(lambda: multigpu.colshard_matmul_device(conf, a, b, None, d, a_mode="broadcast", root=0),
+                             3, 1, barrier, max_over_ranks, torch)
+        bcast_ms = _timed(lambda: multigpu.broadcast_a_library(a, root=0), 3, 1, barrier, max_over_ranks, torch)
+
+    def step():
+        GK.matmul(conf, a, b, None, d, kernel=GK.Kernel.matmul_pipelined)
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     barrier()
     sampler = ClockSampler(local)
@@ -270,76 +365,117 @@ def run_gpu(args):
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     GK.poll_status()
     ms_per_step = total_ms / args.steps
-    value = flops_total / (ms_per_step * 1e-3) / 1e12
+    value = FLOPS_PER_GEMM / (ms_per_step * 1e-3) / 1e12
 
     # correctness spot check of the timed result (one row against the oracle's product)
-    row = np.asarray(A_host[7:8].astype(np.float32) @ B_host.astype(np.float32)) if rank == 0 else None
-    if args.workload == "c5":
-        METRIC_NAME = "GEMM TFLOP/s (BF16->FP32, 16384^3, column-sharded)"
-    else:
-        METRIC_NAME = METRIC
-    if rank == 0:
-        got = d[7:8].cpu().numpy()
-        err = O.normwise_error(got, row)
-        if not err <= 1e-3:
-            raise SystemExit(f"bench result is wrong: normwise error {err}")
+    row = np.asarray(A_host[7:8].astype(np.float32) @ B_host.astype(np.float32))
+    err = O.normwise_error(d[7:8].cpu().numpy(), row)
+    if not err <= 1e-3:
+        raise SystemExit(f"bench result is wrong on rank {rank}: normwise error {err}")
 
-    # end to end: same GEMM from pinned host buffers through gk_gemm_host (H2D of A and B, D2H of D
-    # inside the timed region, every step)
+    # the library GEMM (cuBLAS through torch.matmul) on the same operands, same warm-up and steps, right
+    # after the timed region: the comparator the reference's own benchmark runner always prints
+    cublas_ms = None
+    if world == 1:
+        bt, at = b.T, a.T                      # contiguous views: (B^T A^T) = D^T is the row-major image of D
+        cublas_out = "f32"
+        try:
+            torch.mm(bt, at, out_dtype=torch.float32)
+            def cublas_step():
+                torch.mm(bt, at, out_dtype=torch.float32)
+        except Exception:
+            cublas_out = "f16"                 # this torch cannot ask cuBLAS for a Float32 result: half the output bytes
+            def cublas_step():
+                torch.mm(bt, at)
+        cublas_ms = _timed(cublas_step, args.steps, warm, barrier, max_over_ranks, torch)
+
+    # end to end: the same product from pinned host buffers (H2D of the operands, D2H of D inside the
+    # timed region, every step).  One rank: gk_gemm_host.  Several: every rank uploads 1/N of A over its
+    # own PCIe link, NCCL all-gathers assemble A over NVLink, its block of B goes up and its block of D
+    # comes back (gk_mgpu_gemm_colshard_host).
+    phases = None
     if world > 1:
-        # sharded host path: rank 0 uploads A, NVLink carries it to the others, every rank uploads its own
-        # block of B and downloads its block of D
         def e2e_step():
-            multigpu.colshard_matmul_host(conf, a_pin if rank == 0 else None, a, b_pin, d_pin, src=0, device_index=local)
+            return multigpu.colshard_matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local, times=True)
     else:
         def e2e_step():
             GK.matmul_host(conf, a_pin, b_pin, None, d_pin, device_index=local)
     for _ in range(2):
         e2e_step()
     barrier()
-    e2e_steps = min(args.steps, 100)   # ~10 ms per step over PCIe: bounded so the default run stays short
+    e2e_steps = min(args.steps, 100)   # ~10 ms per step over PCIe on one GPU: bounded so the default run stays short
+    acc = {}
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        e2e_step()
+        t = e2e_step()
+        if t:
+            for k, v in t.items():
+                acc[k] = acc.get(k, 0.0) + float(v)
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
-    if rank == 0:
-        err = O.normwise_error(d_pin[7:8].numpy(), row)
-        if not err <= 1e-3:
-            raise SystemExit(f"end-to-end result is wrong: normwise error {err}")
-    e2e_value = flops_total / (e2e_ms * 1e-3) / 1e12
-    h2d = a_pin.numel() * 2 + b_pin.numel() * 2      # rank 0; with several ranks the others upload only their B block
-    d2h = d_pin.numel() * 4
+    err = O.normwise_error(d_pin[7:8].numpy(), row)
+    if not err <= 1e-3:
+        raise SystemExit(f"end-to-end result is wrong on rank {rank}: normwise error {err}")
+    e2e_value = FLOPS_PER_GEMM / (e2e_ms * 1e-3) / 1e12
+    if world > 1:
+        phases = {k: acc[k] / e2e_steps for k in ("upload_ms", "collective_ms", "compute_ms", "download_ms", "total_ms")}
+        phases_max = {k: max_over_ranks(v) for k, v in phases.items()}
+        h2d = int(acc["h2d_bytes"] / e2e_steps); d2h = int(acc["d2h_bytes"] / e2e_steps)
+        chunks = int(acc["chunks"] / e2e_steps)
+    else:
+        h2d = a_pin.numel() * 2 + b_pin.numel() * 2
+        d2h = d_pin.numel() * 4
+    del a, b, d
+    torch.cuda.empty_cache()
+
+    c5 = None if args.no_c5 else c5_subrecord(args, world, rank, local, barrier, max_over_ranks, peaks)
 
     if rank != 0:
         if world > 1:
-            dist.barrier(); dist.destroy_process_group()
+            dist.barrier(); multigpu.shutdown(local); dist.destroy_process_group()
         return 0
 
-    peaks = measured_peaks()
-    achieved = flops_rank / (ms_per_step * 1e-3) / 1e12     # per launch, one GPU (rank 0's block)
+    achieved = FLOPS_PER_GEMM / world / (ms_per_step * 1e-3) / 1e12     # per launch, one GPU (rank 0's block)
     line = {
-        "metric": METRIC_NAME, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if args.workload == "c5" else "weak",
-        "vs_baseline": None, "dtype": "bf16" if args.workload == "c5" else "f16", "data": "synthetic",
-        "config": workload_config(world, args.workload),
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(world),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"],
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if args.workload == "c0" else None,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+                     "traffic_source": "ncu capture of this kernel on this shape (profiles/tc_gemm_kernel_c0_8192_fp16.md), "
+                                       "not measured in this run",
                      "peak_source": f"{peaks['source']} cuBLAS bf16 burst; sustained {peaks['tflops_sustained']}",
                      "frac_of_nominal_dense_2250": achieved / 2250.0},
         "kernel": {"family": int(plan.kernel), "grid": int(plan.grid), "cluster": int(plan.cluster),
                    "tile": [int(plan.tile_m), int(plan.tile_n), int(plan.tile_k)], "stages": int(plan.stages),
                    "smem_bytes": int(plan.smem_bytes), "tmem_columns": int(plan.tmem_columns)},
     }
-    if bcast_ms is not None:
+    if cublas_ms is not None:
+        line["cublas_same_run_tflops"] = FLOPS_PER_GEMM / (cublas_ms * 1e-3) / 1e12
+        line["vs_cublas_same_run"] = cublas_ms / ms_per_step
+        line["cublas_out_dtype"] = cublas_out
+    if world > 1:
+        tiles = (m_dim // 256) * (-(-n_loc // 512))
         line["a_broadcast_ms"] = bcast_ms
-    if world == 1 and not args.no_cpu_baseline and args.workload == "c0":
+        line["one_shot_broadcast_overlapped_ms"] = one_shot_ms
+        line["e2e"]["phases_ms_rank0"] = phases
+        line["e2e"]["phases_ms_max_over_ranks"] = phases_max
+        line["e2e"]["a_chunks"] = chunks
+        line["e2e"]["h2d_gbs_per_rank"] = h2d / (phases["upload_ms"] * 1e-3) / 1e9 if phases["upload_ms"] > 0 else None
+        line["e2e"]["d2h_gbs_per_rank"] = d2h / (phases["download_ms"] * 1e-3) / 1e9 if phases["download_ms"] > 0 else None
+        line["limiter"] = (f"each rank's block is {tiles} tiles of 256x512 on {int(plan.grid) // 2} CTA pairs: "
+                           f"{tiles / (-(-tiles // 74) * 74):.0%} of the slots of its last round are filled, and the single "
+                           "accumulator stage leaves each tile's epilogue exposed")
+    if c5 is not None:
+        line["c5"] = c5
+    if world == 1 and not args.no_cpu_baseline:
         cols = 2048
         dt, flops, threads = cpu_sgemm_sample(cols, 3, 1)
         line["cpu_baseline"] = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
@@ -347,7 +483,7 @@ def run_gpu(args):
                                           "numpy/OpenBLAS sgemm on Float32-promoted inputs"}
     print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier(); dist.destroy_process_group()
+        dist.barrier(); multigpu.shutdown(local); dist.destroy_process_group()
     return 0
 
 
@@ -490,10 +626,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="c0", choices=["c0", "c5", "c1", "c2", "c3", "c4", "diag"],
-                    help="c0: the headline 8192^3 FP16 GEMM per GPU (weak scaling); c5: one 16384^3 BF16 GEMM "
-                         "split by column blocks (strong scaling); c1-c4, diag: the other configurations, "
-                         "kernel-only on one GPU")
+    ap.add_argument("--no-c5", action="store_true", help="skip the 16384^3 BFloat16 sub-record")
+    ap.add_argument("--workload", default="c0", choices=["c0", "c1", "c2", "c3", "c4", "diag"],
+                    help="c0: the headline 8192^3 FP16 GEMM, split by column blocks over the ranks, with the 16384^3 "
+                         "BF16 configuration as a sub-record of the same line; c1-c4, diag: the other "
+                         "configurations, kernel-only on one GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -20,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libgemmkernels_b200.so"
 
-SOURCES = ["tc_kernels_rank3.cu", "tc_kernels_rank5.cu", "api.cu", "tc_plan.cu", "contract.cu"]
+SOURCES = ["tc_kernels_rank3.cu", "tc_kernels_rank5.cu", "api.cu", "tc_plan.cu", "contract.cu", "mgpu.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -67,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
     cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", str(LIB_PATH), *objs,
-           "-Xlinker", "--exclude-libs=ALL"]
+           "-Xlinker", "--exclude-libs=ALL", "-ldl"]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)

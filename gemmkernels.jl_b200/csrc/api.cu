@@ -394,6 +394,7 @@ gk_status gk_create(gk_handle* out) {
 gk_status gk_destroy(gk_handle h) {
   clear_error();
   if (!h) return GK_OK;
+  mgpu_release(h);
   for (int i = 0; i < 5; ++i)
     if (h->stage_dev[i]) cudaFree(h->stage_dev[i]);
   for (cudaEvent_t e : h->events) cudaEventDestroy(e);
@@ -652,13 +653,30 @@ static size_t operand_bytes(int64_t ld, int64_t cols, int64_t plane, int number,
   return (static_cast<size_t>(plane) + static_cast<size_t>(ld) * cols) * es;
 }
 
-static gk_status stage_reserve(gk_handle h, int slot, size_t bytes) {
+}  // extern "C"
+
+namespace gk {
+gk_status stage_reserve(gk_handle h, int slot, size_t bytes) {
   if (bytes <= h->stage_bytes[slot]) return GK_OK;
   if (h->stage_dev[slot]) { cudaFree(h->stage_dev[slot]); h->stage_dev[slot] = nullptr; h->stage_bytes[slot] = 0; }
   GK_CUDA_CHECK(cudaMalloc(&h->stage_dev[slot], bytes));
   h->stage_bytes[slot] = bytes;
   return GK_OK;
 }
+
+gk_status host_streams_reserve(gk_handle h, size_t n_events) {
+  if (!h->copy_in) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+  if (!h->copy_out) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+  while (h->events.size() < n_events) {
+    cudaEvent_t e;
+    GK_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    h->events.push_back(e);
+  }
+  return GK_OK;
+}
+}  // namespace gk
+
+extern "C" {
 
 // Block (r0.., c0..) of a column-major matrix with leading dimension ld, between host and device images
 // that share the layout.
@@ -689,13 +707,9 @@ static gk_status gemm_host_pipelined(gk_handle h, const gk_gemm_desc& d, const v
   const int64_t nc = ceil_div(ceil_div(d.n, chunks(b_bytes)), 512) * 512;   // columns per chunk
   const int R = static_cast<int>(ceil_div(d.m, mr)), Cn = static_cast<int>(ceil_div(d.n, nc));
   if (R * Cn <= 1) return GK_ERR_UNSUPPORTED;
-  if (!h->copy_in) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
-  if (!h->copy_out) GK_CUDA_CHECK(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
-  const size_t n_events = 2 * static_cast<size_t>(R) * Cn + 2;
-  while (h->events.size() < n_events) {
-    cudaEvent_t e;
-    GK_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    h->events.push_back(e);
+  {
+    const gk_status rs = host_streams_reserve(h, 2 * static_cast<size_t>(R) * Cn + 2);
+    if (rs != GK_OK) return rs;
   }
   const size_t es_a = dtype_size(d.dtype_a), es_b = dtype_size(d.dtype_b), es_c = dtype_size(d.dtype_c),
                es_d = dtype_size(d.dtype_d);

@@ -67,6 +67,8 @@ inline cudaError_t launch_dependent(void (*kernel)(const P), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&cfg, kernel, params);
 }
 
+struct MgpuState;   // mgpu.cu: communicator, communication stream and events of the sharded path
+
 }  // namespace gk
 
 struct gk_handle_s {
@@ -87,4 +89,14 @@ struct gk_handle_s {
   // copy streams and events of the pipelined gk_gemm_host (created on first use)
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> events;
+  gk::MgpuState* mgpu = nullptr;   // set by gk_mgpu_init, released by gk_mgpu_destroy / gk_destroy
 };
+
+namespace gk {
+// api.cu: grows staging buffer `slot` of the handle to at least `bytes` (never shrinks)
+gk_status stage_reserve(gk_handle h, int slot, size_t bytes);
+// api.cu: creates the two copy streams and at least `n_events` untimed events of the handle
+gk_status host_streams_reserve(gk_handle h, size_t n_events);
+// mgpu.cu: releases the communicator (called by gk_destroy)
+void mgpu_release(gk_handle h);
+}  // namespace gk

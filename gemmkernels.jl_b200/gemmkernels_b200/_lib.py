@@ -28,7 +28,11 @@ EXPORTS = (
     "gk_version", "gk_last_error_message", "gk_create", "gk_destroy", "gk_poll_status",
     "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks", "gk_measure_fp32_fma",
     "gk_contract_static",
+    "gk_mgpu_unique_id", "gk_mgpu_init", "gk_mgpu_destroy", "gk_mgpu_gemm_colshard", "gk_mgpu_gemm_colshard_host",
+    "gk_mgpu_host_plan", "gk_mgpu_broadcast",
 )
+GK_MGPU_UNIQUE_ID_BYTES = 128
+GK_MGPU_A_RESIDENT, GK_MGPU_A_BROADCAST = 0, 1
 GK_MAX_MODES = 8
 GK_STATIC_TABLE_ENTRIES = 32768
 
@@ -76,6 +80,14 @@ class GemmPlan(C.Structure):
         ("smem_bytes", C.c_int32), ("tmem_columns", C.c_int32),
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32),
         ("workspace_bytes", C.c_int64),
+    ]
+
+
+class MgpuTimes(C.Structure):
+    _fields_ = [
+        ("upload_ms", C.c_float), ("collective_ms", C.c_float), ("compute_ms", C.c_float), ("download_ms", C.c_float),
+        ("total_ms", C.c_float), ("chunks", C.c_int32), ("reserved", C.c_int32),
+        ("h2d_bytes", C.c_int64), ("d2h_bytes", C.c_int64),
     ]
 
 
@@ -134,6 +146,23 @@ def _load() -> C.CDLL:
     lib.gk_contract_static.restype = C.c_int
     lib.gk_contract_static.argtypes = [C.POINTER(ContractDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p]
+    lib.gk_mgpu_unique_id.restype = C.c_int
+    lib.gk_mgpu_unique_id.argtypes = [C.c_void_p]
+    lib.gk_mgpu_init.restype = C.c_int
+    lib.gk_mgpu_init.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    lib.gk_mgpu_destroy.restype = C.c_int
+    lib.gk_mgpu_destroy.argtypes = [C.c_void_p]
+    lib.gk_mgpu_gemm_colshard.restype = C.c_int
+    lib.gk_mgpu_gemm_colshard.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p,
+                                          C.c_int64, C.c_void_p]
+    lib.gk_mgpu_gemm_colshard_host.restype = C.c_int
+    lib.gk_mgpu_gemm_colshard_host.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.POINTER(EpilogueDesc), C.c_void_p, C.POINTER(MgpuTimes)]
+    lib.gk_mgpu_broadcast.restype = C.c_int
+    lib.gk_mgpu_broadcast.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]
+    lib.gk_mgpu_host_plan.restype = C.c_int
+    lib.gk_mgpu_host_plan.argtypes = [C.POINTER(GemmDesc), C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int64)]
     return lib
 
 

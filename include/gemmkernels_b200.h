@@ -281,6 +281,77 @@ GK_API gk_status gk_gemm_host(gk_handle h, const gk_gemm_desc* desc, const void*
                               const void* b_host, const void* c_host, void* d_host,
                               const gk_epilogue_desc* epi, gk_stream stream);
 
+
+/*
+ * Column-sharded GEMM over the GPUs of one box: D[:, J_r] = A * B[:, J_r], rank r owns the column
+ * block J_r of B, C and D; the only exchange is A.  The reference has no multi-GPU code; these
+ * entry points have no counterpart there.  One rank per GPU — a process per GPU (torchrun,
+ * Julia's Distributed, MPI) or a thread per GPU — each with its own handle.  The library finds NCCL
+ * at gk_mgpu_init with dlopen (the environment variable GK_NCCL_LIB, else a libnccl.so.2 that the
+ * process has loaded already, else the system's), so it still loads on machines without NCCL.
+ * Kernels only ever read this GPU's own memory: A arrives through NCCL into local buffers first.
+ */
+#define GK_MGPU_UNIQUE_ID_BYTES 128
+
+/* Fills id_out (GK_MGPU_UNIQUE_ID_BYTES bytes) on ONE rank; hand the bytes to every rank by any
+ * means (a file, a socket, torch.distributed, MPI) and pass them to gk_mgpu_init. */
+GK_API gk_status gk_mgpu_unique_id(void* id_out);
+
+/* Joins the communicator of `world` ranks as `rank` with the handle's device (collective: every
+ * rank calls it; blocks until all have).  Creates the handle's communication stream. */
+GK_API gk_status gk_mgpu_init(gk_handle h, int32_t rank, int32_t world, const void* unique_id);
+GK_API gk_status gk_mgpu_destroy(gk_handle h);
+
+typedef enum gk_mgpu_a_mode {
+  GK_MGPU_A_RESIDENT = 0,  /* every rank already holds A at `a`: nothing is exchanged              */
+  GK_MGPU_A_BROADCAST = 1  /* rank `root` holds A at `a`; it is sent into every rank's `a` first   */
+} gk_mgpu_a_mode;
+
+/* This rank's block of the sharded product, device operands (collective when a_mode is BROADCAST:
+ * every rank calls it with the same m, k, a_mode, root and k_panels).  desc describes the local block
+ * (n = this rank's column count; may differ between ranks).  a: device buffer of the whole A on every
+ * rank.  With GK_MGPU_A_BROADCAST, A travels in `k_panels` panels of K (0 = choose) over NCCL on the
+ * handle's communication stream while the product of the panels that have arrived runs on `stream`
+ * (D accumulates panel by panel; bias and activation are applied with the last panel), so the
+ * transfer overlaps the arithmetic; a transposed A (trans_a = 1) is sent in one piece.  Enqueues
+ * only; the result is complete when `stream` is. */
+GK_API gk_status gk_mgpu_gemm_colshard(gk_handle h, const gk_gemm_desc* desc, void* a, int32_t a_mode,
+                                       int32_t root, int32_t k_panels, const void* b, const void* c, void* d,
+                                       const gk_epilogue_desc* epi, void* workspace, int64_t workspace_bytes,
+                                       gk_stream stream);
+
+/* Sends `bytes` bytes at `buf` from rank `root` into every rank's `buf` (collective), on the handle's
+ * communication stream, ordered after what `stream` holds so far; `stream` then waits for it.  What
+ * "A broadcast once" means for callers that keep A resident over many products. */
+GK_API gk_status gk_mgpu_broadcast(gk_handle h, void* buf, int64_t bytes, int32_t root, gk_stream stream);
+
+/* Times of the phases of one gk_mgpu_gemm_colshard_host call, in milliseconds (device clocks). */
+typedef struct gk_mgpu_times {
+  float upload_ms;      /* first to last host-to-device copy of this rank (its pieces of A, its B)  */
+  float collective_ms;  /* sum of the all-gathers that assemble A                                   */
+  float compute_ms;     /* sum of the GEMM kernels of this rank                                     */
+  float download_ms;    /* first to last device-to-host copy of this rank's D                       */
+  float total_ms;       /* first upload to last download                                            */
+  int32_t chunks;       /* row chunks A was cut into                                                */
+  int32_t reserved;
+  int64_t h2d_bytes, d2h_bytes; /* bytes this rank moved over PCIe                                  */
+} gk_mgpu_times;
+
+/* The same with operands and result in HOST memory (collective).  a_host points at the whole A in
+ * this rank's host memory, but each rank reads — and sends over its own PCIe link — only 1/world of
+ * it; NCCL all-gathers assemble A in every GPU's memory over NVLink, chunk by chunk, while this
+ * rank's block of B goes up, and each row chunk of D is multiplied and sent back as soon as its
+ * chunk of A is complete.  b_host, c_host, d_host are this rank's column blocks.  Needs K (or, for a
+ * transposed A, M) divisible by world; real products only.  Returns when d_host is complete.
+ * times may be NULL. */
+GK_API gk_status gk_mgpu_gemm_colshard_host(gk_handle h, const gk_gemm_desc* desc, const void* a_host,
+                                            const void* b_host, const void* c_host, void* d_host,
+                                            const gk_epilogue_desc* epi, gk_stream stream, gk_mgpu_times* times);
+
+/* How gk_mgpu_gemm_colshard_host would cut A for this descriptor and world size: number of row chunks
+ * and rows per chunk (the last may be shorter).  Host arithmetic only; needs no GPU and no handle. */
+GK_API gk_status gk_mgpu_host_plan(const gk_gemm_desc* desc, int32_t world, int32_t* chunks, int64_t* rows_per_chunk);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,25 +63,14 @@ def _worker(rank, world, port, n, k, m, out_dir):
         assert torch.equal(a_store, torch.from_numpy(np.ascontiguousarray(A.T)))       # A arrived everywhere
         # second step with A resident: no broadcast, new B block
         multigpu.colshard_matmul(local_product, a_store, b_block * 2, d_block, a_is_resident=True)
-        # the host-path variant: only rank 0 holds A in host memory; the per-rank host GEMM is replaced by
-        # the same stand-in (there is no CUDA here), which must find A in place and be told so
-        import importlib
-        mm = importlib.import_module("gemmkernels_b200.matmul")     # the package re-exports a function of that name
-        seen = {}
-
-        def fake_matmul_host(conf, a, b, c, d, *, device_index=None, a_on_device=False, **kw):
-            seen["a_on_device"] = a_on_device
-            local_product(a.T, b.T, d.T)
-        real, mm.matmul_host = mm.matmul_host, fake_matmul_host
-        try:
-            a_dev = torch.zeros(k, m).T                        # column-major (m, k) "device" array
-            d_host = torch.zeros(shard.count, m).T
-            multigpu.colshard_matmul_host(None, torch.from_numpy(np.ascontiguousarray(A.T)).T if rank == 0 else None,
-                                          a_dev, (b_block * 2).T, d_host)
-        finally:
-            mm.matmul_host = real
-        assert seen["a_on_device"] is True and torch.equal(a_dev.T, torch.from_numpy(np.ascontiguousarray(A.T)))
-        assert torch.equal(d_host.T, d_block)
+        # the host-path scheme: every rank contributes 1/world of each row chunk of A and an all-gather
+        # assembles the chunk everywhere (gloo here, NCCL inside the library on GPUs)
+        for trans_a in (False, True):
+            chunks, rows = 3, 4
+            got = multigpu.allgather_a_chunks(torch.from_numpy(A), trans_a, rank, world, chunks, rows)
+            assert len(got) == chunks
+            for i, chunk in enumerate(got):
+                assert np.array_equal(chunk.numpy(), A[i * rows:(i + 1) * rows]), (trans_a, i)
         full = multigpu.gather_columns(d_block, shard)
         want = 2 * (A @ B)
         err = np.linalg.norm(full.numpy().T - want) / np.linalg.norm(want)
@@ -98,3 +87,25 @@ def test_two_rank_gloo_colshard(tmp_path):
     for r in range(world):
         err, shape = (tmp_path / f"rank{r}.txt").read_text().split(" ", 1)
         assert float(err) < 1e-5 and shape == "(22, 12)"
+
+
+def test_host_plan_of_the_sharded_host_path():
+    """gk_mgpu_host_plan: chunk arithmetic of the library, no GPU needed."""
+    import gemmkernels_b200 as GK
+    from gemmkernels_b200 import Layout, Operator
+    def conf(m, n, k, trans_a=False):
+        la = (Layout.RowMajor if trans_a else Layout.ColMajor)[GK.Float16]
+        return GK.get_config(gemm_shape=(m, n, k), operator=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                             global_a_layout=la, global_c_layout=Layout.Zero[GK.Float32],
+                             global_d_layout=Layout.ColMajor[GK.Float32], is_a_col_major=not trans_a)
+    # 8192 x 8192 Float16 = 128 MiB -> four chunks of 2048 rows
+    assert multigpu.host_plan(conf(8192, 1024, 8192), 8) == (4, 2048)
+    # 16384^2 BFloat16-sized A (512 MiB) -> the cap of eight chunks
+    assert multigpu.host_plan(conf(16384, 2048, 16384), 8) == (8, 2048)
+    # small A: one chunk of all rows
+    assert multigpu.host_plan(conf(1000, 64, 512), 2) == (1, 1000)
+    # chunks of a transposed A are dealt out by rows: whole multiples of lcm(256, world)
+    chunks, rows = multigpu.host_plan(conf(12288, 512, 8192, trans_a=True), 3)
+    assert rows % 768 == 0 and chunks * rows >= 12288
+    with pytest.raises(GK.ConfigError):
+        multigpu.host_plan(conf(4096, 64, 1000), 3)          # K not divisible by the ranks
