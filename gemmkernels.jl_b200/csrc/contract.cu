@@ -337,6 +337,11 @@ static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const 
         plan_only->stages = L.params.stages;
         return GK_OK;
       }
+      if (L.params.debug & 8) {
+        if (!workspace || workspace_bytes < static_cast<int64_t>(L.grid) * 16 * 8)
+          return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace of %lld bytes", (long long)L.grid * 16 * 8);
+        L.params.dbg_out = static_cast<long long*>(workspace);
+      }
       return tc_launch(L, stream);
     }
     why = gk_last_error_message();   // planning refused (e.g. box shapes): use the gather path

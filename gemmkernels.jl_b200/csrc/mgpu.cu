@@ -240,36 +240,67 @@ gk_status gk_mgpu_gemm_colshard(gk_handle h, const gk_gemm_desc* desc, void* a, 
   const gk_gemm_desc& dd = *desc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t es_a = dtype_size(dd.dtype_a), es_b = dtype_size(dd.dtype_b);
-  // panels of K: whole multiples of 256 columns of a column-major A (contiguous in memory, and
-  // every panel of A and B starts 16-byte aligned); a transposed A travels in one piece
-  int panels = k_panels > 0 ? k_panels : (dd.k >= 8192 ? 4 : dd.k >= 2048 ? 2 : 1);
-  if (dd.trans_a) panels = 1;
-  int64_t kp = (dd.k + panels - 1) / panels;
-  kp = (kp + 255) / 256 * 256;
-  panels = static_cast<int>((dd.k + kp - 1) / kp);
+  const size_t es_c = dtype_size(dd.dtype_c), es_d = dtype_size(dd.dtype_d);
+  // Panels.  A column-major A (M x K) is contiguous in runs of whole columns, i.e. in panels of K: the
+  // product of panel p adds to D (beta = 1 from the second panel on; bias and activation with the
+  // last), which costs one more read and write of the D block per extra panel.  A transposed A
+  // (stored K x M) is contiguous in panels of M: each is an independent block of rows of D, nothing
+  // accumulates.  Panel boundaries are multiples of 256, so every panel starts 16-byte aligned.
+  const bool by_m = dd.trans_a != 0;
+  const int64_t cut = by_m ? dd.m : dd.k;
+  int panels = k_panels;
+  if (panels <= 0) {
+    if (by_m) {
+      panels = cut >= 8192 ? 4 : cut >= 2048 ? 2 : 1;
+    } else {
+      // rough times in seconds: broadcast at NVLink rate, product at the tensor-core rate, D traffic at HBM rate
+      const double bcast = static_cast<double>(dd.m) * dd.k * es_a / 600e9;
+      const double extra = 2.0 * dd.m * dd.n * es_d / 6.0e12;          // per extra panel
+      double best = 1e30;
+      for (int p : {1, 2, 4}) {
+        if (cut < 2048 * p && p > 1) continue;
+        const double t = bcast / p + (p - 1) * extra;                    // what the product cannot hide
+        if (t < best) { best = t; panels = p; }
+      }
+    }
+  }
+  int64_t step = (cut + panels - 1) / panels;
+  step = (step + 255) / 256 * 256;
+  panels = static_cast<int>((cut + step - 1) / step);
   gk_status s = reserve_events(&m->events, static_cast<size_t>(panels) + 1, cudaEventDisableTiming);
   if (s != GK_OK) return s;
   // the transfers start after whatever the caller queued on `stream` (A may still be in use there)
   GK_CUDA_CHECK(cudaEventRecord(m->events[0], st));
   GK_CUDA_CHECK(cudaStreamWaitEvent(m->comm_stream, m->events[0], 0));
-  const int64_t a_cols = dd.trans_a ? dd.m : dd.k;
+  const int64_t a_rows = by_m ? dd.k : dd.m;      // rows of the stored A
+  gk_epilogue_desc epi_p;
+  if (epi) epi_p = *epi;
   for (int p = 0; p < panels; ++p) {
-    const int64_t k0 = p * kp, kn = std::min<int64_t>(kp, dd.k - k0);
-    char* a_p = static_cast<char*>(a) + (dd.trans_a ? 0 : static_cast<size_t>(k0) * dd.lda * es_a);
-    const int64_t cols = dd.trans_a ? a_cols : kn;
-    // the last column of the last panel is sent without the padding behind it
-    const size_t bytes = (static_cast<size_t>(cols - 1) * dd.lda + (dd.trans_a ? dd.k : dd.m)) * es_a;
+    const int64_t x0 = p * step, xn = std::min<int64_t>(step, cut - x0);   // stored columns x0 .. x0 + xn
+    char* a_p = static_cast<char*>(a) + static_cast<size_t>(x0) * dd.lda * es_a;
+    // the last column of a panel is sent without the padding behind it
+    const size_t bytes = (static_cast<size_t>(xn - 1) * dd.lda + a_rows) * es_a;
     GK_NCCL_CHECK(m->api, m->api->Broadcast(a_p, a_p, bytes, kNcclUint8, root, m->comm, m->comm_stream));
     GK_CUDA_CHECK(cudaEventRecord(m->events[p + 1], m->comm_stream));
     GK_CUDA_CHECK(cudaStreamWaitEvent(st, m->events[p + 1], 0));
     gk_gemm_desc blk = dd;
-    blk.k = kn;
     if (blk.max_ctas == 0 && panels > 1) blk.max_ctas = std::max(2, (h->sm_count - 16) & ~1);   // leave SMs to NCCL
-    const char* b_p = static_cast<const char*>(b) + (dd.trans_b ? static_cast<size_t>(k0) * dd.ldb : static_cast<size_t>(k0)) * es_b;
+    const void* b_p = b;
     const void* c_p = c;
-    if (p > 0) { blk.beta = 1.0; blk.layout_c = GK_LAYOUT_DENSE; blk.dtype_c = dd.dtype_d; blk.ldc = dd.ldd; c_p = d; }
-    const bool last = p == panels - 1;
-    s = gk_gemm(h, &blk, a_p, b_p, c_p, d, last ? epi : nullptr, workspace, workspace_bytes, stream);
+    void* d_p = d;
+    const gk_epilogue_desc* e_p = epi;
+    if (by_m) {
+      blk.m = xn;
+      if (c) c_p = static_cast<const char*>(c) + static_cast<size_t>(x0) * es_c;
+      d_p = static_cast<char*>(d) + static_cast<size_t>(x0) * es_d;
+      if (epi && epi->bias_axis == GK_BIAS_ROW && epi->bias) { epi_p.bias = epi->bias + x0; e_p = &epi_p; }
+    } else {
+      blk.k = xn;
+      b_p = static_cast<const char*>(b) + (dd.trans_b ? static_cast<size_t>(x0) * dd.ldb : static_cast<size_t>(x0)) * es_b;
+      if (p > 0) { blk.beta = 1.0; blk.layout_c = GK_LAYOUT_DENSE; blk.dtype_c = dd.dtype_d; blk.ldc = dd.ldd; c_p = d; }
+      if (p != panels - 1) e_p = nullptr;
+    }
+    s = gk_gemm(h, &blk, a_p, b_p, c_p, d_p, e_p, workspace, workspace_bytes, stream);
     if (s != GK_OK) {
       cudaStreamSynchronize(m->comm_stream);
       return s;
@@ -315,7 +346,7 @@ gk_status gk_mgpu_gemm_colshard_host(gk_handle h, const gk_gemm_desc* desc, cons
   for (int i = 0; i < 5; ++i)
     if (need[i] && (s = stage_reserve(h, i, need[i])) != GK_OK) return s;
   if ((s = host_streams_reserve(h, 2)) != GK_OK) return s;
-  if ((s = reserve_events(&m->events, 3 * static_cast<size_t>(R) + 4, cudaEventDisableTiming)) != GK_OK) return s;
+  if ((s = reserve_events(&m->events, 4 * static_cast<size_t>(R) + 4, cudaEventDisableTiming)) != GK_OK) return s;
   const bool timing = times != nullptr;
   if (timing && (s = reserve_events(&m->timed, 4 * static_cast<size_t>(R) + 4, cudaEventDefault)) != GK_OK) return s;
   char* a_dev = static_cast<char*>(h->stage_dev[0]);

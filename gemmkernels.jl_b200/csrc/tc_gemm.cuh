@@ -315,6 +315,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   // Let the next kernel of the stream begin its own set-up as SMs free up (it waits, as this one does
   // below, before touching global memory).
   pdl_launch_dependents();
+  const uint64_t t_entry = (p.debug & 8) ? global_timer_ns() : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(bar_full + 8u * s, 1);
@@ -742,6 +743,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       if ((p.debug & 8) && warp == 4 && lane == 0) {
         p.dbg_out[blockIdx.x * 16 + 7] += e1 - e0;
         p.dbg_out[blockIdx.x * 16 + 8] += clock64() - e1;
+        p.dbg_out[blockIdx.x * 16 + 15] = static_cast<long long>(global_timer_ns());   // last tile stored
       }
     }
   }
@@ -753,6 +755,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   if (warp == 2) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, p.tmem_cols);
+  }
+  if ((p.debug & 8) && threadIdx.x == 0) {   // the launch's timeline: entry and exit of this CTA
+    p.dbg_out[blockIdx.x * 16 + 13] = static_cast<long long>(t_entry);
+    p.dbg_out[blockIdx.x * 16 + 14] = static_cast<long long>(global_timer_ns());
   }
 }
 

@@ -310,11 +310,13 @@ typedef enum gk_mgpu_a_mode {
 /* This rank's block of the sharded product, device operands (collective when a_mode is BROADCAST:
  * every rank calls it with the same m, k, a_mode, root and k_panels).  desc describes the local block
  * (n = this rank's column count; may differ between ranks).  a: device buffer of the whole A on every
- * rank.  With GK_MGPU_A_BROADCAST, A travels in `k_panels` panels of K (0 = choose) over NCCL on the
- * handle's communication stream while the product of the panels that have arrived runs on `stream`
- * (D accumulates panel by panel; bias and activation are applied with the last panel), so the
- * transfer overlaps the arithmetic; a transposed A (trans_a = 1) is sent in one piece.  Enqueues
- * only; the result is complete when `stream` is. */
+ * rank.  With GK_MGPU_A_BROADCAST, A travels in `k_panels` panels (0 = choose) over NCCL on the
+ * handle's communication stream while the product of the panels that have arrived runs on `stream`,
+ * so the transfer overlaps the arithmetic.  A column-major A is cut into panels of K (D accumulates
+ * panel by panel, bias and activation are applied with the last panel; each extra panel re-reads
+ * and re-writes the D block, which the automatic choice weighs against the transfer it hides); a
+ * transposed A (trans_a = 1) is cut into panels of M, independent row blocks of D.  Enqueues only;
+ * the result is complete when `stream` is. */
 GK_API gk_status gk_mgpu_gemm_colshard(gk_handle h, const gk_gemm_desc* desc, void* a, int32_t a_mode,
                                        int32_t root, int32_t k_panels, const void* b, const void* c, void* d,
                                        const gk_epilogue_desc* epi, void* workspace, int64_t workspace_bytes,

@@ -89,6 +89,18 @@ def _worker(rank, world, port, out_dir):
             want = np.maximum(A @ B[:, cols] + Cm[:, cols] + bias[:, None], 0)
             assert np.array_equal(GK.to_numpy(d), want), ("device", panels)
             assert np.array_equal(GK.to_numpy(a), A), "A must have arrived on every rank"
+        # a transposed A (stored K x M) travels in panels of M: independent row blocks of D
+        conf_t = _conf(GK, M, shard.count, K, trans_a=True, with_c=True)
+        at = GK.to_cuarray(A.T.copy() if rank == 1 else np.zeros((K, M), np.float32), GK.Float16)
+        for panels in (0, 2, 3):
+            if rank != 1:
+                at.zero_()
+            d.zero_()
+            multigpu.colshard_matmul_device(conf_t, at, b, c, d, a_mode="broadcast", root=1, k_panels=panels, epilogue=epi,
+                                            transform_shared_to_global_d=relu)
+            torch.cuda.synchronize(); GK.poll_status()
+            assert np.array_equal(GK.to_numpy(d), want), ("device, transposed A", panels)
+            assert np.array_equal(GK.to_numpy(at), A.T)
         # resident form: nothing is exchanged
         multigpu.colshard_matmul_device(conf, a, b, c, d, a_mode="resident", epilogue=epi, transform_shared_to_global_d=relu)
         torch.cuda.synchronize()
