@@ -42,7 +42,7 @@ def _stale() -> bool:
     if not LIB_PATH.exists():
         return True
     t = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.inc"))
     deps.append(HERE.parent / "include" / "gemmkernels_b200.h")
     deps.append(Path(__file__))
     return any(d.stat().st_mtime > t for d in deps)

@@ -455,6 +455,21 @@ gk_status gk_measure_fp32_fma(gk_handle h, double* tflops, gk_stream stream) {
   return GK_OK;
 }
 
+gk_status gk_load_tuning(gk_handle h, const gk_tuning_entry* entries, int32_t count) {
+  clear_error();
+  if (!h || count < 0 || (count > 0 && !entries)) return set_error(GK_ERR_INVALID_ARGUMENT, "handle or entries is NULL, or a negative count");
+  for (int i = 0; i < count; ++i) {
+    const gk_tuning_entry& e = entries[i];
+    const bool tile_ok = e.tile_n == 0 || e.tile_n == 512 || (e.tile_n >= 32 && e.tile_n <= 256 && e.tile_n % 32 == 0);
+    if (!tile_ok || e.cta_group < 0 || e.cta_group > 2 || e.stages < 0 || e.raster_group < 0 || e.m < 1 || e.n < 1 || e.k < 1)
+      return set_error(GK_ERR_INVALID_CONFIG, "tuning entry %d is not usable (tile_n %d, cta_group %d, stages %d)", i, e.tile_n,
+                       e.cta_group, e.stages);
+  }
+  std::lock_guard<std::mutex> lock(h->mu);
+  h->tuning.assign(entries, entries + count);
+  return GK_OK;
+}
+
 gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
                         gk_gemm_plan* plan) {
   clear_error();
@@ -597,7 +612,7 @@ static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* 
       if (reinterpret_cast<uintptr_t>(workspace) & 255)
         return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
       TcProblem ps = pr;
-      ps.C = nullptr; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
+      ps.C = nullptr; ps.has_c = false; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
       ps.c_sn[0] = desc->m; ps.d_sn[0] = desc->m;
       ps.alpha = 1.0; ps.beta = 0.0; ps.epi = nullptr;
       if (pr.tile_n == 0) { ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg; }   // same tile as planned

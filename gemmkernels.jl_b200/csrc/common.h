@@ -89,6 +89,7 @@ struct gk_handle_s {
   // copy streams and events of the pipelined gk_gemm_host (created on first use)
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   std::vector<cudaEvent_t> events;
+  std::vector<gk_tuning_entry> tuning;   // loaded by gk_load_tuning (guarded by mu)
   gk::MgpuState* mgpu = nullptr;   // set by gk_mgpu_init, released by gk_mgpu_destroy / gk_destroy
 };
 

@@ -166,6 +166,7 @@ static bool build_tc_problem(const gk_contract_desc& d, Groups g, const void* a,
   if ((pr->A.mn_major ? pr->A.mn_ext[0] : pr->A.k_ext[0]) * es % 16 || (pr->B.mn_major ? pr->B.mn_ext[0] : pr->B.k_ext[0]) * es % 16)
     return no("contiguous mode is not a multiple of 16 bytes");
   pr->C = (d.beta != 0.0) ? c : nullptr; pr->D = dd;
+  pr->has_c = d.beta != 0.0;
   pr->dtype_c = d.dtype_c; pr->dtype_d = d.dtype_d;
   pr->m_ext0 = g.m[0].extent; pr->n_ext0 = g.n[0].extent;
   int64_t e2[2];

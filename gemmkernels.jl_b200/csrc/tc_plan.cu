@@ -202,7 +202,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
     if (c.n_sub * planes * c.bn > 256) {
       // an epilogue that also reads C (or writes through the general path) is several times
       // longer; exposed, it eats the gain
-      const bool light = pr.C == nullptr || pr.beta == 0.0;
+      const bool light = !pr.has_c;
       eff = pr.K >= 1024 ? (light ? kWideEff : 0.85) : 0.5;
     }
     const double t = static_cast<double>(waves) * c.bn * c.n_sub / eff;
@@ -216,6 +216,41 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
   *cg_out = bcg;
   *bn_out = bbn;
   *nsub_out = bns;
+}
+
+// Tile choices measured on B200 by the tuning sweep (generated file; see tuning.emit_table).
+static const gk_tuning_entry kBuiltinTuning[] = {
+#include "tuned_table.inc"
+    {-1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}   // terminator
+};
+
+// Nearest measured entry for this problem (see gk_tuning_entry), or nullptr.
+static const gk_tuning_entry* tuning_lookup(gk_handle h, const TcProblem& pr, gk_tuning_entry* copy) {
+  if (pr.rank5 || pr.number != GK_REAL || pr.batch > 1 || pr.k_split > 1) return nullptr;
+  const int has_c = pr.has_c ? 1 : 0;
+  const int ta = pr.A.mn_major ? 0 : 1, tb = pr.B.mn_major ? 1 : 0;
+  double best = 1e30;
+  const gk_tuning_entry* hit = nullptr;
+  auto consider = [&](const gk_tuning_entry& e) {
+    if (e.dtype != pr.A.dtype || e.trans_a != ta || e.trans_b != tb || e.has_c != has_c) return;
+    if (e.m < 1 || e.n < 1 || e.k < 1) return;
+    double dist = 0.0;
+    const double have[3] = {static_cast<double>(pr.M), static_cast<double>(pr.N), static_cast<double>(pr.K)};
+    const double want[3] = {static_cast<double>(e.m), static_cast<double>(e.n), static_cast<double>(e.k)};
+    for (int i = 0; i < 3; ++i) {
+      const double r = have[i] / want[i];
+      if (r > 1.5 || r < 1.0 / 1.5) return;
+      dist += std::fabs(std::log2(r));
+    }
+    if (dist < best) { best = dist; hit = &e; }
+  };
+  {
+    std::lock_guard<std::mutex> lock(h->mu);
+    for (const gk_tuning_entry& e : h->tuning) consider(e);
+    if (hit) { *copy = *hit; hit = copy; }       // the vector may be replaced once the lock is gone
+  }
+  for (const gk_tuning_entry* e = kBuiltinTuning; e->dtype >= 0; ++e) consider(*e);
+  return hit;
 }
 
 void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
@@ -236,6 +271,7 @@ void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, co
   pr.m_ext0 = d.m; pr.n_ext0 = d.n;
   pr.c_sm[0] = 1; pr.c_sn[0] = d.ldc; pr.d_sm[0] = 1; pr.d_sn[0] = d.ldd;
   pr.c_plane = d.plane_c; pr.d_plane = d.plane_d;
+  pr.has_c = d.layout_c != GK_LAYOUT_ZERO && d.beta != 0.0;
   pr.alpha = d.alpha; pr.beta = d.beta; pr.epi = epi;
   pr.tile_n = d.tile_n; pr.cta_group = d.cta_group; pr.stages = d.stages; pr.raster = d.raster;
   pr.raster_group = d.raster_group; pr.max_ctas = d.max_ctas; pr.debug = d.debug;
@@ -250,7 +286,20 @@ static int32_t clamp_div(int64_t ext0, int64_t ext1) {
   return static_cast<int32_t>(ext0);
 }
 
-gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out) {
+gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* out) {
+  TcProblem pr_tuned;
+  const TcProblem* prp = &pr_in;
+  if (pr_in.tile_n == 0 && pr_in.cta_group == 0) {
+    gk_tuning_entry copy;
+    if (const gk_tuning_entry* e = tuning_lookup(h, pr_in, &copy)) {
+      pr_tuned = pr_in;
+      pr_tuned.tile_n = e->tile_n; pr_tuned.cta_group = e->cta_group;
+      if (pr_tuned.stages == 0) pr_tuned.stages = e->stages;
+      if (pr_tuned.raster_group == 0 && pr_tuned.raster == GK_RASTER_AUTO) pr_tuned.raster_group = e->raster_group;
+      prp = &pr_tuned;
+    }
+  }
+  const TcProblem& pr = *prp;
   TcParams& p = out->params;
   std::memset(&p, 0, sizeof(p));
   const int es = dtype_size(pr.A.dtype);

@@ -27,6 +27,7 @@ struct TcProblem {
   // output / C: two-mode split of M and N with strides per mode
   const void* C = nullptr;
   void* D = nullptr;
+  bool has_c = false;            // the epilogue reads C (beta != 0 and C is not Layout.Zero), whether or not the pointer is known yet
   int32_t dtype_c = GK_F32, dtype_d = GK_F32;
   int64_t m_ext0 = 0, n_ext0 = 0;           // inner extents (== M, N for plain matrices)
   int64_t c_sm[2] = {1, 0}, c_sn[2] = {0, 0}, d_sm[2] = {1, 0}, d_sn[2] = {0, 0};

@@ -29,7 +29,7 @@ EXPORTS = (
     "gk_gemm_query", "gk_gemm", "gk_gemm_host", "gk_contract_query", "gk_contract", "gk_debug_marks", "gk_measure_fp32_fma",
     "gk_contract_static",
     "gk_mgpu_unique_id", "gk_mgpu_init", "gk_mgpu_destroy", "gk_mgpu_gemm_colshard", "gk_mgpu_gemm_colshard_host",
-    "gk_mgpu_host_plan", "gk_mgpu_broadcast",
+    "gk_mgpu_host_plan", "gk_mgpu_broadcast", "gk_load_tuning",
 )
 GK_MGPU_UNIQUE_ID_BYTES = 128
 GK_MGPU_A_RESIDENT, GK_MGPU_A_BROADCAST = 0, 1
@@ -80,6 +80,14 @@ class GemmPlan(C.Structure):
         ("smem_bytes", C.c_int32), ("tmem_columns", C.c_int32),
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32),
         ("workspace_bytes", C.c_int64),
+    ]
+
+
+class TuningEntry(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("has_c", C.c_int32),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32), ("raster_group", C.c_int32),
     ]
 
 
@@ -146,6 +154,8 @@ def _load() -> C.CDLL:
     lib.gk_contract_static.restype = C.c_int
     lib.gk_contract_static.argtypes = [C.POINTER(ContractDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p]
+    lib.gk_load_tuning.restype = C.c_int
+    lib.gk_load_tuning.argtypes = [C.c_void_p, C.POINTER(TuningEntry), C.c_int32]
     lib.gk_mgpu_unique_id.restype = C.c_int
     lib.gk_mgpu_unique_id.argtypes = [C.c_void_p]
     lib.gk_mgpu_init.restype = C.c_int

@@ -5,8 +5,11 @@ Mirrors what tuning/tune.jl of the reference does where it still applies:
   * a parameter sweep per (shape, transposes) — there: block/warp/operator shapes (tuning/wmma.jl:34-47);
     here: tile_n, cta_group, stages, raster_group;
   * "measure until no improvement" timing (tuning/tune.jl:143-163);
-  * each candidate's result is verified (tune.jl:172-176) — here against the output of the built-in
-    configuration, which the parity tests pin;
+  * each candidate's result is verified against an independent product (tune.jl:172-176 compares with
+    the cuBLAS baseline) — here sampled rows of a Float32 `torch.matmul` of the same operands;
+  * the winners become the defaults: `emit_table` writes them as the table compiled into the library
+    (csrc/tuned_table.inc), `load_into_library` hands them to a running library (gk_load_tuning), and
+    the planner consults both before its own cost model (tuning/wmma.jl:34-47 plays this role there);
   * an error taxonomy per candidate (tune.jl:90-179): config_error / cuda_error / invalid_result / timeout;
   * checkpoint and resume (tune.jl:315-357): one JSON line per measured candidate, measured keys are
     skipped on restart, unreadable lines are ignored;
@@ -217,9 +220,24 @@ def _operands(prob: Problem):
     if prob.with_c:
         c = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
         c.copy_(torch.rand(prob.n, prob.m, device="cuda", generator=g).t())
-    d_ref = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
     d = arrays.cuarray(eltypes.Float32, prob.m, prob.n)
-    _cache[prob.key()] = (a, b, c, d, d_ref, [False])
+    # the comparator: sampled rows of the product, computed by the library GEMM of torch in Float32
+    # (for TF32 problems on the operands as the tensor cores read them: low 13 mantissa bits cleared)
+    rows = torch.randperm(prob.m, device="cuda", generator=g)[: min(prob.m, 64)].sort().values
+    def as_read(t):
+        t = t.float()
+        return (t.view(torch.int32) & -8192).view(torch.float32) if prob.dtype == "TF32" else t
+    opa = as_read(a).t() if prob.trans_a else as_read(a)
+    opb = as_read(b).t() if prob.trans_b else as_read(b)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        want = opa[rows] @ opb
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    if c is not None:
+        want = want + c[rows]
+    _cache[prob.key()] = (a, b, c, d, rows, want)
     return _cache[prob.key()]
 
 
@@ -240,18 +258,13 @@ def _config(prob: Problem, cand: Candidate | None):
 
 def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None, nvml_handle=None) -> dict:
     """Verifies and times one candidate.  Categories: success, config_error (the engine refused the
-    combination), invalid_result (differs from the built-in configuration's output), timeout (a
-    device-side wait gave up), cuda_error (anything else the library reported)."""
+    combination), invalid_result (sampled rows differ from the Float32 torch.matmul of the same
+    operands), timeout (a device-side wait gave up), cuda_error (anything else the library reported)."""
     import torch
     from .config import ConfigError
     from .matmul import bind, matmul, poll_status, DeviceTimeout, GemmKernelsError
-    a, b, c, d, d_ref, have_ref = _operands(prob)
+    a, b, c, d, rows, want = _operands(prob)
     try:
-        if not have_ref[0]:
-            matmul(_config(prob, None), a, b, c, d_ref)
-            torch.cuda.synchronize()
-            poll_status()
-            have_ref[0] = True
         conf = _config(prob, cand)
         d.zero_()
         launch = bind(conf, a, b, c, d)
@@ -264,7 +277,7 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
         return {"category": "timeout", "message": str(e)[:200]}
     except GemmKernelsError as e:
         return {"category": "cuda_error", "message": str(e)[:200]}
-    err = (torch.linalg.norm(d - d_ref) / torch.linalg.norm(d_ref).clamp_min(1e-30)).item()
+    err = (torch.linalg.norm(d[rows].double() - want.double()) / torch.linalg.norm(want.double()).clamp_min(1e-30)).item()
     if not err <= rtol:
         return {"category": "invalid_result", "rel_error": err}
     if nvml is not None:
@@ -286,6 +299,75 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
             "tflops": 2.0 * prob.m * prob.n * prob.k / t / 1e6}
 
 
+# ------------------------------------------------------------------------------------------------
+# winners -> defaults
+# ------------------------------------------------------------------------------------------------
+_GK_DTYPE = {"Float16": 0, "BFloat16": 1, "TF32": 2}       # gk_dtype of the stored operands
+
+
+def _parse_problem_key(key: str):
+    """'Float16:2048x2048x2048:NT+C' -> (dtype, m, n, k, trans_a, trans_b, has_c)."""
+    dtype, shape, rest = key.split(":")
+    m, n, k = (int(x) for x in shape.split("x"))
+    has_c = rest.endswith("+C")
+    lay = rest[:2]
+    return dtype, m, n, k, lay[0] == "T", lay[1] == "T", has_c
+
+
+def winners(results: dict, min_gain: float = 0.02) -> list[dict]:
+    """One entry per measured problem whose fastest candidate beats the planner's own choice (the
+    candidate tn0-cg0-st0-rg0 of the same sweep) by at least `min_gain`; problems where the planner
+    was already within that margin need no entry."""
+    by_problem: dict = {}
+    for (pk, _), r in results.items():
+        if r.get("category") == "success":
+            by_problem.setdefault(pk, []).append(r)
+    out = []
+    for pk, recs in sorted(by_problem.items()):
+        top = min(recs, key=lambda r: r["time_us"])
+        base = next((r for r in recs if r["candidate"] == "tn0-cg0-st0-rg0"), None)
+        if top["tile_n"] == 0 or (base is not None and base["time_us"] <= top["time_us"] * (1.0 + min_gain)):
+            continue
+        dtype, m, n, k, ta, tb, has_c = _parse_problem_key(pk)
+        out.append(dict(dtype=_GK_DTYPE[dtype], trans_a=int(ta), trans_b=int(tb), has_c=int(has_c), m=m, n=n, k=k,
+                        tile_n=top["tile_n"], cta_group=top["cta_group"], stages=top["stages"],
+                        raster_group=top["raster_group"], time_us=top["time_us"],
+                        planner_time_us=base["time_us"] if base else None, problem=pk))
+    return out
+
+
+def emit_table(results_path, out_path) -> int:
+    """Writes the winners of a results file as the initialiser list the library compiles in
+    (csrc/tuned_table.inc).  Returns the number of entries."""
+    entries = winners(load_results(results_path))
+    lines = ["// Generated by `python -m gemmkernels_b200.tuning --emit-table` from a sweep on B200: the fastest verified",
+             "// candidate of each measured problem where it beat the planner's own choice by 2 % or more.",
+             "// {dtype, trans_a, trans_b, has_c, m, n, k, tile_n, cta_group, stages, raster_group}"]
+    for e in entries:
+        note = f"{e['time_us']:.1f} us" + (f" (planner {e['planner_time_us']:.1f} us)" if e["planner_time_us"] else "")
+        lines.append(f"    {{{e['dtype']}, {e['trans_a']}, {e['trans_b']}, {e['has_c']}, {e['m']}, {e['n']}, {e['k']}, "
+                     f"{e['tile_n']}, {e['cta_group']}, {e['stages']}, {e['raster_group']}}},   // {e['problem']}: {note}")
+    Path(out_path).write_text("\n".join(lines) + "\n")
+    return len(entries)
+
+
+def load_into_library(results_path, device_index=None) -> int:
+    """Hands the winners of a results file to the running library (gk_load_tuning) for this device:
+    from then on descriptors that leave the tile to the library get the measured choice."""
+    import ctypes as C
+    from . import _lib as L
+    from .matmul import _raise, handle
+    entries = winners(load_results(results_path))
+    arr = (L.TuningEntry * max(len(entries), 1))()
+    for i, e in enumerate(entries):
+        for f, _ in L.TuningEntry._fields_:
+            setattr(arr[i], f, e[f])
+    st = L.lib.gk_load_tuning(handle(device_index), arr, len(entries))
+    if st != L.GK_OK:
+        _raise(st)
+    return len(entries)
+
+
 DEFAULT_PROBLEMS = tuple(Problem(n, n, n, ta, tb) for n in (2048, 4096, 8192)
                          for ta in (False, True) for tb in (False, True))
 
@@ -299,7 +381,11 @@ def main(argv=None) -> int:
     ap.add_argument("--layouts", nargs="*", default=["NN", "NT", "TN", "TT"])
     ap.add_argument("--with-c", action="store_true", help="tune D = A*B + C instead of D = A*B")
     ap.add_argument("--quick", action="store_true", help="stages and raster band left to the built-in choice")
+    ap.add_argument("--emit-table", metavar="PATH", help="write the winners of --out as the library's compiled-in table and exit")
     args = ap.parse_args(argv)
+    if args.emit_table:
+        print(f"{emit_table(args.out, args.emit_table)} entries written to {args.emit_table}")
+        return 0
     probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype, args.with_c) for n in args.sizes for l in args.layouts]
     fn = (lambda p: candidates(p, stages=(0,), raster_group=(0,))) if args.quick else candidates
     tune(probs, args.out, candidate_fn=fn)

@@ -180,6 +180,27 @@ GK_API gk_status gk_measure_fp32_fma(gk_handle h, double* tflops, gk_stream stre
 GK_API gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue_desc* epi,
                         gk_gemm_plan* plan);
 
+/*
+ * Measured tile choices.  The reference ships what its tuning sweep found as the package's defaults
+ * (tuning/tune.jl, tuning/wmma.jl:34-47); here the sweep (python -m gemmkernels_b200.tuning) writes
+ * one entry per problem it measured, a generated table of them is compiled into the library, and a
+ * caller may load its own on top.  When a descriptor leaves tile_n and cta_group at 0, the planner
+ * takes the entry of the same element type, transposes and C use whose (m, n, k) matches exactly,
+ * else the nearest one whose extents are all within a factor 1.5; without one it falls back to its
+ * built-in cost model.  Entries apply to single real tensor-core products.
+ */
+typedef struct gk_tuning_entry {
+  int32_t dtype;        /* gk_dtype of A and B (GK_F32 stands for the TF32 path) */
+  int32_t trans_a, trans_b;
+  int32_t has_c;        /* measured with beta != 0 (the epilogue reads C) */
+  int64_t m, n, k;
+  int32_t tile_n, cta_group, stages, raster_group;   /* as in gk_gemm_desc; 0 = leave to the planner */
+} gk_tuning_entry;
+
+/* Replaces the handle's table with `count` entries (copied); count = 0 clears it.  The compiled-in
+ * table stays underneath: a loaded entry wins over a compiled-in one at equal distance. */
+GK_API gk_status gk_load_tuning(gk_handle h, const gk_tuning_entry* entries, int32_t count);
+
 /* Enqueues one GEMM on `stream`.  a, b, c, d are device pointers (c may be NULL when beta == 0 or
  * layout_c is ZERO; c == d is allowed).  epi may be NULL.  workspace is a 256-byte aligned device
  * buffer of workspace_bytes bytes (NULL / 0 when there is none); gk_gemm_query reports in
