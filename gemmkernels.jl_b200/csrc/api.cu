@@ -9,7 +9,6 @@
 #include "diag_gemm.cuh"
 #include "fpu_gemm.cuh"
 #include "simt_gemm.cuh"
-#include "splitk_reduce.cuh"
 #include "split_planes.cuh"
 #include "tc_plan.h"
 
@@ -310,26 +309,6 @@ static gk_status launch_simt(const gk_gemm_desc& d, const gk_epilogue_desc* epi,
 
 using namespace gk;
 
-// Split-K decision for a planned product: the plan's own tiles if they leave at least half of the CTA
-// slots idle; otherwise, when the tile shape was left to the library, 256 x 256 pair tiles cut along K
-// (small tiles were chosen to fill the SMs in one round, which a long K makes slow: every tile then
-// streams all of K with little operand reuse).  Returns the number of runs (1 = no split) and may
-// replace *pr's tile choice.
-static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
-  if (pr->tile_n == 0 && pr->cta_group == 0) {
-    TcProblem alt = *pr;
-    alt.tile_n = 256; alt.cta_group = 2;
-    TcLaunch La;
-    if (tc_plan(h, alt, false, &La) == GK_OK) {
-      const int splits = tc_choose_k_split(alt, La, h->sm_count);
-      if (splits > 1) { pr->tile_n = 256; pr->cta_group = 2; return splits; }
-    } else {
-      clear_error();
-    }
-  }
-  return tc_choose_k_split(*pr, L, h->sm_count);
-}
-
 // Register-only FP32 FMA throughput probe: kFmaPeakChains independent packed-FMA chains per thread.
 constexpr int kFmaPeakChains = 16;
 __global__ void __launch_bounds__(256) fma_peak_kernel(float* sink, int iters, float seed) {
@@ -498,10 +477,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
-    if (!(sp.a || sp.b) && desc->batch <= 1) {
-      const int splits = plan_k_split(h, &pr, L);
-      if (splits > 1) plan->workspace_bytes = static_cast<int64_t>(splits) * desc->m * desc->n * 4;   // optional: enables split-K
-    }
+    if (!(sp.a || sp.b) && desc->batch <= 1) plan->workspace_bytes = tc_split_workspace_bytes(h, pr, L);   // optional: enables split-K
   } else if (fam == 3 && fpu_eligible(*desc, nullptr, nullptr, nullptr, nullptr, nullptr)) {
     plan->kernel = 2;
     plan->grid = static_cast<int32_t>((desc->m / kFpuBM) * (desc->n / kFpuBN));
@@ -601,43 +577,7 @@ static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* 
       L.params.dbg_out = static_cast<long long*>(workspace);
       return tc_launch(L, st);
     }
-    // Few tiles and a long K: cut K into runs that fill the idle SMs, partial sums in the workspace
-    // (only when the caller passed one that is large enough: gk_gemm_query reports the size), then
-    // one reduction pass.
-    const int64_t plane_bytes = desc->m * desc->n * 4;
-    int splits = (workspace && !(sp.a || sp.b) && batch == 1) ? plan_k_split(h, &pr, L) : 1;
-    if (splits > 1 && static_cast<int64_t>(splits) * plane_bytes > workspace_bytes)
-      splits = static_cast<int>(workspace_bytes / plane_bytes);      // as many runs as the buffer holds
-    if (splits > 1) {
-      if (reinterpret_cast<uintptr_t>(workspace) & 255)
-        return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
-      TcProblem ps = pr;
-      ps.C = nullptr; ps.has_c = false; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
-      ps.c_sn[0] = desc->m; ps.d_sn[0] = desc->m;
-      ps.alpha = 1.0; ps.beta = 0.0; ps.epi = nullptr;
-      if (pr.tile_n == 0) { ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg; }   // same tile as planned
-      ps.k_split = splits; ps.split_stride = desc->m * desc->n;
-      TcLaunch Ls;
-      s = tc_plan(h, ps, true, &Ls);
-      if (s != GK_OK) return s;
-      s = tc_launch(Ls, st);
-      if (s != GK_OK) return s;
-      SplitKReduceParams r{};
-      r.partial = static_cast<const float*>(workspace); r.splits = Ls.params.k_split; r.stride = ps.split_stride;
-      r.M = static_cast<int>(desc->m); r.N = static_cast<int>(desc->n);
-      r.alpha = static_cast<float>(desc->alpha);
-      r.beta = (pr.C != nullptr) ? static_cast<float>(desc->beta) : 0.0f;
-      r.C = pr.C; r.ldc = desc->ldc; r.dtype_c = (desc->dtype_c == GK_F16 ? 0 : desc->dtype_c == GK_BF16 ? 1 : 2);
-      r.D = d; r.ldd = desc->ldd; r.dtype_d = (desc->dtype_d == GK_F16 ? 0 : desc->dtype_d == GK_BF16 ? 1 : 2);
-      if (epi) { r.bias = epi->bias; r.bias_axis = epi->bias_axis; r.act = epi->activation; }
-      const bool vec = desc->m % 4 == 0;
-      const int64_t units = (vec ? desc->m / 4 : desc->m) * desc->n;
-      const int blocks = static_cast<int>(std::min<int64_t>((units + 255) / 256, 8 * h->sm_count));
-      GK_CUDA_CHECK(launch_dependent(vec ? splitk_reduce_kernel<true> : splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0,
-                                     st, r));
-      return GK_OK;
-    }
-    return tc_launch(L, st);
+    return tc_run(h, pr, L, (sp.a || sp.b || batch > 1) ? nullptr : workspace, workspace_bytes, st);
   }
   // The SIMT families have no batch index: one launch per product of the batch.
   // (the FFMA kernel's vector loads need every product of a batch 16-byte aligned like the first)

@@ -25,8 +25,8 @@ struct ModeInfo {
 };
 
 struct Groups {
-  std::vector<ModeInfo> m, n, k;
-  int64_t M = 1, N = 1, K = 1;
+  std::vector<ModeInfo> m, n, k, b;   // free modes of A, of B, contracted modes, batch modes (in A, B and C)
+  int64_t M = 1, N = 1, K = 1, Bt = 1;
 };
 
 static int find_mode(const int32_t* modes, int rank, int label) {
@@ -61,9 +61,8 @@ static gk_status classify(const gk_contract_desc& d, Groups* g) {
     mi.extent = e;
     mi.sa = ia >= 0 ? d.strides_a[ia] : 0; mi.sb = ib >= 0 ? d.strides_b[ib] : 0;
     mi.sc = ic >= 0 ? d.strides_c[ic] : 0; mi.sd = ic >= 0 ? d.strides_d[ic] : 0;
-    if (ia >= 0 && ib >= 0 && ic >= 0)
-      return set_error(GK_ERR_UNSUPPORTED, "mode '%c' is in A, B and C: batched contractions are not supported", label);
-    if (ia >= 0 && ic >= 0) { g->m.push_back(mi); g->M *= e; }
+    if (ia >= 0 && ib >= 0 && ic >= 0) { g->b.push_back(mi); g->Bt *= e; }   // a batch mode: one contraction per index value
+    else if (ia >= 0 && ic >= 0) { g->m.push_back(mi); g->M *= e; }
     else if (ib >= 0 && ic >= 0) { g->n.push_back(mi); g->N *= e; }
     else if (ia >= 0 && ib >= 0) { g->k.push_back(mi); g->K *= e; }
     else return set_error(GK_ERR_INVALID_CONFIG, "mode '%c' appears in one tensor only", label);
@@ -312,15 +311,11 @@ static gk_status launch_gather(const gk_contract_desc& d, const Groups& g, const
   return GK_OK;
 }
 
-static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const void* a, const void* b, const void* c,
-                               void* dd, void* workspace, int64_t workspace_bytes, cudaStream_t stream,
-                               gk_gemm_plan* plan_only) {
-  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
-  if (!desc || desc->struct_size != sizeof(gk_contract_desc))
-    return set_error(GK_ERR_INVALID_ARGUMENT, "gk_contract_desc.struct_size does not match this library (%zu)", sizeof(gk_contract_desc));
-  Groups g;
-  gk_status s = classify(*desc, &g);
-  if (s != GK_OK) return s;
+// One contraction without batch modes (one index value of each batch mode of the caller's).
+static gk_status contract_one(gk_handle h, const gk_contract_desc* desc, const Groups& g, const void* a, const void* b,
+                              const void* c, void* dd, void* workspace, int64_t workspace_bytes, cudaStream_t stream,
+                              gk_gemm_plan* plan_only) {
+  gk_status s = GK_OK;
   TcProblem pr;
   std::string why;
   const void* a_chk = plan_only ? reinterpret_cast<const void*>(16) : a;
@@ -336,14 +331,18 @@ static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const 
         plan_only->smem_bytes = L.smem_bytes; plan_only->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
         plan_only->tile_m = kTcTileM * L.cg; plan_only->tile_n = L.params.bn * L.params.n_sub; plan_only->tile_k = L.params.bk;
         plan_only->stages = L.params.stages;
+        plan_only->workspace_bytes = tc_split_workspace_bytes(h, pr, L);   // optional: enables split-K
         return GK_OK;
       }
       if (L.params.debug & 8) {
         if (!workspace || workspace_bytes < static_cast<int64_t>(L.grid) * 16 * 8)
           return set_error(GK_ERR_INVALID_ARGUMENT, "debug counters need a workspace of %lld bytes", (long long)L.grid * 16 * 8);
         L.params.dbg_out = static_cast<long long*>(workspace);
+        return tc_launch(L, stream);
       }
-      return tc_launch(L, stream);
+      // a 256-byte aligned workspace lets a contraction with few output tiles and a long K be cut along K
+      const bool ws_ok = workspace && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0;
+      return tc_run(h, pr, L, ws_ok ? workspace : nullptr, workspace_bytes, stream);
     }
     why = gk_last_error_message();   // planning refused (e.g. box shapes): use the gather path
     clear_error();
@@ -365,6 +364,53 @@ static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const 
                      (long long)need, (long long)workspace_bytes);
   if (reinterpret_cast<uintptr_t>(workspace) & 7) return set_error(GK_ERR_INVALID_ARGUMENT, "workspace must be 8-byte aligned");
   return launch_gather(*desc, g, a, b, (desc->beta != 0.0) ? c : nullptr, dd, static_cast<int64_t*>(workspace), stream);
+}
+
+// Offsets (in elements) of every combination of the batch modes' index values, in A, B, C and D.
+struct BatchOffsets { int64_t a, b, c, d; };
+static constexpr int64_t kMaxBatch = 65536;
+
+static gk_status batch_offsets(const Groups& g, std::vector<BatchOffsets>* out) {
+  if (g.Bt > kMaxBatch)
+    return set_error(GK_ERR_INVALID_CONFIG, "batch modes span %lld contractions; at most %lld are launched from one call",
+                     (long long)g.Bt, (long long)kMaxBatch);
+  out->assign(static_cast<size_t>(g.Bt), BatchOffsets{0, 0, 0, 0});
+  for (int64_t i = 0; i < g.Bt; ++i) {
+    int64_t rem = i;
+    BatchOffsets o{0, 0, 0, 0};
+    for (const ModeInfo& m : g.b) {
+      const int64_t x = rem % m.extent;
+      rem /= m.extent;
+      o.a += x * m.sa; o.b += x * m.sb; o.c += x * m.sc; o.d += x * m.sd;
+    }
+    (*out)[static_cast<size_t>(i)] = o;
+  }
+  return GK_OK;
+}
+
+// Batch modes (labels in A, B and C) make the call a set of independent contractions, one per
+// combination of their index values: each is planned and launched on its own, on the same stream.
+static gk_status contract_impl(gk_handle h, const gk_contract_desc* desc, const void* a, const void* b, const void* c,
+                               void* dd, void* workspace, int64_t workspace_bytes, cudaStream_t stream,
+                               gk_gemm_plan* plan_only) {
+  if (!h) return set_error(GK_ERR_INVALID_ARGUMENT, "handle is NULL");
+  if (!desc || desc->struct_size != sizeof(gk_contract_desc))
+    return set_error(GK_ERR_INVALID_ARGUMENT, "gk_contract_desc.struct_size does not match this library (%zu)", sizeof(gk_contract_desc));
+  Groups g;
+  gk_status s = classify(*desc, &g);
+  if (s != GK_OK) return s;
+  if (g.b.empty() || plan_only) return contract_one(h, desc, g, a, b, c, dd, workspace, workspace_bytes, stream, plan_only);
+  std::vector<BatchOffsets> offs;
+  if ((s = batch_offsets(g, &offs)) != GK_OK) return s;
+  const size_t ea = dtype_size(desc->dtype_a), eb = dtype_size(desc->dtype_b), ec = dtype_size(desc->dtype_c),
+               ed = dtype_size(desc->dtype_d);
+  for (const BatchOffsets& o : offs) {
+    s = contract_one(h, desc, g, static_cast<const char*>(a) + o.a * ea, static_cast<const char*>(b) + o.b * eb,
+                     c ? static_cast<const char*>(c) + o.c * ec : nullptr, static_cast<char*>(dd) + o.d * ed, workspace,
+                     workspace_bytes, stream, nullptr);
+    if (s != GK_OK) return s;
+  }
+  return GK_OK;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -443,8 +489,18 @@ gk_status gk_contract_static(const gk_contract_desc* desc, const void* a, const 
   s = static_tables_for_current_device(&tables);   // first call on a device: symbol address look-up
   if (s != GK_OK) return s;
   // The tables are rewritten in full for this contraction before the gather kernel reads them
-  // (same stream), so nothing has to start at zero.
-  return launch_gather(*desc, g, a, b, (desc->beta != 0.0) ? c : nullptr, d, tables, static_cast<cudaStream_t>(stream));
+  // (same stream), so nothing has to start at zero.  Batch modes: one launch per index combination.
+  std::vector<BatchOffsets> offs;
+  if ((s = batch_offsets(g, &offs)) != GK_OK) return s;
+  const size_t ea = dtype_size(desc->dtype_a), eb = dtype_size(desc->dtype_b), ec = dtype_size(desc->dtype_c),
+               ed = dtype_size(desc->dtype_d);
+  for (const BatchOffsets& o : offs) {
+    s = launch_gather(*desc, g, static_cast<const char*>(a) + o.a * ea, static_cast<const char*>(b) + o.b * eb,
+                      (desc->beta != 0.0) ? static_cast<const char*>(c) + o.c * ec : nullptr, static_cast<char*>(d) + o.d * ed,
+                      tables, static_cast<cudaStream_t>(stream));
+    if (s != GK_OK) return s;
+  }
+  return GK_OK;
 }
 
 }  // extern "C"

@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       float bias_row = 0.0f;
       if (p.bias_axis == TC_BIAS_ROW && m_ok) bias_row = p.bias[m];
       const int m_in = m % p.m_div, m_out = m / p.m_div;
-      const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch;
+      const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch + split_off;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1 + bt * p.c_batch;
       for (int c = chunk_first; c < bn_tile; c += chunk_step) {
         uint32_t v[PLANES][32];
@@ -647,7 +647,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         if (fast_store) {
           // FP32 output, no C, no per-column bias: one FMA (+ max) and one coalesced store per
           // column; a warp writes 32 consecutive rows = 128 bytes of a column of D.
-          float* dp = static_cast<float*>(p.D) + split_off + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
+          float* dp = static_cast<float*>(p.D) + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
           if (ncols >= 32) {
             if (p.act == TC_ACT_RELU) {
 #pragma unroll

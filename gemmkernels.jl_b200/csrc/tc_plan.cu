@@ -5,6 +5,7 @@
 
 #include "common.h"
 #include "tc_gemm.cuh"
+#include "splitk_reduce.cuh"
 #include "tc_plan.h"
 
 namespace gk {
@@ -326,8 +327,8 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   p.k_blocks = (p.K + p.bk - 1) / p.bk;
   p.k_split = 1; p.kb_per_split = std::max(1, p.k_blocks); p.split_stride = 0;
   if (pr.k_split > 1) {
-    if (planes != 1 || pr.rank5 || pr.dtype_d != GK_F32 || pr.C != nullptr || pr.epi != nullptr || pr.alpha != 1.0)
-      return set_error(GK_ERR_INVALID_ARGUMENT, "split-K takes a plain real product into an FP32 workspace");
+    if (pr.dtype_d != GK_F32 || pr.C != nullptr || pr.epi != nullptr || pr.alpha != 1.0 || pr.m_ext0 < pr.M || pr.n_ext0 < pr.N)
+      return set_error(GK_ERR_INVALID_ARGUMENT, "split-K writes raw partial sums into a plain FP32 workspace");
     p.kb_per_split = (p.k_blocks + pr.k_split - 1) / pr.k_split;
     p.k_split = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;   // no empty runs
     p.split_stride = pr.split_stride;
@@ -585,7 +586,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
 
 int tc_choose_k_split(const TcProblem& pr, const TcLaunch& L, int sm_count) {
   const TcParams& p = L.params;
-  if (L.planes != 1 || L.rank5 || p.k_split != 1) return 1;
+  if (p.k_split != 1 || p.batch != 1) return 1;
   const int tiles = p.tiles_m * p.tiles_n;
   const int slots = std::max(1, sm_count / L.cg);
   if (tiles * 2 > slots || p.k_blocks < 16) return 1;
@@ -616,6 +617,74 @@ gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {
   cfg.attrs = at; cfg.numAttrs = n_at;
   void* args[1] = {const_cast<TcParams*>(&L.params)};
   GK_CUDA_CHECK(cudaLaunchKernelExC(&cfg, L.kernel, args));
+  return GK_OK;
+}
+
+// Split-K decision for a planned product: the plan's own tiles if they leave at least half of the CTA
+// slots idle; otherwise, when the tile shape was left to the library, 256 x 256 pair tiles cut along K
+// (small tiles were chosen to fill the SMs in one round, which a long K makes slow: every tile then
+// streams all of K with little operand reuse).  Returns the number of runs (1 = no split) and may
+// replace *pr's tile choice.
+static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
+  if (pr->tile_n == 0 && pr->cta_group == 0) {
+    TcProblem alt = *pr;
+    alt.tile_n = pr->number == GK_REAL ? 256 : 128; alt.cta_group = 2;
+    TcLaunch La;
+    if (tc_plan(h, alt, false, &La) == GK_OK) {
+      const int splits = tc_choose_k_split(alt, La, h->sm_count);
+      if (splits > 1) { pr->tile_n = alt.tile_n; pr->cta_group = 2; return splits; }
+    } else {
+      clear_error();
+    }
+  }
+  return tc_choose_k_split(*pr, L, h->sm_count);
+}
+
+int64_t tc_split_workspace_bytes(gk_handle h, const TcProblem& pr, const TcLaunch& L) {
+  TcProblem q = pr;
+  const int splits = plan_k_split(h, &q, L);
+  return splits > 1 ? static_cast<int64_t>(splits) * L.planes * pr.M * pr.N * 4 : 0;
+}
+
+gk_status tc_run(gk_handle h, const TcProblem& pr_in, const TcLaunch& L, void* workspace, int64_t workspace_bytes,
+                 cudaStream_t st) {
+  if (!workspace || workspace_bytes <= 0) return tc_launch(L, st);
+  TcProblem pr = pr_in;
+  const int64_t set_bytes = static_cast<int64_t>(L.planes) * pr.M * pr.N * 4;     // the planes of one K-run
+  int splits = plan_k_split(h, &pr, L);
+  if (splits > 1 && splits * set_bytes > workspace_bytes) splits = static_cast<int>(workspace_bytes / set_bytes);
+  if (splits <= 1) return tc_launch(L, st);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255)
+    return set_error(GK_ERR_INVALID_ARGUMENT, "the split-K workspace must be 256-byte aligned");
+  TcProblem ps = pr;
+  ps.C = nullptr; ps.has_c = false; ps.D = workspace; ps.dtype_c = GK_F32; ps.dtype_d = GK_F32;
+  ps.m_ext0 = pr.M; ps.n_ext0 = pr.N;
+  ps.c_sm[0] = 1; ps.c_sm[1] = 0; ps.d_sm[0] = 1; ps.d_sm[1] = 0;
+  ps.c_sn[0] = pr.M; ps.c_sn[1] = 0; ps.d_sn[0] = pr.M; ps.d_sn[1] = 0;
+  ps.c_plane = ps.d_plane = pr.M * pr.N;
+  ps.alpha = 1.0; ps.beta = 0.0; ps.epi = nullptr;
+  if (pr.tile_n == 0) { ps.tile_n = L.params.bn * L.params.n_sub; ps.cta_group = L.cg; }   // same tile as planned
+  ps.k_split = splits; ps.split_stride = set_bytes / 4;
+  TcLaunch Ls;
+  gk_status s = tc_plan(h, ps, true, &Ls);
+  if (s != GK_OK) return s;
+  if ((s = tc_launch(Ls, st)) != GK_OK) return s;
+  SplitKReduceParams r{};
+  r.partial = static_cast<const float*>(workspace); r.splits = Ls.params.k_split; r.planes = L.planes; r.stride = ps.split_stride;
+  r.M = static_cast<int>(pr.M); r.N = static_cast<int>(pr.N);
+  r.alpha = static_cast<float>(pr.alpha);
+  r.beta = (pr.C != nullptr) ? static_cast<float>(pr.beta) : 0.0f;
+  r.C = pr.C; r.dtype_c = tc_dtype_of(pr.dtype_c);
+  r.D = pr.D; r.dtype_d = tc_dtype_of(pr.dtype_d);
+  r.m_div = clamp_div(pr.m_ext0, pr.m_ext0 < pr.M ? 2 : 1); r.n_div = clamp_div(pr.n_ext0, pr.n_ext0 < pr.N ? 2 : 1);
+  r.c_sm0 = pr.c_sm[0]; r.c_sm1 = pr.c_sm[1]; r.c_sn0 = pr.c_sn[0]; r.c_sn1 = pr.c_sn[1]; r.c_plane = pr.c_plane;
+  r.d_sm0 = pr.d_sm[0]; r.d_sm1 = pr.d_sm[1]; r.d_sn0 = pr.d_sn[0]; r.d_sn1 = pr.d_sn[1]; r.d_plane = pr.d_plane;
+  if (pr.epi) { r.bias = pr.epi->bias; r.bias_axis = pr.epi->bias_axis; r.act = pr.epi->activation; }
+  const bool plain = L.planes == 1 && pr.m_ext0 >= pr.M && pr.n_ext0 >= pr.N && pr.d_sm[0] == 1 && (pr.C == nullptr || pr.c_sm[0] == 1);
+  const bool vec = plain && pr.M % 4 == 0;
+  const int64_t units = (vec ? pr.M / 4 : pr.M) * pr.N;
+  const int blocks = static_cast<int>(std::min<int64_t>((units + 255) / 256, 8 * h->sm_count));
+  GK_CUDA_CHECK(launch_dependent(vec ? splitk_reduce_kernel<true> : splitk_reduce_kernel<false>, dim3(blocks), dim3(256), 0, st, r));
   return GK_OK;
 }
 

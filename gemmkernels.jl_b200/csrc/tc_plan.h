@@ -66,5 +66,13 @@ void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, co
 // Tile choice, descriptors, grid, epilogue and (when `encode`) the TMA tensor maps.
 gk_status tc_plan(gk_handle h, const TcProblem& pr, bool encode, TcLaunch* out);
 gk_status tc_launch(const TcLaunch& L, cudaStream_t stream);
+// Runs the planned product `L` of `pr`.  Given a 256-byte aligned workspace, a product with few output
+// tiles and a long K is cut into K-runs over the otherwise idle SMs: FP32 partial sums go to the
+// workspace (as many runs as it holds) and a reduction pass applies alpha, beta, bias and activation
+// and writes D the way the one-pass epilogue would.  Without one (or when nothing is gained) `L` runs as is.
+gk_status tc_run(gk_handle h, const TcProblem& pr, const TcLaunch& L, void* workspace, int64_t workspace_bytes,
+                 cudaStream_t stream);
+// Bytes of workspace with which tc_run would cut K for this problem (0: it would not).
+int64_t tc_split_workspace_bytes(gk_handle h, const TcProblem& pr, const TcLaunch& L);
 
 }  // namespace gk

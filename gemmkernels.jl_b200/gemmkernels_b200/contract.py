@@ -60,9 +60,10 @@ def contract_(D, modes_d: str, A, modes_a: str, B, modes_b: str, alpha=1.0, beta
     """D[modes_d] = alpha * sum over shared modes of A[modes_a] * B[modes_b] + beta * C[modes_d].
 
     Tensors are torch CUDA tensors with any strides (Julia arrays are column-major: use `cuarray`).
-    C defaults to D (in place) when beta != 0.  If the contraction needs the gather kernel and no
-    `workspace` (uint8/int64 CUDA tensor) is given, one is allocated with torch for this call.
-    Returns D."""
+    C defaults to D (in place) when beta != 0.  A mode in A, B and D is a batch mode: one contraction
+    per index value.  If the contraction can use scratch memory (offset tables of the gather kernel,
+    partial sums of a split along K) and no `workspace` (uint8/int64 CUDA tensor) is given, the
+    package lends its grow-only buffer of this device and stream.  Returns D."""
     import torch
     if beta != 0 and C_in is None:
         C_in = D
@@ -71,16 +72,17 @@ def contract_(D, modes_d: str, A, modes_a: str, B, modes_b: str, alpha=1.0, beta
     ws_ptr, ws_bytes = None, 0
     with torch.cuda.device(dev):
         h = handle(dev)
+        s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
         if workspace is None:
             plan = L.GemmPlan()
             st = L.lib.gk_contract_query(h, C.byref(d), C.byref(plan))
             if st != L.GK_OK:
                 _raise(st)
             if plan.workspace_bytes:
-                workspace = torch.empty(plan.workspace_bytes // 8 + 1, dtype=torch.int64, device=D.device)
+                from .matmul import lend_workspace
+                workspace = lend_workspace(D.device, s, plan.workspace_bytes)
         if workspace is not None:
             ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
-        s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
         st = L.lib.gk_contract(h, C.byref(d), A.data_ptr(), B.data_ptr(), C_in.data_ptr() if C_in is not None else None,
                                D.data_ptr(), ws_ptr, ws_bytes, C.c_void_p(s))
     if st != L.GK_OK:

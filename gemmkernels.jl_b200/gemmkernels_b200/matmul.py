@@ -273,28 +273,34 @@ def _check_user_workspace(h, desc, epi, workspace):
         raise GemmKernelsError("workspace must be 256-byte aligned")
 
 
+def lend_workspace(device, stream: int, nbytes: int):
+    """The lent scratch buffer of (device, stream), at least `nbytes` long: allocated on first need,
+    replaced only by a larger one (never per call)."""
+    import torch
+    key = (device.index, int(stream))
+    with _workspaces_lock:
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            size = max(nbytes, 2 * (ws.numel() if ws is not None else 0))
+            # allocate under the caller's stream so the caching allocator ties the block to it
+            if int(stream) == torch.cuda.current_stream(device).cuda_stream:
+                ws = torch.empty(size, dtype=torch.uint8, device=device)
+            else:
+                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream), device=device)):
+                    ws = torch.empty(size, dtype=torch.uint8, device=device)
+            _workspaces[key] = ws
+    return ws
+
+
 def _auto_workspace(h, desc, epi, like, stream: int):
     """The lent workspace of (device, stream), grown to the size gk_gemm_query reports, or None."""
-    import torch
     plan = L.GemmPlan()
     st = L.lib.gk_gemm_query(h, C.byref(desc), C.byref(epi), C.byref(plan))
     if st != L.GK_OK:
         _raise(st)
     if not plan.workspace_bytes:
         return None
-    key = (like.device.index, int(stream))
-    with _workspaces_lock:
-        ws = _workspaces.get(key)
-        if ws is None or ws.numel() < plan.workspace_bytes:
-            # allocate under the caller's stream so the caching allocator ties the block to it
-            size = max(plan.workspace_bytes, 2 * (ws.numel() if ws is not None else 0))
-            if int(stream) == torch.cuda.current_stream(like.device).cuda_stream:
-                ws = torch.empty(size, dtype=torch.uint8, device=like.device)
-            else:
-                with torch.cuda.stream(torch.cuda.ExternalStream(int(stream), device=like.device)):
-                    ws = torch.empty(size, dtype=torch.uint8, device=like.device)
-            _workspaces[key] = ws
-    return ws
+    return lend_workspace(like.device, stream, plan.workspace_bytes)
 
 
 def matmul(conf: Config, a, b, c, d, *,

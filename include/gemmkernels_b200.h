@@ -221,12 +221,16 @@ GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, c
  * benchmarks/tensor-contractions/run.jl:88-131 (custom layouts that map one contraction onto the
  * GEMM kernels) with an entry point, e.g. GemmKernels.contract!(D, "abcd", A, "aebf", B, "dfce").
  * A mode label is any integer (characters, usually).  A label in A and C is a free mode of A, in B
- * and C a free mode of B, in A and B a contracted mode; a label in all three is rejected.  Strides
+ * and C a free mode of B, in A and B a contracted mode; a label in all three is a batch mode: the
+ * call is one independent contraction per value of that index (launched one by one on the stream;
+ * at most 65536).  Strides
  * are in elements and arbitrary (column-major tensors have strides 1, e0, e0*e1, ...); C and D share
  * modes_c / extents_c and have their own strides.  Tensors are read in place: when every index
  * splits into at most two modes that tile into TMA boxes the tensor cores run it through 5-D tensor
  * maps; otherwise a gather kernel runs it and needs a workspace (gk_contract_query reports
- * plan.kernel == 5 and plan.workspace_bytes).
+ * plan.kernel == 5 and plan.workspace_bytes).  On the tensor-core path a reported workspace is
+ * optional, as for gk_gemm: given one (256-byte aligned), few output tiles with a long contracted
+ * index are cut along K over the idle SMs.
  */
 #define GK_MAX_MODES 8
 
@@ -249,8 +253,9 @@ typedef struct gk_contract_desc {
 GK_API gk_status gk_contract_query(gk_handle h, const gk_contract_desc* desc, gk_gemm_plan* plan);
 
 /* Enqueues the contraction on `stream`.  c may be NULL when beta == 0; c == d is allowed.
- * workspace / workspace_bytes: device scratch for the gather path (offset tables, 8-byte aligned);
- * may be NULL / 0 when the query reports workspace_bytes == 0. */
+ * workspace / workspace_bytes: device scratch — the gather path's offset tables (required there,
+ * 8-byte aligned) or the partial sums of a split along K (optional); may be NULL / 0 when the query
+ * reports workspace_bytes == 0. */
 GK_API gk_status gk_contract(gk_handle h, const gk_contract_desc* desc, const void* a, const void* b,
                              const void* c, void* d, void* workspace, int64_t workspace_bytes,
                              gk_stream stream);

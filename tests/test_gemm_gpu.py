@@ -677,6 +677,61 @@ def test_contraction_alpha_beta_and_three_index_case():
     assert O.normwise_error(GK.to_numpy(d), want) <= TOL_TENSOR
 
 
+@pytest.mark.parametrize("force_gather", [False, True])
+def test_contraction_with_batch_modes(force_gather):
+    """A label in A, B and D is a batch mode: D[m,n,p,q] = sum_k A[m,k,p,q] B[k,q,n,p] is one product per
+    (p, q), each on its own slices (here 3 x 2 of them, B's batch strides permuted)."""
+    rng = np.random.default_rng(21)
+    m, n, k, p, q = 128, 96, 64, 3, 2
+    A = rng.integers(-2, 3, (m, k, p, q)).astype(np.float16)
+    B = rng.integers(-2, 3, (k, q, n, p)).astype(np.float16)
+    Cm = rng.integers(-3, 4, (m, n, p, q)).astype(np.float32)
+    d = _julia_tensor(Cm)
+    GK.contract_(d, "mnpq", _julia_tensor(A), "mkpq", _julia_tensor(B), "kqnp", alpha=2.0, beta=1.0, force_gather=force_gather)
+    torch.cuda.synchronize(); GK.poll_status()
+    want = 2.0 * np.einsum("mkpq,kqnp->mnpq", A.astype(np.float32), B.astype(np.float32)) + Cm
+    assert np.array_equal(GK.to_numpy(d), want)
+    assert np.array_equal(want, O.contract(A, "mkpq", B, "kqnp", "mnpq", 2.0, 1.0, Cm))
+
+
+def test_split_k_for_contractions_and_two_plane_products():
+    """Few output tiles and a long contracted index: with a workspace the contraction (two-mode
+    strides of D) and the complex product (two accumulator planes) are cut along K as well."""
+    rng = np.random.default_rng(23)
+    # D[a,b,c] = sum_{e,f} A[a,e,b,f] B[f,c,e]: M = (a,b) = 64*4, N = c = 128, K = (e,f) = 64*128 = 8192
+    A = rng.integers(-2, 3, (64, 64, 4, 128)).astype(np.float16)
+    B = rng.integers(-2, 3, (128, 128, 64)).astype(np.float16)
+    a, b = _julia_tensor(A), _julia_tensor(B)
+    d = GK.cuarray(GK.Float32, 64, 4, 128)
+    plan = GK.contract_query(d, "abc", a, "aebf", b, "fce")
+    assert plan.kernel == 1 and plan.workspace_bytes >= 2 * 256 * 128 * 4, (plan.kernel, plan.workspace_bytes)
+    GK.contract_(d, "abc", a, "aebf", b, "fce")                  # the package lends the workspace
+    torch.cuda.synchronize(); GK.poll_status()
+    want = O.contract(A, "aebf", B, "fce", "abc")
+    assert np.array_equal(GK.to_numpy(d), want)
+    d2 = GK.cuarray(GK.Float32, 64, 4, 128)
+    tiny = torch.zeros(64, dtype=torch.int64, device="cuda")       # too small to split: same numbers, unsplit
+    GK.contract_(d2, "abc", a, "aebf", b, "fce", workspace=tiny)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert torch.equal(d2, d)
+    # planar complex, 256 x 256 x 8192, interleaved Complex{Float32} result with C and alpha/beta
+    M, N, K = 256, 256, 8192
+    Ac = rng.integers(-2, 3, (2, M, K)).astype(np.float16); Bc = rng.integers(-2, 3, (2, K, N)).astype(np.float16)
+    Cc = rng.integers(-3, 4, (2, M, N)).astype(np.float32)
+    dc = planar(Cc)
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.WMMAComplexOp[16, 16, 16, GK.Float16, GK.Float32],
+                         global_a_layout=Layout.SplitColMajor[GK.Float16], global_b_layout=Layout.SplitColMajor[GK.Float16],
+                         global_c_layout=Layout.SplitColMajor[GK.Float32], global_d_layout=Layout.SplitColMajor[GK.Float32],
+                         block_shape=(64, 64, 32))
+    pa, pb = planar(Ac), planar(Bc)
+    assert GK.query(conf, pa, pb, dc, dc).workspace_bytes >= 2 * 2 * M * N * 4
+    GK.matmul(conf, pa, pb, dc, dc, transform_shared_to_regs_a=Transform.Elementwise(Transform.Scale(2.0)))
+    torch.cuda.synchronize(); GK.poll_status()
+    re, im = O.complex_gemm(Ac[0], Ac[1], Bc[0], Bc[1], Cc[0], Cc[1], 2.0, 1.0)
+    got = GK.to_numpy(dc)
+    assert np.array_equal(got[..., 0], re) and np.array_equal(got[..., 1], im)
+
+
 def test_contraction_errors():
     a = GK.cuarray(GK.Float16, 8, 8); b = GK.cuarray(GK.Float16, 8, 4); d = GK.cuarray(GK.Float32, 8, 8)
     with pytest.raises(GK.DimensionMismatch):
