@@ -20,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libgemmkernels_b200.so"
 
-SOURCES = ["tc_kernels_rank3.cu", "tc_kernels_rank5.cu", "api.cu", "tc_plan.cu", "contract.cu", "mgpu.cu"]
+SOURCES = ["tc_kernels_rank3.cu", "tc_kernels_rank5.cu", "api.cu", "tc_plan.cu", "contract.cu", "mgpu.cu", "tc_kernels_generic.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

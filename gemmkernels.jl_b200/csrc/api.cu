@@ -217,7 +217,11 @@ static gk_status launch_diag(gk_handle h, const gk_gemm_desc& d, const gk_epilog
 }
 
 // Which kernel family serves this descriptor: 1 tcgen05, 2 FP32 FFMA, 3 generic SIMT, 4 diagonal.
-static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+// *generic_loads is set when the tensor-core kernel must read its operands with ordinary loads
+// (TMA cannot address them: alignment), which the reference's bounds-checked layouts correspond to
+// (src/layout.jl:111-184, chosen in src/matmul.jl:121-156).
+static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why, bool* generic_loads = nullptr) {
+  if (generic_loads) *generic_loads = false;
   if (d.layout_a == GK_LAYOUT_DIAGONAL) return 4;
   // Nothing to multiply (Layout.Zero operands, alpha == 0, K == 0): D = act(beta * C + bias),
   // which the generic kernel does without touching A or B.
@@ -227,14 +231,10 @@ static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, st
   const bool tc_types = (d.compute == GK_F16 || d.compute == GK_BF16 || d.compute == GK_TF32);
   if (d.op == GK_OP_TCGEN05 || (d.op == GK_OP_AUTO && tc_types)) {
     if (tc_eligible(d, a, b, why)) return 1;
-    if (d.number != GK_REAL) return -1;        // no SIMT complex/dual kernel
-    if (d.compute == GK_TF32) return -1;       // an FP32 SIMT result is not a TF32 result: refuse
-    // Only a TMA obstacle (alignment, leading dimension) may reroute a tensor-core request, and
-    // only for 16-bit inputs, whose FP32-accumulated SIMT product meets the same tolerance.
-    const bool f16 = d.dtype_a == GK_F16 && d.dtype_b == GK_F16 && d.compute == GK_F16;
-    const bool bf16 = d.dtype_a == GK_BF16 && d.dtype_b == GK_BF16 && d.compute == GK_BF16;
-    if (!(f16 || bf16) || d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE) return -1;
-    return 3;
+    // Only TMA's alignment rule stands in the way: the same kernel, fed by bounds-checked loads.
+    std::string why2;
+    if (generic_loads && tc_eligible_generic(d, &why2)) { *generic_loads = true; return 1; }
+    return -1;                                 // no SIMT complex/dual kernel; an FP32 SIMT result is not a TF32 result
   }
   if (d.number != GK_REAL) { if (why) *why = "complex and dual products need the TCGen05Operator"; return -1; }
   return 3;
@@ -462,7 +462,8 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
   if (sp.a) { planar.lda = sp.a_ld; planar.plane_a = sp.a_ld * sp.a_cols; }
   if (sp.b) { planar.ldb = sp.b_ld; planar.plane_b = sp.b_ld * sp.b_cols; }
   desc = &planar;
-  const int fam = choose_family(*desc, nullptr, nullptr, &why);
+  bool generic_loads = false;
+  const int fam = choose_family(*desc, nullptr, nullptr, &why, &generic_loads);
   if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
   plan->kernel = fam;
   if (fam == 4) return launch_diag(h, *desc, epi, nullptr, nullptr, nullptr, nullptr, nullptr, plan);
@@ -470,6 +471,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     TcLaunch L;
     TcProblem pr;
     tc_problem_from_gemm(*desc, epi, nullptr, nullptr, nullptr, nullptr, &pr);
+    pr.generic = generic_loads;
     s = tc_plan(h, pr, false, &L);
     if (s != GK_OK) return s;
     plan->grid = L.grid; plan->block = tc_threads(L.planes); plan->cluster = L.cg;
@@ -558,7 +560,8 @@ static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* 
     }
     desc = &planar;
   }
-  int fam = choose_family(*desc, a, b, &why);
+  bool generic_loads = false;
+  int fam = choose_family(*desc, a, b, &why, &generic_loads);
   if (fam < 0) return set_error(GK_ERR_INVALID_CONFIG, "no kernel takes this GEMM: %s", why.c_str());
   if (fam == 4) return launch_diag(h, *desc, epi, a, b, c, d, st, nullptr);
   if (desc->m == 0 || desc->n == 0) return GK_OK;
@@ -568,6 +571,7 @@ static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* 
     TcLaunch L;
     TcProblem pr;
     tc_problem_from_gemm(*desc, epi, a, b, c, d, &pr);
+    pr.generic = generic_loads;
     s = tc_plan(h, pr, true, &L);
     if (s != GK_OK) return s;
     if (L.params.debug & 8) {

@@ -91,6 +91,12 @@ struct TcParams {
   uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;  // bytes
   uint32_t a_swz, b_swz;      // descriptor swizzle field per operand (ptx.cuh: smem_desc_hi)
   uint32_t tmem_cols;         // power of two >= acc_stages * n_sub * acc_planes * bn
+  // GENERIC kernels (operands that TMA cannot address: a base or leading dimension that is not a
+  // multiple of 16 bytes): the producer warps read A and B with bounds-checked loads and write the same
+  // swizzled stage layout themselves.  16-bit element types, one plane, one CTA per tile.
+  const void* ga; const void* gb;
+  int64_t g_lda, g_ldb;          // elements between consecutive values of the strided index
+  int64_t g_a_batch, g_b_batch;  // elements between the operands of consecutive products of a batch
   // Tensor contractions split an index of the product in two modes: index = in + div * out.
   // For a plain matrix the divisor is INT32_MAX (out == 0).  RANK5 kernels use these in the
   // producers (5-D tensor maps: {in, out} of the contiguous index, {in, out} of the other, plane).
@@ -284,8 +290,35 @@ __device__ __forceinline__ void tc_tile_coords(const TcParams& p, int t, int& tm
   tn = along_n ? a : b;
 }
 
-template <int CG, int PLANES, bool TF32, bool RANK5>
+// One box of a stage written by a warp with ordinary loads: `rows` rows of 128 bytes (64 16-bit
+// elements of the contiguous index u, starting at u0) for the strided index v0 .. v0 + rows - 1, in
+// the layout TMA's 128-byte swizzle produces (16-byte chunk c of row r lands at chunk c ^ (r % 8);
+// dst is 1024-byte aligned).  Elements outside [0, U) x [0, V) read as zero, as TMA fills them.
+__device__ __forceinline__ void tc_fill_box_generic(uint8_t* dst, const uint16_t* g, int64_t ld, int u0, int v0, int U,
+                                                    int V, int rows, int lane) {
+  for (int idx = lane; idx < rows * 8; idx += 32) {
+    const int r = idx >> 3, c = idx & 7;
+    const int u = u0 + c * 8, v = v0 + r;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (v < V && u < U) {
+      const uint16_t* src = g + static_cast<int64_t>(v) * ld + u;
+      if (u + 8 <= U && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        val = *reinterpret_cast<const uint4*>(src);
+      } else {
+        uint16_t e[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = (u + j < U) ? src[j] : static_cast<uint16_t>(0);
+        val.x = e[0] | (static_cast<uint32_t>(e[1]) << 16); val.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
+        val.z = e[4] | (static_cast<uint32_t>(e[5]) << 16); val.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + r * 128 + ((c ^ (r & 7)) << 4)) = val;
+  }
+}
+
+template <int CG, int PLANES, bool TF32, bool RANK5, bool GENERIC = false>
 __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+  static_assert(!GENERIC || (CG == 1 && PLANES == 1 && !TF32 && !RANK5), "generic loads: one CTA, one plane, 16-bit types");
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes and the pattern is a function of the address.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -318,7 +351,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const uint64_t t_entry = (p.debug & 8) ? global_timer_ns() : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(bar_full + 8u * s, 1);
+      mbar_init(bar_full + 8u * s, GENERIC ? 2 : 1);   // TMA: one arrival that also expects the bytes; generic: one per producer warp
       mbar_init(bar_empty + 8u * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -328,8 +361,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
     fence_mbar_init();
-    prefetch_tensormap(&p.tm_a);
-    prefetch_tensormap(&p.tm_b);
+    if constexpr (!GENERIC) {
+      prefetch_tensormap(&p.tm_a);
+      prefetch_tensormap(&p.tm_b);
+    }
   }
   if (warp == 2) {
     tmem_alloc<CG>(tmem_slot, p.tmem_cols);
@@ -352,7 +387,54 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const uint32_t acc_cols = p.n_sub * sub_cols;  // TMEM columns per accumulator stage
   const bool two_acc = p.acc_stages == 2;
 
-  if (warp == 0 || warp == 3) {
+  if constexpr (GENERIC) {
+    if (warp == 0 || warp == 3) {
+      // -------------------------------------------------------------- producers with ordinary loads
+      // Warp 0 fills A's part of each stage, warp 3 B's; a stage is full once both have arrived.
+      const bool is_a = warp == 0;
+      const bool mn_major = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
+      const int boxes = is_a ? p.a_boxes : p.b_boxes;
+      const int box_mn = is_a ? p.a_box_mn : p.b_box_mn;
+      const uint32_t box_bytes = is_a ? p.a_box_bytes : p.b_box_bytes;
+      const uint32_t part_off = is_a ? 0u : static_cast<uint32_t>(p.a_planes * p.a_plane_bytes);
+      const int64_t ld = is_a ? p.g_lda : p.g_ldb;
+      const int mn_ext = is_a ? p.M : p.N;
+      const int rows_k_major = is_a ? kTcTileM : p.bn;     // rows of the one box of a K-major operand
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      pdl_wait();
+      for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
+        int tm, tn;
+        const int bt = t / units_per_product;
+        tc_tile_coords(p, (t - bt * units_per_product) / p.k_split, tm, tn);
+        const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        const int mn0 = is_a ? tm * kTcTileM : tn * bn_tile;
+        const uint16_t* g = static_cast<const uint16_t*>(is_a ? p.ga : p.gb) + bt * (is_a ? p.g_a_batch : p.g_b_batch);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* stage = smem_gen + s * stage_bytes + part_off;
+          const int k0 = kb * p.bk;
+          if (mn_major) {
+            for (int bx = 0; bx < boxes; ++bx)
+              tc_fill_box_generic(stage + bx * box_bytes, g, ld, mn0 + bx * box_mn, k0, mn_ext, p.K, p.bk, lane);
+          } else {
+            tc_fill_box_generic(stage, g, ld, k0, mn0, p.K, mn_ext, rows_k_major, lane);
+          }
+          fence_proxy_async_smem();   // the tensor cores read shared memory through the asynchronous proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_full + 8u * s);
+          if (++s == p.stages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  }
+  if (!GENERIC && (warp == 0 || warp == 3)) {
     // ------------------------------------------------------------------ TMA producers
     // Warp 0 loads A, warp 3 loads B: issuing a copy costs its thread on the order of 100
     // cycles, and splitting the operands keeps each producer loop well under one k-block of MMA.

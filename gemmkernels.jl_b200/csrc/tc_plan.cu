@@ -19,7 +19,8 @@ static int tc_dtype_of(int32_t dt) {
   }
 }
 
-bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+// Everything tc_eligible asks for except TMA's alignment rules.
+static bool tc_eligible_types(const gk_gemm_desc& d, std::string* why) {
   auto no = [&](const char* s) { if (why) *why = s; return false; };
   if (d.layout_a != GK_LAYOUT_DENSE || d.layout_b != GK_LAYOUT_DENSE)
     return no("operand layout is not dense");
@@ -33,6 +34,20 @@ bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::strin
     return no("C/D element type must be Float16, BFloat16 or Float32");
   if (d.m < 1 || d.n < 1 || d.k < 1) return no("empty dimension");
   if (d.m > INT32_MAX / 2 || d.n > INT32_MAX / 2 || d.k > INT32_MAX / 2) return no("dimension too large");
+  return true;
+}
+
+bool tc_eligible_generic(const gk_gemm_desc& d, std::string* why) {
+  if (!tc_eligible_types(d, why)) return false;
+  auto no = [&](const char* s) { if (why) *why = s; return false; };
+  if (d.number != GK_REAL) return no("complex and dual operands must be 16-byte aligned planes");
+  if (dtype_size(d.dtype_a) != 2) return no("32-bit operands must be 16-byte aligned");
+  return true;
+}
+
+bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::string* why) {
+  if (!tc_eligible_types(d, why)) return false;
+  auto no = [&](const char* s) { if (why) *why = s; return false; };
   const int es = dtype_size(d.dtype_a);
   // TMA: 16-byte aligned base, strides that are multiples of 16 bytes.
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
@@ -150,6 +165,8 @@ const void* tc_kernel_select_r(int cg, int planes, bool tf32);
 extern template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32);
 extern template const void* tc_kernel_select_r<true>(int cg, int planes, bool tf32);
 
+const void* tc_kernel_generic();   // tc_kernels_generic.cu: <1, 1, false, false, GENERIC>
+
 static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5) {
   return rank5 ? tc_kernel_select_r<true>(cg, planes, tf32) : tc_kernel_select_r<false>(cg, planes, tf32);
 }
@@ -188,6 +205,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
   for (const Cand& c : cands) {
     if (c.n_sub * planes * c.bn > 512) continue;  // accumulators of one tile must fit 512 TMEM columns
     if (c.n_sub > 1 && pr.rank5) continue;
+    if (pr.generic && (c.cg != 1 || c.n_sub != 1)) continue;
     if ((c.bn / c.cg) % n_unit) continue;
     if (pr.cta_group && c.cg != pr.cta_group) continue;
     if (pr.tile_n && c.bn * c.n_sub != pr.tile_n) continue;
@@ -210,7 +228,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
     if (t < best) { best = t; bcg = c.cg; bbn = c.bn; bns = c.n_sub; }
   }
   if (best == 1e300) {  // overrides that match no candidate: honour them if they are valid
-    bcg = pr.cta_group ? pr.cta_group : 1;
+    bcg = pr.generic ? 1 : pr.cta_group ? pr.cta_group : 1;
     bbn = pr.tile_n ? pr.tile_n : 128;
     if (bbn == 512) { bbn = 256; bns = 2; }
   }
@@ -227,7 +245,7 @@ static const gk_tuning_entry kBuiltinTuning[] = {
 
 // Nearest measured entry for this problem (see gk_tuning_entry), or nullptr.
 static const gk_tuning_entry* tuning_lookup(gk_handle h, const TcProblem& pr, gk_tuning_entry* copy) {
-  if (pr.rank5 || pr.number != GK_REAL || pr.batch > 1 || pr.k_split > 1) return nullptr;
+  if (pr.rank5 || pr.generic || pr.number != GK_REAL || pr.batch > 1 || pr.k_split > 1) return nullptr;
   const int has_c = pr.has_c ? 1 : 0;
   const int ta = pr.A.mn_major ? 0 : 1, tb = pr.B.mn_major ? 1 : 0;
   double best = 1e30;
@@ -311,6 +329,9 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   choose_tile(pr, h->sm_count, planes, &cg, &bn, &n_sub);
   if (cg != 1 && cg != 2)
     return set_error(GK_ERR_INVALID_CONFIG, "cta_group must be 1 or 2, got %d", cg);
+  if (pr.generic && (cg != 1 || n_sub != 1 || planes != 1 || tf32 || pr.rank5))
+    return set_error(GK_ERR_INVALID_CONFIG, "operands that are not 16-byte aligned run one CTA per tile (cta_group = 1, "
+                     "tile_n <= 256), real 16-bit types only");
   if (bn < 32 || bn > 256 || bn % 32 || n_sub * planes * bn > 512 || (cg == 2 && bn % 64))
     return set_error(GK_ERR_INVALID_CONFIG,
                      "tile_n = %d is not usable (multiple of 32 (64 for CTA pairs), <= %d)", bn * n_sub,
@@ -527,8 +548,15 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   out->planes = planes;
   out->tf32 = tf32;
   out->rank5 = pr.rank5;
+  out->generic = pr.generic;
   out->smem_bytes = stages * stage_bytes + kCtrlBytes + 1024;
-  out->kernel = tc_kernel_select(cg, planes, tf32, pr.rank5);
+  out->kernel = pr.generic ? tc_kernel_generic() : tc_kernel_select(cg, planes, tf32, pr.rank5);
+  if (pr.generic) {
+    p.ga = pr.A.ptr; p.gb = pr.B.ptr;
+    p.g_lda = pr.A.mn_major ? pr.A.k_str[0] : pr.A.mn_str[0];
+    p.g_ldb = pr.B.mn_major ? pr.B.k_str[0] : pr.B.mn_str[0];
+    p.g_a_batch = pr.batch_a; p.g_b_batch = pr.batch_b;
+  }
 
   // persistent grid
   const int64_t tiles64 = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.k_split * p.batch;
@@ -537,7 +565,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   int slots;
   {
     std::lock_guard<std::mutex> lock(h->mu);
-    bool& set = h->attr_set[cg - 1][planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
+    bool& set = pr.generic ? h->attr_set_generic : h->attr_set[cg - 1][planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
     if (!set) {
       GK_CUDA_CHECK(cudaFuncSetAttribute(out->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
       set = true;
@@ -566,7 +594,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   if (pr.max_ctas > 0) slots = std::max(1, std::min(slots, pr.max_ctas / cg));
   out->grid = cg * std::min(tiles, slots);
 
-  if (encode) {
+  if (encode && !pr.generic) {
     gk_status s;
     if (pr.rank5) {
       s = encode_modes(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, a_row_mode, a_rows, a_tma);

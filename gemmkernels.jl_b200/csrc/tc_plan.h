@@ -24,6 +24,7 @@ struct TcProblem {
   int32_t number = GK_REAL;
   TcOperand A, B;
   bool rank5 = false;            // operands need the two-mode split (5-D tensor maps)
+  bool generic = false;          // operands are not TMA-addressable (alignment): producers use bounds-checked loads
   // output / C: two-mode split of M and N with strides per mode
   const void* C = nullptr;
   void* D = nullptr;
@@ -53,13 +54,16 @@ struct TcLaunch {
   TcParams params;
   const void* kernel = nullptr;
   int cg = 1, planes = 1;
-  bool tf32 = false, rank5 = false;
+  bool tf32 = false, rank5 = false, generic = false;
   int grid = 0;
   int smem_bytes = 0;
 };
 
 // True when the descriptor (and, if given, the operand addresses) can go through TMA + tcgen05.
 bool tc_eligible(const gk_gemm_desc& d, const void* a, const void* b, std::string* why);
+// True when the only obstacle to tc_eligible is TMA's alignment rule (base address, leading dimension,
+// batch stride) and the product is one the generic-load form of the kernel takes: real, 16-bit operands.
+bool tc_eligible_generic(const gk_gemm_desc& d, std::string* why);
 // gk_gemm_desc -> TcProblem (plain matrices).
 void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a, const void* b,
                           const void* c, void* dd, TcProblem* out);

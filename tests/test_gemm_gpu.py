@@ -181,13 +181,56 @@ def test_blas_matmatmul(ab, cd, wmma, min_dim, ta, tb):
         B = (rng.random((N, K) if tb == "T" else (K, N)) / math.sqrt(K)).astype(AB.np_dtype)
         Cm = rng.random((M, N)).astype(CD.np_dtype)
         c = dev(Cm)
-        out = GK.matmatmul_(c, ta, tb, dev(A), dev(B), alpha, beta, wmma=wmma)
+        a_d, b_d = dev(A), dev(B)
+        out = GK.matmatmul_(c, ta, tb, a_d, b_d, alpha, beta, wmma=wmma)
         torch.cuda.synchronize(); GK.poll_status()
         assert out is c
+        if wmma:      # every wmma = true case of test/blas.jl runs on the tensor cores, whatever its alignment
+            ld = GK.arrays.leading_dimension
+            conf, _, kern = GK.create_config(AB, tuple(a_d.shape), (1, ld(a_d)), ta == "T", AB, tuple(b_d.shape), (1, ld(b_d)),
+                                             tb == "T", CD, (M, N), (1, ld(c)), alpha == 0, beta == 0, wmma)
+            assert GK.query(conf, a_d, b_d, c, c, kernel=kern).kernel == 1, (M, N, K)
         want = O.gemm(A, B, Cm, alpha, beta, ta == "T", tb == "T")
         got = GK.to_numpy(c)
         assert O.isapprox_normwise(want, got, cd if cd == "Float16" else ab), (M, N, K, O.normwise_error(got, want))
         assert O.normwise_error(got, want) <= (TOL_FPU if ab == "Float32" else (2e-3 if cd == "Float16" else TOL_TENSOR))
+
+
+@pytest.mark.parametrize("ab", ["Float16", "BFloat16"])
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_unaligned_operands_stay_on_the_tensor_cores(ab, ta, tb):
+    """Leading dimensions and base addresses that are not multiples of 16 bytes (the reference's
+    bounds-checked ColMajor / RowMajor layouts, src/layout.jl:111-184, which its WMMA operator runs on
+    the sizes of test/blas.jl:19-21): the tcgen05 kernel runs them with ordinary loads in its producer
+    warps instead of TMA.  The plan must say tensor cores; small-integer inputs make the result exact."""
+    ET = getattr(GK, ab)
+    rng = np.random.default_rng(100 + 2 * ta + tb)
+    for (M, N, K) in [(10, 10, 10), (10, 128, 1000), (1000, 10, 128), (130, 70, 10), (333, 257, 75), (129, 1, 2050)]:
+        A = rng.integers(-2, 3, (K, M) if ta else (M, K)).astype(np.float32)
+        B = rng.integers(-2, 3, (N, K) if tb else (K, N)).astype(np.float32)
+        Cm = rng.integers(-4, 5, (M, N)).astype(np.float32)
+
+        def odd_storage(x):
+            # column-major with a leading dimension of rows + 3 elements, starting one element into the buffer
+            r, c = x.shape
+            store = torch.zeros(c * (r + 3) + 1, dtype=ET.torch_dtype(), device="cuda")
+            view = store[1:].view(c, r + 3)[:, :r].t()
+            view.copy_(torch.from_numpy(x).to(ET.torch_dtype()))
+            return view
+        a, b = odd_storage(A), odd_storage(B)
+        assert a.data_ptr() % 16 != 0
+        c = dev(Cm)
+        conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.TCGen05Operator[ET, GK.Float32],
+                             global_a_layout=(Layout.RowMajor if ta else Layout.ColMajor)[ET],
+                             global_b_layout=(Layout.RowMajor if tb else Layout.ColMajor)[ET],
+                             global_c_layout=Layout.ColMajor[GK.Float32], global_d_layout=Layout.ColMajor[GK.Float32],
+                             is_a_col_major=not ta, is_b_col_major=not tb)
+        plan = GK.query(conf, a, b, c, c)
+        assert plan.kernel == 1 and plan.cluster == 1, (M, N, K, plan.kernel)
+        GK.matmul(conf, a, b, c, c, transform_shared_to_regs_a=Transform.Elementwise(Transform.Scale(2.0)))
+        torch.cuda.synchronize(); GK.poll_status()
+        want = O.gemm(A, B, Cm, 2.0, 1.0, bool(ta), bool(tb))
+        assert np.array_equal(GK.to_numpy(c), want), (M, N, K)
 
 
 def test_mul_with_transposed_views():
