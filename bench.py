@@ -462,7 +462,10 @@ def run_gpu(args):
         line["vs_cublas_same_run"] = cublas_ms / ms_per_step
         line["cublas_out_dtype"] = cublas_out
     if world > 1:
-        tiles = (m_dim // 256) * (-(-n_loc // 512))
+        tm_, tn_ = int(plan.tile_m), int(plan.tile_n)
+        tiles = (-(-m_dim // tm_)) * (-(-n_loc // tn_))
+        slots = max(1, int(plan.grid) // int(plan.cluster))
+        rounds = -(-tiles // slots)
         line["a_broadcast_ms"] = bcast_ms
         line["one_shot_broadcast_overlapped_ms"] = one_shot_ms
         line["e2e"]["phases_ms_rank0"] = phases
@@ -470,9 +473,10 @@ def run_gpu(args):
         line["e2e"]["a_chunks"] = chunks
         line["e2e"]["h2d_gbs_per_rank"] = h2d / (phases["upload_ms"] * 1e-3) / 1e9 if phases["upload_ms"] > 0 else None
         line["e2e"]["d2h_gbs_per_rank"] = d2h / (phases["download_ms"] * 1e-3) / 1e9 if phases["download_ms"] > 0 else None
-        line["limiter"] = (f"each rank's block is {tiles} tiles of 256x512 on {int(plan.grid) // 2} CTA pairs: "
-                           f"{tiles / (-(-tiles // 74) * 74):.0%} of the slots of its last round are filled, and the single "
-                           "accumulator stage leaves each tile's epilogue exposed")
+        line["limiter"] = (f"each rank's block is {tiles} tiles of {tm_}x{tn_} on {slots} CTA slots = {rounds} round(s) "
+                           f"{tiles / (rounds * slots):.0%} full (one GPU alone: "
+                           f"{(N_DIM // 256) * (N_DIM // 512)} tiles of 256x512 on 74 slots, 99% full)"
+                           + ("; the single accumulator stage of the 512-wide tile leaves each tile's epilogue exposed" if tn_ == 512 else ""))
     if c5 is not None:
         line["c5"] = c5
     if world == 1 and not args.no_cpu_baseline:

@@ -223,6 +223,7 @@ static gk_status launch_diag(gk_handle h, const gk_gemm_desc& d, const gk_epilog
 static int choose_family(const gk_gemm_desc& d, const void* a, const void* b, std::string* why, bool* generic_loads = nullptr) {
   if (generic_loads) *generic_loads = false;
   if (d.layout_a == GK_LAYOUT_DIAGONAL) return 4;
+  if (d.m == 0 || d.n == 0) return 3;          // nothing to write: no launch follows
   // Nothing to multiply (Layout.Zero operands, alpha == 0, K == 0): D = act(beta * C + bias),
   // which the generic kernel does without touching A or B.
   const bool no_product = d.layout_a == GK_LAYOUT_ZERO || d.layout_b == GK_LAYOUT_ZERO ||
