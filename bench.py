@@ -420,6 +420,9 @@ def run_gpu(args):
     if world > 1:
         phases = {k: acc[k] / e2e_steps for k in ("upload_ms", "collective_ms", "compute_ms", "download_ms", "total_ms")}
         phases_max = {k: max_over_ranks(v) for k, v in phases.items()}
+        tot = torch.tensor([acc["h2d_bytes"] / e2e_steps, acc["d2h_bytes"] / e2e_steps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tot)
+        all_h2d, all_d2h = float(tot[0].item()), float(tot[1].item())
         h2d = int(acc["h2d_bytes"] / e2e_steps); d2h = int(acc["d2h_bytes"] / e2e_steps)
         chunks = int(acc["chunks"] / e2e_steps)
     else:
@@ -464,7 +467,7 @@ def run_gpu(args):
     if world > 1:
         tm_, tn_ = int(plan.tile_m), int(plan.tile_n)
         tiles = (-(-m_dim // tm_)) * (-(-n_loc // tn_))
-        slots = max(1, int(plan.grid) // int(plan.cluster))
+        slots = max(1, torch.cuda.get_device_properties(local).multi_processor_count // int(plan.cluster))
         rounds = -(-tiles // slots)
         line["a_broadcast_ms"] = bcast_ms
         line["one_shot_broadcast_overlapped_ms"] = one_shot_ms
@@ -473,6 +476,12 @@ def run_gpu(args):
         line["e2e"]["a_chunks"] = chunks
         line["e2e"]["h2d_gbs_per_rank"] = h2d / (phases["upload_ms"] * 1e-3) / 1e9 if phases["upload_ms"] > 0 else None
         line["e2e"]["d2h_gbs_per_rank"] = d2h / (phases["download_ms"] * 1e-3) / 1e9 if phases["download_ms"] > 0 else None
+        line["e2e"]["all_ranks_h2d_bytes_per_step"] = all_h2d
+        line["e2e"]["all_ranks_d2h_bytes_per_step"] = all_d2h
+        line["e2e"]["host_link_gbs_all_ranks"] = (all_h2d + all_d2h) / (e2e_ms * 1e-3) / 1e9
+        line["e2e"]["limiter"] = ("the host: A and B go up once (1/N of A per rank) and D comes down once whatever N is, and the "
+                                  "ranks' copies share the host's memory and PCIe root ports; host_link_gbs_all_ranks is what "
+                                  "they sustained together (one GPU alone: ~72 GB/s over both directions)")
         line["limiter"] = (f"each rank's block is {tiles} tiles of {tm_}x{tn_} on {slots} CTA slots = {rounds} round(s) "
                            f"{tiles / (rounds * slots):.0%} full (one GPU alone: "
                            f"{(N_DIM // 256) * (N_DIM // 512)} tiles of 256x512 on 74 slots, 99% full)"
