@@ -566,17 +566,30 @@ def run_side(args):
         check = lambda: (d[3], torch.einsum("ebf,dfce->bcd", a[3].float(), b.float()))
         flops, name = 2.0 * e ** 6, "c4: C[a,b,c,d] = sum_ef A[a,e,b,f] B[d,f,c,e], extents 32 (M=N=K=1024), tcgen05 via 5-D TMA"
         plan = GK.contract_query(d, "abcd", a, "aebf", b, "dfce")
+    elif w == "c5":
+        n = 16384
+        a, b, d = rnd(GK.BFloat16, n, n, lo=-0.03, hi=0.03), rnd(GK.BFloat16, n, n, lo=-0.03, hi=0.03), GK.cuarray(GK.Float32, n, n)
+        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.TCGen05Operator[GK.BFloat16, GK.Float32],
+                             global_a_layout=Lay.UnsafeAlignedColMajor[GK.BFloat16], global_c_layout=Lay.Zero[GK.Float32],
+                             global_d_layout=Lay.UnsafeAlignedColMajor[GK.Float32])
+        step = GK.bind(conf, a, b, None, d)
+        check = lambda: (d[5:9], a[5:9].float() @ b.float())
+        flops, name = 2.0 * n ** 3, "c5 on one GPU: 16384^3 BFloat16 -> Float32, col-major, tcgen05"
+        plan = GK.query(conf, a, b, None, d)
     else:
-        n = 4096
-        v, b, c, d = rnd(GK.Float16, n), rnd(GK.Float16, n, n), rnd(GK.Float32, n, n), GK.cuarray(GK.Float32, n, n)
-        conf = GK.get_config(gemm_shape=(n, n, n), operator=Op.TCGen05Operator[GK.Float16, GK.Float32],
+        # diag: 4096^2 (the reference's benchmark size; 160 MiB working set, partly L2-resident);
+        # diag-large: 16384 x 8192 columns (1.25 GiB streamed: 10x L2, a clean HBM figure)
+        n = 4096 if w == "diag" else 16384
+        cols = n if w == "diag" else 8192
+        v, b, c, d = rnd(GK.Float16, n), rnd(GK.Float16, n, cols), rnd(GK.Float32, n, cols), GK.cuarray(GK.Float32, n, cols)
+        conf = GK.get_config(gemm_shape=(n, cols, n), operator=Op.TCGen05Operator[GK.Float16, GK.Float32],
                              global_a_layout=Lay.Diagonal[GK.Float16], global_b_layout=Lay.UnsafeAlignedColMajor[GK.Float16],
                              global_c_layout=Lay.UnsafeAlignedColMajor[GK.Float32], block_shape=(128, 128, 64),
                              shared_a_layout=Lay.Padded[Lay.UnsafeAlignedColMajor[GK.Float16], 8])
         step = GK.bind(conf, v, b, c, d)
         check = lambda: (d[5:9], v[5:9, None].float() * b[5:9].float() + c[5:9])
         # streams B (2 B), C (4 B) in and D (4 B) out per element
-        flops, name, bound, unit = 10.0 * n * n, "diag: D = diag(v) B + C, 4096^2, Float16 B, Float32 C/D (10 B per element)", "hbm", "GB/s"
+        flops, name, bound, unit = 10.0 * n * cols, f"{w}: D = diag(v) B + C, {n}x{cols}, Float16 B, Float32 C/D (10 B per element)", "hbm", "GB/s"
         plan = GK.query(conf, v, b, c, d)
 
     for _ in range(max(args.warmup, 3)):
@@ -620,11 +633,13 @@ def run_side(args):
     print(json.dumps({
         "metric": f"{unit} ({name})", "value": achieved, "unit": unit, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": {"c2": "f32", "diag": "f32"}.get(w, "f16"), "data": "synthetic",
+        "dtype": {"c2": "f32", "diag": "f32", "diag-large": "f32", "c5": "bf16"}.get(w, "f16"), "data": "synthetic",
         "config": {"workload": name, "l2": "back-to-back launches on resident operands; kernel-only, no end-to-end leg"},
         "clocks": clocks, "gpu_launches": args.steps, "sample_normwise_error": err,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": None, "peak_source": src},
+        "us_per_launch": ms * 1e3,
+        **({"hbm_gbs_of_algorithmic_bytes": (3 * 4096 * 4096 * 4 + 4096 * 4) / (ms * 1e-3) / 1e9} if w == "c2" else {}),
         "kernel": {"family": int(plan.kernel), "grid": int(plan.grid), "cluster": int(plan.cluster),
                    "tile": [int(plan.tile_m), int(plan.tile_n), int(plan.tile_k)], "stages": int(plan.stages),
                    "smem_bytes": int(plan.smem_bytes), "tmem_columns": int(plan.tmem_columns)},
@@ -640,14 +655,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c5", action="store_true", help="skip the 16384^3 BFloat16 sub-record")
-    ap.add_argument("--workload", default="c0", choices=["c0", "c1", "c2", "c3", "c4", "diag"],
+    ap.add_argument("--workload", default="c0", choices=["c0", "c1", "c2", "c3", "c4", "c5", "diag", "diag-large"],
                     help="c0: the headline 8192^3 FP16 GEMM, split by column blocks over the ranks, with the 16384^3 "
                          "BF16 configuration as a sub-record of the same line; c1-c4, diag: the other "
-                         "configurations, kernel-only on one GPU")
+                         "configurations (c5: on one GPU; diag-large: 16384 x 8192, ten times L2), kernel-only on one GPU")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    if args.workload in ("c1", "c2", "c3", "c4", "diag"):
+    if args.workload != "c0":
         return run_side(args)
     return run_gpu(args)
 

@@ -483,6 +483,14 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         const int m_cta = (tm * CG + static_cast<int>(rank)) * kTcTileM;
         const int n_cta = tn * bn_tile + static_cast<int>(rank) * bn_cta;
         const int mn = (is_a ? m_cta : n_cta) + mn_add;
+        // RANK5: the two-mode split of the M/N coordinate is fixed for the tile, and that of the K
+        // coordinate advances by one k-block per step: no division inside the k loop.
+        [[maybe_unused]] int mn_in = 0, mn_out = 0, k_in = 0, k_out = 0;
+        if constexpr (RANK5) {
+          mn_in = mn % mn_div; mn_out = mn / mn_div;
+          const int kk0 = kb0 * p.bk + k_add;
+          k_in = kk0 % k_div; k_out = kk0 / k_div;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (prof) pt0 = clock64();
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
@@ -505,8 +513,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
               const uint32_t dst = smem_base + s * stage_bytes + dst_off;
               if constexpr (RANK5) {
                 // coordinates of (mn_in, mn_out, k_in, k_out), placed where the tensor map lists them
-                const int kk = k0 + k_add;
-                const int v[4] = {mn % mn_div, mn / mn_div, kk % k_div, kk / k_div};
+                const int v[4] = {mn_in, mn_out, k_in, k_out};
                 int c[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -525,6 +532,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             }
           }
           if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 2);   // first copies issued
+          if constexpr (RANK5) {
+            k_in += p.bk;
+            while (k_in >= k_div) { k_in -= k_div; ++k_out; }
+          }
           ++issued;
           if (++s == p.stages) { s = 0; ph ^= 1u; }
           if (prof) pi += clock64() - pt1;

@@ -119,10 +119,11 @@ static bool plan_modes(const TcOperand& op, int order[4], int32_t* perm) {
   return true;
 }
 
-// Each box is `box_contig` elements of the contiguous mode by `box_rows` of ONE other mode
-// (`row_mode`, numbered as above); every other mode has box 1.
+// Each box is `box_contig` elements of the contiguous mode by `box_rows` of one other mode
+// (`row_mode`, numbered as above) and, when the outer mode of the same index follows it in memory
+// (`row_mode2`, `box_rows2` > 1), by that many steps of the outer mode too; every other mode has box 1.
 static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, int box_contig,
-                              int row_mode, int box_rows, CUtensorMapSwizzle swizzle) {
+                              int row_mode, int box_rows, int row_mode2, int box_rows2, CUtensorMapSwizzle swizzle) {
   const int es = dtype_size(op.dtype);
   CUtensorMapDataType tdt = op.dtype == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                             : op.dtype == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -142,7 +143,9 @@ static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op,
     const cuuint64_t sbytes = (ext[m] > 1 || i == 0) ? static_cast<cuuint64_t>(str[m]) * es : covered;
     if (i > 0) strides[i - 1] = sbytes;
     covered = std::max<cuuint64_t>(covered, sbytes * dims[i]);
-    box[i] = i == 0 ? static_cast<cuuint32_t>(box_contig) : (m == row_mode ? static_cast<cuuint32_t>(box_rows) : 1u);
+    box[i] = i == 0 ? static_cast<cuuint32_t>(box_contig)
+                    : (m == row_mode ? static_cast<cuuint32_t>(box_rows)
+                                     : (m == row_mode2 && box_rows2 > 1 ? static_cast<cuuint32_t>(box_rows2) : 1u));
   }
   dims[4] = static_cast<cuuint64_t>(planes);
   strides[3] = planes > 1 ? static_cast<cuuint64_t>(op.plane_stride) * es : covered;
@@ -420,11 +423,11 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   // Two-mode operands: a box covers one swizzle span of the contiguous mode and rows of ONE other
   // mode; what a k-block (MN-major) or the tile's rows (K-major) need beyond that comes from
   // `sub` boxes stepping through the outer mode.
-  int a_row_mode = 0, a_rows = 0, b_row_mode = 0, b_rows = 0;
+  int a_row_mode = 0, a_rows = 0, b_row_mode = 0, b_rows = 0, a_rows2 = 1, b_rows2 = 1;
   p.a_sub = p.b_sub = 1;
   if (pr.rank5) {
     auto plan_sub = [&](const TcOperand& op, bool mn_major, int tile_rows, uint32_t row_bytes, int32_t* sub,
-                        int32_t* step, int32_t* sub_bytes, int* row_mode, int* rows) -> bool {
+                        int32_t* step, int32_t* sub_bytes, int* row_mode, int* rows, int* rows2) -> bool {
       const int need = mn_major ? p.bk : tile_rows;       // rows of one chunk
       const int64_t* e = mn_major ? op.k_ext : op.mn_ext;
       *row_mode = mn_major ? 2 : 0;
@@ -433,6 +436,12 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
       else return false;
       *step = *rows;
       *sub_bytes = static_cast<int32_t>(*rows * row_bytes);
+      // The sub-boxes step through the outer mode of the same index.  When that mode also lies further
+      // out in memory, TMA writes a box that spans both modes in exactly the order the sub-boxes would
+      // have been placed in: one copy instead of `sub`.
+      const int64_t* st = mn_major ? op.k_str : op.mn_str;
+      *rows2 = 1;
+      if (*sub > 1 && *sub <= 256 && st[0] < st[1]) { *rows2 = *sub; *sub = 1; }
       // K-major operands need whole 128-byte runs of their inner contracted mode
       if (!mn_major && op.k_ext[1] > 1 && op.k_ext[0] % p.bk != 0) return false;
       // MN-major operands: the chunk must be cut from the inner mode
@@ -443,8 +452,8 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
     const uint32_t b_row_bytes = p.b_mn_major ? static_cast<uint32_t>(p.b_box_bytes / p.bk) : kTcKBytes;
     int order[4];
     const bool ok =
-        plan_sub(pr.A, p.a_mn_major != 0, kTcTileM, a_row_bytes, &p.a_sub, &p.a_sub_step, &p.a_sub_bytes, &a_row_mode, &a_rows) &&
-        plan_sub(pr.B, p.b_mn_major != 0, bn_cta, b_row_bytes, &p.b_sub, &p.b_sub_step, &p.b_sub_bytes, &b_row_mode, &b_rows) &&
+        plan_sub(pr.A, p.a_mn_major != 0, kTcTileM, a_row_bytes, &p.a_sub, &p.a_sub_step, &p.a_sub_bytes, &a_row_mode, &a_rows, &a_rows2) &&
+        plan_sub(pr.B, p.b_mn_major != 0, bn_cta, b_row_bytes, &p.b_sub, &p.b_sub_step, &p.b_sub_bytes, &b_row_mode, &b_rows, &b_rows2) &&
         plan_modes(pr.A, order, &p.a_perm) && plan_modes(pr.B, order, &p.b_perm) &&
         planes * p.a_boxes * p.a_sub <= 32 && planes * p.b_boxes * p.b_sub <= 32;
     if (!ok)
@@ -597,9 +606,9 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   if (encode && !pr.generic) {
     gk_status s;
     if (pr.rank5) {
-      s = encode_modes(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, a_row_mode, a_rows, a_tma);
+      s = encode_modes(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, a_row_mode, a_rows, a_row_mode + 1, a_rows2, a_tma);
       if (s != GK_OK) return s;
-      s = encode_modes(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, b_row_mode, b_rows, b_tma);
+      s = encode_modes(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, b_row_mode, b_rows, b_row_mode + 1, b_rows2, b_tma);
     } else {
       s = encode_plain(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, p.a_mn_major ? p.bk : kTcTileM, a_tma,
                        pr.batch, pr.batch_a);

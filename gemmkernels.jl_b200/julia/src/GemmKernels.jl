@@ -1,6 +1,6 @@
 # GemmKernels with the Blackwell engine underneath: same module and export names as the reference's
-# src/GemmKernels.jl; device code replaced by libgemmkernels_b200 (see INTEGRATION.md at the repository
-# root).  Not executed in this repository's environment (no Julia).
+# src/GemmKernels.jl; device code replaced by libgemmkernels_b200 (C ABI: include/gemmkernels_b200.h).
+# Not executed in this repository's environment (no Julia).
 module GemmKernels
 
 include("vocabulary.jl")

@@ -87,7 +87,7 @@ struct GkContractDesc
     dtype_a::Int32; dtype_b::Int32; dtype_c::Int32; dtype_d::Int32
     compute::Int32; force_gather::Int32
     alpha::Float64; beta::Float64
-    tile_n::Int32; cta_group::Int32; stages::Int32; reserved::NTuple{3, Int32}
+    tile_n::Int32; cta_group::Int32; stages::Int32; debug::Int32; reserved::NTuple{2, Int32}
 end
 
 pad8(xs, T) = ntuple(i -> i <= length(xs) ? T(xs[i]) : zero(T), 8)
@@ -99,11 +99,11 @@ function contract!(D::CuArray, modes_d::AbstractString, A::CuArray, modes_a::Abs
                           pad8(size(A), Int64), pad8(size(B), Int64), pad8(size(D), Int64),
                           pad8(strides(A), Int64), pad8(strides(B), Int64), pad8(strides(C), Int64), pad8(strides(D), Int64),
                           gk_dtype(eltype(A)), gk_dtype(eltype(B)), gk_dtype(eltype(C)), gk_dtype(eltype(D)),
-                          gk_dtype(eltype(A) === Float32 ? Float32 : eltype(A)), 0, alpha, beta, 0, 0, 0, (0, 0, 0))
+                          gk_dtype(eltype(A) === Float32 ? Float32 : eltype(A)), 0, alpha, beta, 0, 0, 0, 0, (0, 0))
     if workspace === nothing
         plan = Ref{GkGemmPlan}()
         gk_check(ccall((:gk_contract_query, libgk), Cint, (Ptr{Cvoid}, Ref{GkContractDesc}, Ref{GkGemmPlan}), gk_handle(), desc, plan))
-        plan[].workspace_bytes > 0 && (workspace = CuArray{UInt8}(undef, plan[].workspace_bytes))
+        plan[].workspace_bytes > 0 && (workspace = lent_workspace(plan[].workspace_bytes))
     end
     ws = workspace === nothing ? CU_NULL : reinterpret(CuPtr{Cvoid}, pointer(workspace))
     gk_check(ccall((:gk_contract, libgk), Cint,
@@ -111,4 +111,26 @@ function contract!(D::CuArray, modes_d::AbstractString, A::CuArray, modes_a::Abs
                    gk_handle(), desc, pointer(A), pointer(B), pointer(C), pointer(D), ws,
                    workspace === nothing ? 0 : sizeof(workspace), CUDA.stream().handle))
     D
+end
+
+
+# ---- column-sharded GEMM over the GPUs of one box: one Julia process (or task) per GPU ---------------------
+# The 128-byte id made on one rank reaches the others by any transport (Distributed.jl, MPI.jl, a file).
+mgpu_unique_id() = (id = Vector{UInt8}(undef, 128); gk_check(ccall((:gk_mgpu_unique_id, libgk), Cint, (Ptr{UInt8},), id)); id)
+mgpu_init(rank::Integer, world::Integer, id::Vector{UInt8}) =
+    gk_check(ccall((:gk_mgpu_init, libgk), Cint, (Ptr{Cvoid}, Int32, Int32, Ptr{UInt8}), gk_handle(), rank, world, id))
+mgpu_destroy() = gk_check(ccall((:gk_mgpu_destroy, libgk), Cint, (Ptr{Cvoid},), gk_handle()))
+
+"""
+    matmul_colshard(conf, a, b_block, c_block, d_block; a_mode = :resident, root = 0, k_panels = 0, ...)
+
+This rank's column block of D = A * B (`conf` describes the block).  `a_mode = :broadcast` sends A from
+rank `root` into every rank's `a` in panels that overlap the product (collective).
+"""
+function matmul_colshard(desc::GkGemmDesc, epi::GkEpilogueDesc, a, b, c, d; a_mode = :resident, root = 0, k_panels = 0)
+    gk_check(ccall((:gk_mgpu_gemm_colshard, libgk), Cint,
+                   (Ptr{Cvoid}, Ref{GkGemmDesc}, CuPtr{Cvoid}, Int32, Int32, Int32, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid},
+                    Ref{GkEpilogueDesc}, CuPtr{Cvoid}, Int64, Ptr{Cvoid}),
+                   gk_handle(), desc, pointer(a), a_mode === :broadcast ? 1 : 0, root, k_panels, pointer(b),
+                   c === nothing ? CU_NULL : pointer(c), pointer(d), epi, CU_NULL, 0, CUDA.stream().handle))
 end

@@ -19,7 +19,9 @@ struct GkGemmDesc
     layout_a::Int32; layout_b::Int32; layout_c::Int32; raster::Int32
     alpha::Float64; beta::Float64
     tile_n::Int32; cta_group::Int32; stages::Int32; raster_group::Int32; max_ctas::Int32
-    reserved::NTuple{3, Int32}
+    debug::Int32; host_chunk_mib::Int32; a_resident::Int32
+    batch::Int32                                     # (4 bytes of padding follow, as in C)
+    batch_stride_a::Int64; batch_stride_b::Int64; batch_stride_c::Int64; batch_stride_d::Int64
 end
 struct GkEpilogueDesc
     struct_size::UInt32; bias_axis::Int32
@@ -137,7 +139,8 @@ function matmul(conf::Config, a, b, c, d;
                       compute, op, ld(a, la), ld(b, lb), ld(c, lc), ld(d, ldl),
                       plane(a, la), plane(b, lb), plane(c, lc), plane(d, ldl),
                       layout_kind(la), layout_kind(lb), layout_kind(lc), rk, alpha, beta,
-                      conf.tile_n, conf.cta_group, conf.stages, rg == 0 ? conf.raster_group : rg, 0, (0, 0, 0))
+                      conf.tile_n, conf.cta_group, conf.stages, rg == 0 ? conf.raster_group : rg, 0,
+                      0, 0, 0, 0, 0, 0, 0, 0)
     epi = GkEpilogueDesc(sizeof(GkEpilogueDesc), has_bias ? (epilogue.axis === :row ? 1 : 2) : 0,
                          has_bias ? reinterpret(CuPtr{Float32}, epilogue.bias_pointer) : CuPtr{Float32}(0), act, (0, 0, 0))
     # Interleaved complex / dual operands need a workspace (they are split into planes first); real products
@@ -148,13 +151,28 @@ function matmul(conf::Config, a, b, c, d;
         plan = Ref(GkGemmPlan(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0))
         gk_check(ccall((:gk_gemm_query, libgk), Cint, (Ptr{Cvoid}, Ref{GkGemmDesc}, Ref{GkEpilogueDesc}, Ref{GkGemmPlan}),
                        gk_handle(), desc, epi, plan))
-        plan[].workspace_bytes > 0 && (workspace = CuArray{UInt8}(undef, plan[].workspace_bytes))
+        plan[].workspace_bytes > 0 && (workspace = lent_workspace(plan[].workspace_bytes))
     end
     ws = workspace === nothing ? CU_NULL : reinterpret(CuPtr{Cvoid}, pointer(workspace))
     gk_check(ccall((:gk_gemm, libgk), Cint,
                    (Ptr{Cvoid}, Ref{GkGemmDesc}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid}, CuPtr{Cvoid},
-                    Ref{GkEpilogueDesc}, CuPtr{Cvoid}, Ptr{Cvoid}),
+                    Ref{GkEpilogueDesc}, CuPtr{Cvoid}, Int64, Ptr{Cvoid}),
                    gk_handle(), desc, devptr(a, la), devptr(b, lb), devptr(c, lc), devptr(d, ldl), epi, ws,
-                   CUDA.stream().handle))
+                   workspace === nothing ? 0 : sizeof(workspace), CUDA.stream().handle))
     return
+end
+
+# Scratch the package lends to the library when the caller passes none: one buffer per (device, stream),
+# allocated on first need and replaced only by a larger one, so the hot path does not allocate.
+const gk_workspaces = Dict{Tuple{CuDevice, CuStream}, CuVector{UInt8}}()
+function lent_workspace(bytes::Integer)
+    lock(gk_handles_lock) do
+        key = (device(), CUDA.stream())
+        ws = get(gk_workspaces, key, nothing)
+        if ws === nothing || length(ws) < bytes
+            ws = CuVector{UInt8}(undef, max(bytes, ws === nothing ? 0 : 2 * length(ws)))
+            gk_workspaces[key] = ws
+        end
+        ws
+    end
 end

@@ -1,7 +1,7 @@
 /*
  * Plain C restatement of the reference's definition of the GEMM math — TEST INFRASTRUCTURE ONLY
- * (used by tests/ to cross-check the numpy oracle, and by bench.py as a scalar CPU baseline;
- * never linked into or called from the product library).
+ * (used by tests/ to cross-check the numpy oracle; never linked into or called from the product
+ * library).
  *
  * PARITY UNPINNED: GemmKernels.jl ships no golden vectors for this path and cannot run here;
  * this file and gemm_oracle.py pin each other on the fixtures in tests/golden/.
