@@ -668,7 +668,9 @@ static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
     alt.tile_n = pr->number == GK_REAL ? 256 : 128; alt.cta_group = 2;
     TcLaunch La;
     if (tc_plan(h, alt, false, &La) == GK_OK) {
-      const int splits = tc_choose_k_split(alt, La, h->sm_count);
+      // worth it only for a long K (32 k-blocks or more): below that the second pass costs more than the
+      // large tiles save (measured: the 1024^3 contraction took 25 us this way against 13 us unsplit)
+      const int splits = La.params.k_blocks >= 32 ? tc_choose_k_split(alt, La, h->sm_count) : 1;
       if (splits > 1) { pr->tile_n = alt.tile_n; pr->cta_group = 2; return splits; }
     } else {
       clear_error();
