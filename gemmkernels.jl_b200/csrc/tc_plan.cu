@@ -559,6 +559,11 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   out->rank5 = pr.rank5;
   out->generic = pr.generic;
   out->smem_bytes = stages * stage_bytes + kCtrlBytes + 1024;
+  // One CTA of this kernel per SM, whatever the stage count: a CTA allocates up to all 512 TMEM columns
+  // without a bound on that wait, and with dependent launch the next kernel's CTAs arrive while this one's
+  // are still draining.  Asking for more than half of an SM's shared memory makes two tcgen05 CTAs on one
+  // SM impossible, so two CTA pairs can never each hold one SM's tensor memory and wait for the other's.
+  out->smem_bytes = std::max(out->smem_bytes, kSmemBudget / 2 + 2048);
   out->kernel = pr.generic ? tc_kernel_generic() : tc_kernel_select(cg, planes, tf32, pr.rank5);
   if (pr.generic) {
     p.ga = pr.A.ptr; p.gb = pr.B.ptr;

@@ -98,9 +98,13 @@ def fpu_config(A, B, CD, ta, tb, op, block, M, N, K, tropical=False) -> Configur
 
 
 def wmma_config(AB, CD, ta, tb, block, op, M, N, K, zero_c=False, kernel=Kernel.matmul_pipelined, warps=(4, 2)) -> Configuration:
-    """@get_wmma_config (configs.jl:224-266)."""
+    """@get_wmma_config (configs.jl:224-266): block shape, warp grid (warps_per_block = WARPS_M * WARPS_N,
+    compute_warp = block / warps) and operator shape all go to get_config, which raises ConfigError for the
+    combinations its rules exclude."""
     la, lb = _layouts(AB, ta, tb)
     conf = get_config(gemm_shape=(M, N, K), block_shape=block, operator=Operator.WMMAOp[op[0], op[1], op[2], AB, CD],
+                      warps_per_block=warps[0] * warps[1],
+                      compute_warp=(block[0] // warps[0], block[1] // warps[1], op[2]),
                       global_a_layout=la, global_b_layout=lb,
                       global_c_layout=(Layout.Zero if zero_c else Layout.UnsafeAlignedColMajor)[CD],
                       global_d_layout=Layout.UnsafeAlignedColMajor[CD], is_a_col_major=not ta, is_b_col_major=not tb)
@@ -191,8 +195,11 @@ def get_configs(largest: bool = True) -> list:
         for M, N, K in sizes:
             push(wmma_config, AB, CD, ta, tb, (128, 128, 64), op, M, N, K)
     blocks = [b for b in itertools.product([64, 128, 256], [64, 128, 256], [16, 32, 64]) if b[0] * b[1] <= 128 * 128]
-    for ta, tb, block, zero_c, kern in itertools.product(tf, tf, blocks, tf, [Kernel.matmul_singlestage, Kernel.matmul_pipelined]):
-        push(wmma_config, T.Float16, T.Float32, ta, tb, block, (16, 16, 16), 256, 256, 256, zero_c=zero_c, kernel=kern)
+    # the parameter sweep of configs.jl:597-612: block shapes x warp grids x zero_c x kernels at 256^3
+    warp_grids = [w for w in itertools.product([1, 2, 4], [1, 2, 4]) if w[0] * w[1] >= 4]
+    for ta, tb, block, warps, zero_c, kern in itertools.product(tf, tf, blocks, warp_grids, tf,
+                                                                [Kernel.matmul_singlestage, Kernel.matmul_pipelined]):
+        push(wmma_config, T.Float16, T.Float32, ta, tb, block, (16, 16, 16), 256, 256, 256, zero_c=zero_c, kernel=kern, warps=warps)
     for ta, tb, op in itertools.product(tf, tf, WMMA_OPS):
         for M, N, K in [(128, 128, 128), (256, 256, 256)] + ([(4096, 4096, 4096)] if largest else []):
             push(wmma_bias_config, T.Float16, T.Float32, ta, tb, op, M, N, K)

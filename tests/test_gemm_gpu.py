@@ -949,6 +949,41 @@ def test_zoo_wmma(cd, min_dim, ta, tb, op_shape, zero_c):
 
 
 @pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_zoo_wmma_parameter_sweep(ta, tb):
+    """The parameter sweep of configs/configs.jl:597-612 at 256^3: block shapes with BLOCK_M * BLOCK_N <= 128^2,
+    warp grids with at least four warps, zero_c, both kernels.  A combination the validity rules exclude
+    raises ConfigError and counts as skipped (test/matmul.jl:22-24); every other one must run and match
+    the oracle (alpha = 2, beta = 3, or 0 with Layout.Zero) under the reference's element-wise rule."""
+    import itertools
+    M = N = K = 256
+    rng = np.random.default_rng(597 + 2 * ta + tb)
+    A = rng.random((K, M) if ta else (M, K)).astype(np.float16); B = rng.random((N, K) if tb else (K, N)).astype(np.float16)
+    Cm = rng.random((M, N)).astype(np.float32)
+    a, b, c = dev(A), dev(B), dev(Cm)
+    want = {False: O.gemm(A, B, Cm, 2.0, 3.0, bool(ta), bool(tb)), True: O.gemm(A, B, None, 2.0, 0.0, bool(ta), bool(tb))}
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float16]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float16]
+    blocks = [blk for blk in itertools.product([64, 128, 256], [64, 128, 256], [16, 32, 64]) if blk[0] * blk[1] <= 128 * 128]
+    grids = [w for w in itertools.product([1, 2, 4], [1, 2, 4]) if w[0] * w[1] >= 4]
+    ran = skipped = 0
+    for blk, (wm, wn), zero_c, kern in itertools.product(blocks, grids, [False, True],
+                                                         [Kernel.matmul_singlestage, Kernel.matmul_pipelined]):
+        d = GK.cuarray(GK.Float32, M, N)
+        try:
+            run_matmul(a, b, None if zero_c else c, d, M=M, N=N, K=K, op=Operator.WMMAOp[16, 16, 16, GK.Float16, GK.Float32],
+                       la=la, lb=lb, lc=(Layout.Zero if zero_c else Layout.UnsafeAlignedColMajor)[GK.Float32],
+                       ld=Layout.UnsafeAlignedColMajor[GK.Float32], alpha=2.0, beta=3.0, block_shape=blk,
+                       warps_per_block=wm * wn, compute_warp=(blk[0] // wm, blk[1] // wn, 16), kernel=kern)
+        except GK.ConfigError:
+            skipped += 1
+            continue
+        ran += 1
+        assert O.isapprox_elementwise(want[zero_c], GK.to_numpy(d), "Float16"), (blk, wm, wn, zero_c, kern)
+    assert ran + skipped == 18 * 6 * 2 * 2
+    assert ran >= 200 and skipped >= 50, (ran, skipped)       # the rules cut a good part of the sweep, and leave most of it
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("n", [128, 256, 4096])
 def test_zoo_bias(ta, tb, n):
     """Bias configurations (configs.jl:615-633): per-column Float32 bias, alpha = beta = 1."""
