@@ -441,7 +441,8 @@ gk_status gk_load_tuning(gk_handle h, const gk_tuning_entry* entries, int32_t co
   for (int i = 0; i < count; ++i) {
     const gk_tuning_entry& e = entries[i];
     const bool tile_ok = e.tile_n == 0 || e.tile_n == 512 || (e.tile_n >= 32 && e.tile_n <= 256 && e.tile_n % 32 == 0);
-    if (!tile_ok || e.cta_group < 0 || e.cta_group > 2 || e.stages < 0 || e.raster_group < 0 || e.m < 1 || e.n < 1 || e.k < 1)
+    if (!tile_ok || e.cta_group < 0 || e.cta_group > 2 || e.stages < 0 || e.raster_group < 0 || e.m < 1 || e.n < 1 || e.k < 1 ||
+        e.k_blocks_per_stage < 0 || e.k_blocks_per_stage > 2)
       return set_error(GK_ERR_INVALID_CONFIG, "tuning entry %d is not usable (tile_n %d, cta_group %d, stages %d)", i, e.tile_n,
                        e.cta_group, e.stages);
   }
@@ -477,7 +478,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     if (s != GK_OK) return s;
     plan->grid = L.grid; plan->block = tc_threads(L.planes); plan->cluster = L.cg;
     plan->smem_bytes = L.smem_bytes; plan->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
-    plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk;
+    plan->tile_m = kTcTileM * L.cg; plan->tile_n = L.params.bn * L.params.n_sub; plan->tile_k = L.params.bk * L.params.kps;
     plan->stages = L.params.stages;
     plan->workspace_bytes = sp.a_bytes + sp.b_bytes;
     if (!(sp.a || sp.b) && desc->batch <= 1) plan->workspace_bytes = tc_split_workspace_bytes(h, pr, L);   // optional: enables split-K

@@ -329,7 +329,7 @@ static gk_status contract_one(gk_handle h, const gk_contract_desc* desc, const G
         std::memset(plan_only, 0, sizeof(*plan_only));
         plan_only->kernel = 1; plan_only->grid = L.grid; plan_only->block = tc_threads(L.planes); plan_only->cluster = L.cg;
         plan_only->smem_bytes = L.smem_bytes; plan_only->tmem_columns = static_cast<int32_t>(L.params.tmem_cols);
-        plan_only->tile_m = kTcTileM * L.cg; plan_only->tile_n = L.params.bn * L.params.n_sub; plan_only->tile_k = L.params.bk;
+        plan_only->tile_m = kTcTileM * L.cg; plan_only->tile_n = L.params.bn * L.params.n_sub; plan_only->tile_k = L.params.bk * L.params.kps;
         plan_only->stages = L.params.stages;
         plan_only->workspace_bytes = tc_split_workspace_bytes(h, pr, L);   // optional: enables split-K
         return GK_OK;

@@ -78,6 +78,8 @@ struct TcParams {
   int32_t n_sub;             // a cluster tile is n_sub (1 or 2) such column blocks that share A
   int32_t acc_stages;        // accumulator stages in TMEM: 2, or 1 when one tile fills all 512 columns
   int32_t bk;                // K elements per k-block (128 bytes)
+  int32_t kps;               // k-blocks per pipeline stage (1 or 2): one full/empty barrier round trip and one
+                             // tcgen05.commit serve kps k-blocks, which halves the fixed cost per k-block
   int32_t stages;
   int32_t a_mn_major, b_mn_major;
   int32_t a_boxes, b_boxes;  // TMA boxes per plane per CTA per k-block
@@ -330,7 +332,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const bool leader = (rank == 0);
 
   const uint32_t b_sub_bytes = p.b_planes * p.b_plane_bytes;   // one column block of B in a stage
-  const uint32_t stage_bytes = p.a_planes * p.a_plane_bytes + p.n_sub * b_sub_bytes;
+  const uint32_t kblock_bytes = p.a_planes * p.a_plane_bytes + p.n_sub * b_sub_bytes;   // operands of one k-block
+  const uint32_t stage_bytes = p.kps * kblock_bytes;                                     // a stage holds kps of them
   const uint32_t ctrl = smem_base + p.stages * stage_bytes;  // control block after the stages
   // control block layout (8-byte slots): full[stages], empty[stages], tmem_full[2], tmem_empty[2],
   // drain, then two 32-bit words: tmem base, abort flag.
@@ -411,20 +414,22 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
         const int mn0 = is_a ? tm * kTcTileM : tn * bn_tile;
         const uint16_t* g = static_cast<const uint16_t*>(is_a ? p.ga : p.gb) + bt * (is_a ? p.g_a_batch : p.g_b_batch);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += p.kps) {
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (!__all_sync(0xffffffffu, got)) {
             if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
             ok = false;
             break;
           }
-          uint8_t* stage = smem_gen + s * stage_bytes + part_off;
-          const int k0 = kb * p.bk;
-          if (mn_major) {
-            for (int bx = 0; bx < boxes; ++bx)
-              tc_fill_box_generic(stage + bx * box_bytes, g, ld, mn0 + bx * box_mn, k0, mn_ext, p.K, p.bk, lane);
-          } else {
-            tc_fill_box_generic(stage, g, ld, k0, mn0, p.K, mn_ext, rows_k_major, lane);
+          for (int j = 0; j < p.kps; ++j) {
+            uint8_t* stage = smem_gen + s * stage_bytes + j * kblock_bytes + part_off;
+            const int k0 = (kb + j) * p.bk;
+            if (mn_major) {
+              for (int bx = 0; bx < boxes; ++bx)
+                tc_fill_box_generic(stage + bx * box_bytes, g, ld, mn0 + bx * box_mn, k0, mn_ext, p.K, p.bk, lane);
+            } else {
+              tc_fill_box_generic(stage, g, ld, k0, mn0, p.K, mn_ext, rows_k_major, lane);
+            }
           }
           fence_proxy_async_smem();   // the tensor cores read shared memory through the asynchronous proxy
           __syncwarp();
@@ -447,18 +452,20 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const int subs = RANK5 ? (is_a ? p.a_sub : p.b_sub) : 1;
       const int per_plane = (is_a ? p.a_boxes : p.b_boxes) * subs;
       const int per_block = (is_a ? p.a_planes : p.b_planes) * per_plane;   // boxes of one column block
-      const int n_boxes = (is_a ? 1 : p.n_sub) * per_block;
-      const bool active = lane < n_boxes;
-      const int nb = active ? lane / per_block : 0;            // which column block (B only)
-      const int pl = active ? (lane % per_block) / per_plane : 0;
-      const int bx = active ? (lane % per_plane) / subs : 0;   // which swizzle-span chunk
-      const int sb = active ? (lane % per_plane) % subs : 0;   // which sub-box of it (RANK5)
+      const int n_boxes = (is_a ? 1 : p.n_sub) * per_block;    // boxes of one k-block
+      const bool active = lane < n_boxes * p.kps;
+      const int kj = active ? lane / n_boxes : 0;              // which k-block of the stage
+      const int bl = active ? lane % n_boxes : 0;              // which box of that k-block
+      const int nb = bl / per_block;                           // which column block (B only)
+      const int pl = (bl % per_block) / per_plane;
+      const int bx = (bl % per_plane) / subs;                  // which swizzle-span chunk
+      const int sb = (bl % per_plane) % subs;                  // which sub-box of it (RANK5)
       const bool mn_major = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
       const int sub_step = RANK5 ? (is_a ? p.a_sub_step : p.b_sub_step) : 0;
       const uint32_t dst_off =
           (is_a ? pl * p.a_plane_bytes + bx * p.a_box_bytes
                 : p.a_planes * p.a_plane_bytes + nb * b_sub_bytes + pl * p.b_plane_bytes + bx * p.b_box_bytes) +
-          (RANK5 ? sb * (is_a ? p.a_sub_bytes : p.b_sub_bytes) : 0);
+          (RANK5 ? sb * (is_a ? p.a_sub_bytes : p.b_sub_bytes) : 0) + kj * kblock_bytes;
       const void* tmap = is_a ? static_cast<const void*>(&p.tm_a) : static_cast<const void*>(&p.tm_b);
       const int mn_add = (mn_major ? bx * (is_a ? p.a_box_mn : p.b_box_mn) : sb * sub_step) + nb * p.bn;
       [[maybe_unused]] const int k_add = mn_major ? sb * sub_step : 0;
@@ -488,10 +495,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         [[maybe_unused]] int mn_in = 0, mn_out = 0, k_in = 0, k_out = 0;
         if constexpr (RANK5) {
           mn_in = mn % mn_div; mn_out = mn / mn_div;
-          const int kk0 = kb0 * p.bk + k_add;
+          const int kk0 = (kb0 + kj) * p.bk + k_add;
           k_in = kk0 % k_div; k_out = kk0 / k_div;
         }
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) pt0 = clock64();
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
@@ -509,7 +516,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             if (lane == 0 && leader && is_a) mbar_arrive_expect_tx(bar_full + 8u * s, tx_bytes);
             __syncwarp();
             if (active) {
-              const int k0 = kb * p.bk;
+              const int k0 = (kb + kj) * p.bk;     // a k-block past the end of K (or of this K-run) is loaded too:
+                                                   // zeros, or operands the MMA issuer does not use
               const uint32_t dst = smem_base + s * stage_bytes + dst_off;
               if constexpr (RANK5) {
                 // coordinates of (mn_in, mn_out, k_in, k_out), placed where the tensor map lists them
@@ -533,7 +541,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
           if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 2);   // first copies issued
           if constexpr (RANK5) {
-            k_in += p.bk;
+            k_in += p.kps * p.bk;
             while (k_in >= k_div) { k_in -= k_div; ++k_out; }
           }
           ++issued;
@@ -587,7 +595,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         t_keep[ti] = tr.first ? 0u : 1u;
       }
       const uint32_t base16 = (smem_base & 0x3FFFFu) >> 4;
-      const uint32_t stage16 = stage_bytes >> 4;
+      const uint32_t stage16 = stage_bytes >> 4, kblock16 = kblock_bytes >> 4;
       const uint32_t a_k16 = p.a_kadv >> 4, b_k16 = p.b_kadv >> 4;
       const uint32_t b_sub16 = b_sub_bytes >> 4;
       const int n_terms = (p.debug & 2) ? 0 : p.n_terms;
@@ -614,7 +622,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         tc_fence_after_sync();
         const uint32_t d_base = tmem_base + as * acc_cols;
         const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) t0 = clock64();
           const bool fgot = mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs);
           if (prof) { t1 = clock64(); mw += t1 - t0; }
@@ -625,23 +633,32 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
           tc_fence_after_sync();
           if (kb == kb0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 1);   // first stage landed
+          for (int kj = 0; kj < p.kps && kb + kj < kb1; ++kj) {   // the k-blocks of this stage that belong to the run
+            const uint32_t k16 = s16 + kj * kblock16;
 #pragma unroll
-          for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
+            for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
 #pragma unroll
-            for (int nb = 0; nb < 2; ++nb) {
-              if (nb < p.n_sub) {
+              for (int nb = 0; nb < 2; ++nb) {
+                if (nb < p.n_sub) {
 #pragma unroll
-                for (int ti = 0; ti < kMaxTerms; ++ti) {
-                  if (ti < n_terms) {
-                    const uint64_t da = smem_desc(s16 + t_a[ti] + ks * a_k16, hi_a);
-                    const uint64_t db = smem_desc(s16 + t_b[ti] + nb * b_sub16 + ks * b_k16, hi_b);
-                    const uint32_t acc = ((kb - kb0) | ks) ? 1u : t_keep[ti];
-                    if (elected) umma<CG, TF32>(d_base + nb * sub_cols + t_d[ti], da, db, t_id[ti], acc);
+                  for (int ti = 0; ti < kMaxTerms; ++ti) {
+                    if (ti < n_terms) {
+                      const uint64_t da = smem_desc(k16 + t_a[ti] + ks * a_k16, hi_a);
+                      const uint64_t db = smem_desc(k16 + t_b[ti] + nb * b_sub16 + ks * b_k16, hi_b);
+                      const uint32_t acc = ((kb + kj - kb0) | ks) ? 1u : t_keep[ti];
+                      if (elected) umma<CG, TF32>(d_base + nb * sub_cols + t_d[ti], da, db, t_id[ti], acc);
+                    }
                   }
                 }
               }
             }
           }
+          if ((p.debug & 66) == 66) {   // measurement aid (only without MMAs): a plain arrival instead of the commit
+            if (elected) {
+              if constexpr (CG == 2) { mbar_arrive_cluster(map_to_cta(bar_empty + 8u * s, 0)); mbar_arrive_cluster(map_to_cta(bar_empty + 8u * s, 1)); }
+              else mbar_arrive(bar_empty + 8u * s);
+            }
+          } else
           if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
           if (kb == kb0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
@@ -727,6 +744,45 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const int m_in = m % p.m_div, m_out = m / p.m_div;
       const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch + split_off;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1 + bt * p.c_batch;
+      if (PLANES == 1 && fast_store && (p.debug & 32)) {
+        // The same stores, software-pipelined over half chunks of 16 columns: the tensor-memory load of
+        // the next half chunk is in flight while this one is written out.
+        const int halves = 2 * ((bn_tile - chunk_first + chunk_step - 1) / chunk_step);
+        auto col_of = [&](int h) { return chunk_first + (h >> 1) * chunk_step + (h & 1) * 16; };
+        auto taddr_of = [&](int c) { return t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c); };
+        auto store_half = [&](const uint32_t (&v)[16], int c) {
+          const int ncols = p.N - (n0 + c);
+          if (!m_ok || ncols <= 0) return;
+          const int n_in = (n0 + c) % p.n_div, n_out = (n0 + c) / p.n_div;
+          float* dp = static_cast<float*>(p.D) + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
+          if (ncols >= 16) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x = fmaf(p.alpha, __uint_as_float(v[j]), bias_row);
+              dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < ncols) {
+                const float x = fmaf(p.alpha, __uint_as_float(v[j]), bias_row);
+                dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
+              }
+            }
+          }
+        };
+        uint32_t va[16], vb[16];
+        tmem_ld_32x16(taddr_of(col_of(0)), va);
+        tmem_ld_wait();
+        for (int h = 0; h < halves; h += 2) {
+          tmem_ld_32x16(taddr_of(col_of(h + 1)), vb);       // halves is even: h + 1 exists
+          store_half(va, col_of(h));
+          tmem_ld_wait();
+          if (h + 2 < halves) tmem_ld_32x16(taddr_of(col_of(h + 2)), va);
+          store_half(vb, col_of(h + 1));
+          tmem_ld_wait();
+        }
+      } else
       for (int c = chunk_first; c < bn_tile; c += chunk_step) {
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)

@@ -243,7 +243,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
 // Tile choices measured on B200 by the tuning sweep (generated file; see tuning.emit_table).
 static const gk_tuning_entry kBuiltinTuning[] = {
 #include "tuned_table.inc"
-    {-1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}   // terminator
+    {-1, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}   // terminator
 };
 
 // Nearest measured entry for this problem (see gk_tuning_entry), or nullptr.
@@ -297,6 +297,7 @@ void tc_problem_from_gemm(const gk_gemm_desc& d, const gk_epilogue_desc* epi, co
   pr.alpha = d.alpha; pr.beta = d.beta; pr.epi = epi;
   pr.tile_n = d.tile_n; pr.cta_group = d.cta_group; pr.stages = d.stages; pr.raster = d.raster;
   pr.raster_group = d.raster_group; pr.max_ctas = d.max_ctas; pr.debug = d.debug;
+  pr.kps = d.k_blocks_per_stage;
   if (d.batch > 1) {
     pr.batch = d.batch;
     pr.batch_a = d.batch_stride_a; pr.batch_b = d.batch_stride_b; pr.batch_c = d.batch_stride_c; pr.batch_d = d.batch_stride_d;
@@ -318,6 +319,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
       pr_tuned.tile_n = e->tile_n; pr_tuned.cta_group = e->cta_group;
       if (pr_tuned.stages == 0) pr_tuned.stages = e->stages;
       if (pr_tuned.raster_group == 0 && pr_tuned.raster == GK_RASTER_AUTO) pr_tuned.raster_group = e->raster_group;
+      if (pr_tuned.kps == 0) pr_tuned.kps = e->k_blocks_per_stage;
       prp = &pr_tuned;
     }
   }
@@ -420,6 +422,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   }
   if (planes * std::max(p.a_boxes, n_sub * p.b_boxes) > 32)
     return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
+  if (pr.kps < 0 || pr.kps > 2) return set_error(GK_ERR_INVALID_CONFIG, "k_blocks_per_stage must be 1 or 2 (0 = choose), got %d", pr.kps);
   // Two-mode operands: a box covers one swizzle span of the contiguous mode and rows of ONE other
   // mode; what a k-block (MN-major) or the tile's rows (K-major) need beyond that comes from
   // `sub` boxes stepping through the outer mode.
@@ -497,11 +500,20 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   p.idesc = idesc;
   p.idesc_neg = idesc | (1u << 13);                   // negate A
 
-  const int stage_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
+  // Two k-blocks per stage halve what every k-block pays in barrier round trips and in tcgen05.commit
+  // (≈250 ns per stage whatever the tile, measured: as long as one k-block of a 256 x 256 tile takes the
+  // tensor cores).  Taken when three such stages still fit and there are k-blocks enough to fill them.
+  const int kblock_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
+  const int boxes_per_kblock = planes * std::max(p.a_boxes * p.a_sub, n_sub * p.b_boxes * p.b_sub);
+  int kps = pr.kps;
+  if (kps == 0) kps = ((kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 && 2 * boxes_per_kblock <= 32) ? 2 : 1;
+  if (kps * boxes_per_kblock > 32) kps = 1;
+  p.kps = kps;
+  const int stage_bytes = kps * kblock_bytes;
   int stages = (kSmemBudget - 1024 - kCtrlBytes) / stage_bytes;
   stages = std::min(stages, 8);
   if (pr.stages) stages = std::min(stages, pr.stages);
-  stages = std::min(stages, std::max(2, p.k_blocks));
+  stages = std::min(stages, std::max(2, (p.k_blocks + kps - 1) / kps));
   if (stages < 2)
     return set_error(GK_ERR_INVALID_CONFIG, "Requested too much shared memory: one pipeline stage needs %d bytes", stage_bytes);
   p.stages = stages;

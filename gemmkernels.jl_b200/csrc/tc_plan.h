@@ -36,6 +36,7 @@ struct TcProblem {
   double alpha = 1.0, beta = 0.0;
   const gk_epilogue_desc* epi = nullptr;
   int32_t tile_n = 0, cta_group = 0, stages = 0, raster = 0, raster_group = 0, max_ctas = 0, debug = 0;
+  int32_t kps = 0;               // k-blocks per pipeline stage (0 = choose)
   // split-K: number of contiguous runs the k-blocks are cut into (0 or 1 = none); with k_split > 1, D must be an
   // FP32 workspace of k_split planes, split_stride elements apart, and C, bias and activation are left out
   int32_t k_split = 0;

@@ -52,7 +52,7 @@ class GemmDesc(C.Structure):
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32),
         ("raster_group", C.c_int32), ("max_ctas", C.c_int32),
         ("debug", C.c_int32), ("host_chunk_mib", C.c_int32), ("a_resident", C.c_int32),
-        ("batch", C.c_int32),
+        ("batch", C.c_int32), ("k_blocks_per_stage", C.c_int32),
         ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_c", C.c_int64),
         ("batch_stride_d", C.c_int64),
     ]
@@ -88,6 +88,7 @@ class TuningEntry(C.Structure):
         ("dtype", C.c_int32), ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("has_c", C.c_int32),
         ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("stages", C.c_int32), ("raster_group", C.c_int32),
+        ("k_blocks_per_stage", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

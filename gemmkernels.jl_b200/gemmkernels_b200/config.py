@@ -63,6 +63,7 @@ class Config:
     cta_group: int = 0
     stages: int = 0
     raster_group: int = 0
+    k_blocks_per_stage: int = 0
     extra: dict = field(default_factory=dict)
 
     def __str__(self):
@@ -243,4 +244,5 @@ def get_config(*, gemm_shape, operator, global_a_layout, global_c_layout, **para
         params.get("cta_swizzle", CTASwizzle.Identity()),
         tile_n=tile_n, cta_group=cta_group, stages=int(params.get("stages", 0)),
         raster_group=int(params.get("raster_group", 0)),
+        k_blocks_per_stage=int(params.get("k_blocks_per_stage", 0)),
     )

@@ -163,7 +163,8 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
 
     la, lb, lc, ld_ = conf.global_a_layout, conf.global_b_layout, conf.global_c_layout, conf.global_d_layout
     desc = L.GemmDesc(number=number, m=M, n=N, k=K, compute=comp, op=op, alpha=alpha, beta=beta,
-                      tile_n=conf.tile_n, cta_group=conf.cta_group, stages=conf.stages)
+                      tile_n=conf.tile_n, cta_group=conf.cta_group, stages=conf.stages,
+                      k_blocks_per_stage=conf.k_blocks_per_stage)
     desc.trans_a = 0 if la.col_major else 1
     desc.trans_b = 0 if lb.col_major else 1
     sw = conf.cta_swizzle

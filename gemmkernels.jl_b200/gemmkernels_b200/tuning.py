@@ -32,6 +32,7 @@ TILE_N = (64, 128, 192, 256, 512)   # 512 = two 256-column accumulators sharing 
 CTA_GROUP = (1, 2)
 STAGES = (0, 3, 4, 6)          # 0 = as many as shared memory holds
 RASTER_GROUP = (0, 4, 8, 16)   # 0 = built-in choice
+K_BLOCKS_PER_STAGE = (1, 2)    # 128-byte k-blocks per pipeline stage
 
 
 @dataclass(frozen=True)
@@ -55,22 +56,24 @@ class Candidate:
     cta_group: int
     stages: int
     raster_group: int
+    k_blocks_per_stage: int = 0
 
     def key(self) -> str:
-        return f"tn{self.tile_n}-cg{self.cta_group}-st{self.stages}-rg{self.raster_group}"
+        base = f"tn{self.tile_n}-cg{self.cta_group}-st{self.stages}-rg{self.raster_group}"
+        return base + (f"-kps{self.k_blocks_per_stage}" if self.k_blocks_per_stage else "")
 
 
 def candidates(problem: Problem, tile_n=TILE_N, cta_group=CTA_GROUP, stages=STAGES,
-               raster_group=RASTER_GROUP) -> Iterator[Candidate]:
+               raster_group=RASTER_GROUP, k_blocks_per_stage=K_BLOCKS_PER_STAGE) -> Iterator[Candidate]:
     """The sweep for one problem, without the combinations the engine would refuse anyway."""
-    for tn, cg, st, rg in itertools.product(tile_n, cta_group, stages, raster_group):
+    for tn, cg, st, rg, kps in itertools.product(tile_n, cta_group, stages, raster_group, k_blocks_per_stage):
         if cg == 2 and tn % 64:
             continue
         if tn == 512 and cg != 2:
             continue
         if tn > max(64, -(-problem.n // 32) * 32):        # wider than the whole matrix: a duplicate
             continue
-        yield Candidate(tn, cg, st, rg)
+        yield Candidate(tn, cg, st, rg, kps)
     yield Candidate(0, 0, 0, 0)                            # the built-in choice, for comparison
 
 
@@ -248,7 +251,7 @@ def _config(prob: Problem, cand: Candidate | None):
     la = Layout.UnsafeAlignedRowMajor[et] if prob.trans_a else Layout.UnsafeAlignedColMajor[et]
     lb = Layout.UnsafeAlignedRowMajor[et] if prob.trans_b else Layout.UnsafeAlignedColMajor[et]
     extra = {} if cand is None else dict(tile_n=cand.tile_n, cta_group=cand.cta_group, stages=cand.stages,
-                                         raster_group=cand.raster_group)
+                                         raster_group=cand.raster_group, k_blocks_per_stage=cand.k_blocks_per_stage)
     return get_config(gemm_shape=dict(M=prob.m, N=prob.n, K=prob.k),
                       operator=Operator.TCGen05Operator[Operator.TF32 if prob.dtype == "TF32" else et, eltypes.Float32],
                       global_a_layout=la, global_b_layout=lb,
@@ -269,7 +272,8 @@ def gpu_measure(prob: Problem, cand: Candidate, *, rtol: float = 1e-3, nvml=None
         d.zero_()
         from .matmul import query
         plan = query(conf, a, b, c, d)          # what the library resolves this candidate to
-        resolved = {"plan_tile_n": int(plan.tile_n), "plan_cta_group": int(plan.cluster), "plan_stages": int(plan.stages)}
+        resolved = {"plan_tile_n": int(plan.tile_n), "plan_cta_group": int(plan.cluster), "plan_stages": int(plan.stages),
+                    "plan_tile_k": int(plan.tile_k)}
         launch = bind(conf, a, b, c, d)
         launch()
         torch.cuda.synchronize()
@@ -332,12 +336,13 @@ def winners(results: dict, min_gain: float = 0.02) -> list[dict]:
         if top["tile_n"] == 0 or (base is not None and base["time_us"] <= top["time_us"] * (1.0 + min_gain)):
             continue
         if base is not None and "plan_tile_n" in base and "plan_tile_n" in top and all(
-                base[f] == top[f] for f in ("plan_tile_n", "plan_cta_group", "plan_stages")):
+                base.get(f) == top.get(f) for f in ("plan_tile_n", "plan_cta_group", "plan_stages", "plan_tile_k")):
             continue                      # the winner is what the planner resolves to anyway: the gap is noise
         dtype, m, n, k, ta, tb, has_c = _parse_problem_key(pk)
         out.append(dict(dtype=_GK_DTYPE[dtype], trans_a=int(ta), trans_b=int(tb), has_c=int(has_c), m=m, n=n, k=k,
                         tile_n=top["tile_n"], cta_group=top["cta_group"], stages=top["stages"],
-                        raster_group=top["raster_group"], time_us=top["time_us"],
+                        raster_group=top["raster_group"], k_blocks_per_stage=top.get("k_blocks_per_stage", 0), reserved=0,
+                        time_us=top["time_us"],
                         planner_time_us=base["time_us"] if base else None, problem=pk))
     return out
 
@@ -348,11 +353,12 @@ def emit_table(results_path, out_path) -> int:
     entries = winners(load_results(results_path))
     lines = ["// Generated by `python -m gemmkernels_b200.tuning --emit-table` from a sweep on B200: the fastest verified",
              "// candidate of each measured problem where it beat the planner's own choice by 2 % or more.",
-             "// {dtype, trans_a, trans_b, has_c, m, n, k, tile_n, cta_group, stages, raster_group}"]
+             "// {dtype, trans_a, trans_b, has_c, m, n, k, tile_n, cta_group, stages, raster_group, k_blocks_per_stage, 0}"]
     for e in entries:
         note = f"{e['time_us']:.1f} us" + (f" (planner {e['planner_time_us']:.1f} us)" if e["planner_time_us"] else "")
         lines.append(f"    {{{e['dtype']}, {e['trans_a']}, {e['trans_b']}, {e['has_c']}, {e['m']}, {e['n']}, {e['k']}, "
-                     f"{e['tile_n']}, {e['cta_group']}, {e['stages']}, {e['raster_group']}}},   // {e['problem']}: {note}")
+                     f"{e['tile_n']}, {e['cta_group']}, {e['stages']}, {e['raster_group']}, {e['k_blocks_per_stage']}, 0}},"
+                     f"   // {e['problem']}: {note}")
     Path(out_path).write_text("\n".join(lines) + "\n")
     return len(entries)
 
@@ -393,7 +399,7 @@ def main(argv=None) -> int:
         print(f"{emit_table(args.out, args.emit_table)} entries written to {args.emit_table}")
         return 0
     probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype, args.with_c) for n in args.sizes for l in args.layouts]
-    fn = (lambda p: candidates(p, stages=(0,), raster_group=(0,))) if args.quick else candidates
+    fn = (lambda p: candidates(p, tile_n=(64, 128, 256, 512), stages=(0,), raster_group=(0,))) if args.quick else candidates
     tune(probs, args.out, candidate_fn=fn)
     return 0
 

@@ -130,6 +130,7 @@ typedef struct gk_gemm_desc {
    * batch <= 1 is the single product.  Real number system only; tensor-core operands need batch
    * strides that are multiples of 16 bytes.  The reference has no batched entry point. */
   int32_t batch;
+  int32_t k_blocks_per_stage; /* tuning override: 128-byte k-blocks per pipeline stage, 1 or 2 (0 = choose) */
   int64_t batch_stride_a, batch_stride_b, batch_stride_c, batch_stride_d;
 } gk_gemm_desc;
 
@@ -146,7 +147,7 @@ typedef struct gk_gemm_plan {
                            5 = contraction gather kernel */
   int32_t grid, block, cluster;
   int32_t smem_bytes, tmem_columns;
-  int32_t tile_m, tile_n, tile_k, stages;
+  int32_t tile_m, tile_n, tile_k, stages; /* tile_k: K elements per pipeline stage */
   int64_t workspace_bytes;
 } gk_gemm_plan;
 
@@ -195,6 +196,7 @@ typedef struct gk_tuning_entry {
   int32_t has_c;        /* measured with beta != 0 (the epilogue reads C) */
   int64_t m, n, k;
   int32_t tile_n, cta_group, stages, raster_group;   /* as in gk_gemm_desc; 0 = leave to the planner */
+  int32_t k_blocks_per_stage, reserved;
 } gk_tuning_entry;
 
 /* Replaces the handle's table with `count` entries (copied); count = 0 clears it.  The compiled-in

@@ -42,7 +42,7 @@ def test_version_and_error_string_without_gpu():
 def test_struct_sizes_match_header_layout():
     """The ctypes mirrors must have the C layout: the library rejects any other struct_size."""
     from gemmkernels_b200 import _lib
-    # gk_gemm_desc: 2*4 + 3*8 + 2*4 + 6*4 + 4*8 + 4*8 + 4*4 + 2*8 + 8*4 + (4 + 4 padding) + 4*8 = 232
+    # gk_gemm_desc: 2*4 + 3*8 + 2*4 + 6*4 + 4*8 + 4*8 + 4*4 + 2*8 + 8*4 + 2*4 + 4*8 = 232
     assert ctypes.sizeof(_lib.GemmDesc) == 232
     assert ctypes.sizeof(_lib.ContractDesc) == 4 * 4 + 3 * 8 * 4 + 7 * 8 * 8 + 6 * 4 + 2 * 8 + 6 * 4
     assert ctypes.sizeof(_lib.EpilogueDesc) == 32

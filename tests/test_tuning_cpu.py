@@ -13,7 +13,7 @@ def test_candidates_skip_refused_combinations():
     cs = list(T.candidates(p))
     assert len(set(c.key() for c in cs)) == len(cs)
     assert all(not (c.cta_group == 2 and c.tile_n % 64) for c in cs)
-    assert T.Candidate(256, 2, 0, 0) in cs and T.Candidate(512, 2, 0, 0) in cs
+    assert T.Candidate(256, 2, 0, 0, 1) in cs and T.Candidate(512, 2, 0, 0, 2) in cs
     assert not any(c.tile_n == 512 and c.cta_group == 1 for c in cs)
     assert cs[-1] == T.Candidate(0, 0, 0, 0)                # the built-in choice is measured too
     narrow = list(T.candidates(T.Problem(4096, 64, 4096)))
@@ -103,11 +103,11 @@ def test_winners_and_emitted_table(tmp_path):
     """The sweep's winners become the library's defaults: one entry per problem whose best candidate
     beats the planner's own choice by 2 % or more, written as the initialiser list the library compiles in."""
     path = tmp_path / "r.jsonl"
-    def rec(pk, tn, cg, st, rg, t, cat="success"):
-        T.append_result(path, dict(problem=pk, candidate=T.Candidate(tn, cg, st, rg).key(), tile_n=tn, cta_group=cg,
-                                   stages=st, raster_group=rg, category=cat, time_us=t))
+    def rec(pk, tn, cg, st, rg, t, cat="success", kps=0):
+        T.append_result(path, dict(problem=pk, candidate=T.Candidate(tn, cg, st, rg, kps).key(), tile_n=tn, cta_group=cg,
+                                   stages=st, raster_group=rg, k_blocks_per_stage=kps, category=cat, time_us=t))
     rec("Float16:2048x2048x2048:NN", 0, 0, 0, 0, 20.9)
-    rec("Float16:2048x2048x2048:NN", 256, 1, 4, 0, 19.0)          # 10 % faster than the planner: an entry
+    rec("Float16:2048x2048x2048:NN", 256, 1, 4, 0, 19.0, kps=2)   # 10 % faster than the planner: an entry
     rec("Float16:2048x2048x2048:NN", 128, 2, 0, 0, 5.0, cat="invalid_result")   # fast but wrong: never a winner
     rec("TF32:4096x4096x4096:TN+C", 0, 0, 0, 0, 100.0)
     rec("TF32:4096x4096x4096:TN+C", 256, 2, 0, 8, 99.5)           # within the margin: no entry
@@ -115,12 +115,12 @@ def test_winners_and_emitted_table(tmp_path):
     w = T.winners(T.load_results(path))
     assert [e["problem"] for e in w] == ["BFloat16:8192x1024x8192:NT", "Float16:2048x2048x2048:NN"]
     assert w[1] == dict(w[1], dtype=0, trans_a=0, trans_b=0, has_c=0, m=2048, n=2048, k=2048, tile_n=256, cta_group=1,
-                        stages=4, raster_group=0)
+                        stages=4, raster_group=0, k_blocks_per_stage=2)
     assert w[0]["dtype"] == 1 and w[0]["trans_b"] == 1 and (w[0]["m"], w[0]["n"], w[0]["k"]) == (8192, 1024, 8192)
     out = tmp_path / "tuned_table.inc"
     assert T.emit_table(path, out) == 2
     text = out.read_text()
-    assert "{0, 0, 0, 0, 2048, 2048, 2048, 256, 1, 4, 0}," in text and "{1, 0, 1, 0, 8192, 1024, 8192, 512, 2, 0, 0}," in text
+    assert "{0, 0, 0, 0, 2048, 2048, 2048, 256, 1, 4, 0, 2, 0}," in text and "{1, 0, 1, 0, 8192, 1024, 8192, 512, 2, 0, 0, 0, 0}," in text
     assert all(l.startswith("//") or l.startswith("    {") for l in text.splitlines())
 
 
@@ -132,4 +132,4 @@ def test_compiled_in_table_is_well_formed():
     for line in inc.read_text().splitlines():
         if line.strip() and not line.lstrip().startswith("//"):
             m = re.match(r"\s*\{([^}]*)\},", line)
-            assert m and len(m.group(1).split(",")) == 11, line
+            assert m and len(m.group(1).split(",")) == 13, line
