@@ -653,12 +653,6 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
               }
             }
           }
-          if ((p.debug & 66) == 66) {   // measurement aid (only without MMAs): a plain arrival instead of the commit
-            if (elected) {
-              if constexpr (CG == 2) { mbar_arrive_cluster(map_to_cta(bar_empty + 8u * s, 0)); mbar_arrive_cluster(map_to_cta(bar_empty + 8u * s, 1)); }
-              else mbar_arrive(bar_empty + 8u * s);
-            }
-          } else
           if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
           if (kb == kb0 && acc_it == 0 && lane == 0) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
@@ -744,45 +738,6 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const int m_in = m % p.m_div, m_out = m / p.m_div;
       const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch + split_off;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1 + bt * p.c_batch;
-      if (PLANES == 1 && fast_store && (p.debug & 32)) {
-        // The same stores, software-pipelined over half chunks of 16 columns: the tensor-memory load of
-        // the next half chunk is in flight while this one is written out.
-        const int halves = 2 * ((bn_tile - chunk_first + chunk_step - 1) / chunk_step);
-        auto col_of = [&](int h) { return chunk_first + (h >> 1) * chunk_step + (h & 1) * 16; };
-        auto taddr_of = [&](int c) { return t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c); };
-        auto store_half = [&](const uint32_t (&v)[16], int c) {
-          const int ncols = p.N - (n0 + c);
-          if (!m_ok || ncols <= 0) return;
-          const int n_in = (n0 + c) % p.n_div, n_out = (n0 + c) / p.n_div;
-          float* dp = static_cast<float*>(p.D) + d_row + n_in * p.d_sn0 + n_out * p.d_sn1;
-          if (ncols >= 16) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float x = fmaf(p.alpha, __uint_as_float(v[j]), bias_row);
-              dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (j < ncols) {
-                const float x = fmaf(p.alpha, __uint_as_float(v[j]), bias_row);
-                dp[j * p.d_sn0] = p.act == TC_ACT_RELU ? fmaxf(x, 0.0f) : x;
-              }
-            }
-          }
-        };
-        uint32_t va[16], vb[16];
-        tmem_ld_32x16(taddr_of(col_of(0)), va);
-        tmem_ld_wait();
-        for (int h = 0; h < halves; h += 2) {
-          tmem_ld_32x16(taddr_of(col_of(h + 1)), vb);       // halves is even: h + 1 exists
-          store_half(va, col_of(h));
-          tmem_ld_wait();
-          if (h + 2 < halves) tmem_ld_32x16(taddr_of(col_of(h + 2)), va);
-          store_half(vb, col_of(h + 1));
-          tmem_ld_wait();
-        }
-      } else
       for (int c = chunk_first; c < bn_tile; c += chunk_step) {
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)

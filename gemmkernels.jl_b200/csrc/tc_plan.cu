@@ -500,13 +500,18 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   p.idesc = idesc;
   p.idesc_neg = idesc | (1u << 13);                   // negate A
 
-  // Two k-blocks per stage halve what every k-block pays in barrier round trips and in tcgen05.commit
-  // (≈250 ns per stage whatever the tile, measured: as long as one k-block of a 256 x 256 tile takes the
-  // tensor cores).  Taken when three such stages still fit and there are k-blocks enough to fill them.
+  // Every pipeline stage costs the producer and MMA warps a fixed ≈250 ns (barrier waits, votes, loop
+  // bookkeeping: measured with copies and MMAs switched off, the same for every tile shape), which a
+  // 128-column tile's four MMAs per k-block (≈130 ns) cannot cover.  Small tiles therefore put two
+  // k-blocks in a stage (1024^3: 10.7 -> 8.7 us); for tiles whose MMAs outlast the fixed cost it only
+  // makes the ring shallower (8192^3 with 256 x 256 tiles: 857 -> 898 us), so they keep one.
   const int kblock_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
   const int boxes_per_kblock = planes * std::max(p.a_boxes * p.a_sub, n_sub * p.b_boxes * p.b_sub);
+  const int mma_cycles_per_kblock = 2 * bn * n_sub * p.n_terms;
   int kps = pr.kps;
-  if (kps == 0) kps = ((kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 && 2 * boxes_per_kblock <= 32) ? 2 : 1;
+  if (kps == 0)
+    kps = (mma_cycles_per_kblock < 480 && (kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 &&
+           2 * boxes_per_kblock <= 32) ? 2 : 1;
   if (kps * boxes_per_kblock > 32) kps = 1;
   p.kps = kps;
   const int stage_bytes = kps * kblock_bytes;
