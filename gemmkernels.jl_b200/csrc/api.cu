@@ -100,8 +100,27 @@ static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, co
   return true;
 }
 
+// Tail split of the FFMA kernel (fpu_gemm.cuh): how many parts the tiles of the last round are cut into
+// (1 = none), the first split tile, and the workspace the partial sums need.
+struct FpuSplit { int q = 1, first = 0; int64_t bytes = 0; };
+static FpuSplit fpu_plan_split(gk_handle h, const gk_gemm_desc& d) {
+  FpuSplit sp;
+  const int64_t tiles = (d.m / kFpuBM) * (d.n / kFpuBN);
+  const int64_t slots = 2 * static_cast<int64_t>(h->sm_count);     // two CTAs per SM
+  const int64_t rem = tiles % slots;
+  const int64_t kt = d.k / kFpuBK;
+  if (tiles <= slots || rem == 0 || 2 * rem > slots || kt < 64) return sp;   // one round, a full last round, or a short K
+  int q = static_cast<int>(std::min<int64_t>(slots / rem, 4));
+  while (q > 1 && kt / q < 16) --q;
+  if (q < 2) return sp;
+  sp.q = q; sp.first = static_cast<int>(tiles - rem);
+  sp.bytes = rem * q * static_cast<int64_t>(kFpuBM) * kFpuBN * 4;
+  return sp;
+}
+
 static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogue_desc* epi, const void* a,
-                            const void* b, const void* c, void* dd, cudaStream_t stream) {
+                            const void* b, const void* c, void* dd, cudaStream_t stream, void* workspace = nullptr,
+                            int64_t workspace_bytes = 0) {
   FpuParams p{};
   p.A = a; p.B = b;
   p.C = static_cast<const float*>(c); p.D = static_cast<float*>(dd);
@@ -116,7 +135,16 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
                                  : static_cast<int>(std::lround(std::sqrt(2.0 * h->sm_count)));
   if (d.raster == GK_RASTER_IDENTITY) group = p.tiles_m;
   p.raster_group = std::max(1, std::min(group, p.tiles_m));
-  const dim3 grid(static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n));
+  p.split_q = 1; p.split_first = 0; p.kt_per_part = 0; p.ws = nullptr;
+  unsigned blocks = static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n);
+  const FpuSplit sp = fpu_plan_split(h, d);
+  if (sp.q > 1 && workspace && workspace_bytes >= sp.bytes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
+    p.split_q = sp.q; p.split_first = sp.first; p.ws = static_cast<float*>(workspace);
+    const int kt = p.K / kFpuBK;
+    p.kt_per_part = (kt + sp.q - 1) / sp.q;
+    blocks = static_cast<unsigned>(sp.first) + (blocks - static_cast<unsigned>(sp.first)) * static_cast<unsigned>(sp.q);
+  }
+  const dim3 grid(blocks);
   const bool ak = d.trans_a != 0;   // stored K x M: K is the contiguous index of A
   const bool bk = d.trans_b == 0;   // stored K x N: K is the contiguous index of B
   auto launch = [&](auto tag) {
@@ -130,6 +158,11 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   else if (d.dtype_a == GK_BF16) launch(__nv_bfloat16{});
   else launch(float{});
   GK_CUDA_CHECK(cudaGetLastError());
+  if (p.split_q > 1) {
+    const unsigned n_split = static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n) - static_cast<unsigned>(p.split_first);
+    fpu_tail_reduce_kernel<<<n_split, 256, 0, stream>>>(p);
+    GK_CUDA_CHECK(cudaGetLastError());
+  }
   return GK_OK;
 }
 
@@ -488,6 +521,7 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->block = kFpuThreads; plan->cluster = 1;
     plan->smem_bytes = 2 * 2 * kFpuBK * (kFpuBM + kFpuPad) * 4;
     plan->tile_m = kFpuBM; plan->tile_n = kFpuBN; plan->tile_k = kFpuBK; plan->stages = 2;
+    if (desc->batch <= 1) plan->workspace_bytes = fpu_plan_split(h, *desc).bytes;   // optional: splits the last round's tiles along K
   } else {
     // same rule as launch_simt_typed: 128 x 128 tiles for 4-byte accumulators once there are 96 of them
     const bool float_acc = desc->dtype_d == GK_F32 || desc->dtype_d == GK_F16 || desc->dtype_d == GK_BF16;
@@ -599,7 +633,8 @@ static gk_status gemm_single(gk_handle h, const gk_gemm_desc* desc, const void* 
     const void* bi = at(b, desc->batch_stride_b, desc->dtype_b);
     const void* ci = at(c, desc->batch_stride_c, desc->dtype_c);
     void* di = const_cast<void*>(at(d, desc->batch_stride_d, desc->dtype_d));
-    s = fpu ? launch_fpu(h, *desc, epi, ai, bi, ci, di, st) : launch_simt(*desc, epi, ai, bi, ci, di, st);
+    s = fpu ? launch_fpu(h, *desc, epi, ai, bi, ci, di, st, batch == 1 ? workspace : nullptr, workspace_bytes)
+            : launch_simt(*desc, epi, ai, bi, ci, di, st);
     if (s != GK_OK) return s;
   }
   return GK_OK;

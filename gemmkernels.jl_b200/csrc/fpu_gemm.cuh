@@ -36,6 +36,14 @@ struct FpuParams {
   int act;        // 0 none, 1 relu, 2 gelu
   int tiles_m, tiles_n;
   int raster_group;
+  // Tail split.  CTAs start in block order, two per SM, so the tiles of the last, partly filled round are
+  // the highest-numbered ones.  When that round would fill at most half of the slots, each of its tiles
+  // (those from split_first on) is cut along K into split_q parts that run side by side: block
+  // split_first + u handles part u % split_q of tile split_first + u / split_q and writes its raw
+  // partial sums to ws (one 128 x 128 FP32 tile per part); fpu_tail_reduce_kernel adds the parts and
+  // applies the epilogue.  split_q == 1: no split.
+  int split_first, split_q, kt_per_part;
+  float* ws;
 };
 
 // Global -> registers for one operand tile: 2 float4 per thread.
@@ -102,10 +110,18 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
   __shared__ __align__(16) float As[2][kFpuBK][kFpuBM + kFpuPad];
   __shared__ __align__(16) float Bs[2][kFpuBK][kFpuBN + kFpuPad];
 
+  // which tile, and which part of its K range
+  int t = blockIdx.x, part = 0;
+  const bool split = p.split_q > 1 && t >= p.split_first;
+  if (split) {
+    const int u = t - p.split_first;
+    t = p.split_first + u / p.split_q;
+    part = u % p.split_q;
+  }
   // tile raster: bands of `raster_group` tiles down M, then along N (same walk as the tcgen05 path)
   int tm, tn;
   {
-    const int t = blockIdx.x, g = p.raster_group;
+    const int g = p.raster_group;
     const int band = g * p.tiles_n, band_id = t / band, first_m = band_id * g;
     const int rows = min(g, p.tiles_m - first_m), r = t - band_id * band;
     tm = first_m + r % rows;
@@ -125,16 +141,18 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
     for (int j = 0; j < 8; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
 
   float4 ra[2], rb[2];
-  const int kt_count = p.K / kFpuBK;
-  fpu_load_tile<A_KMAJOR>(gA, p.lda, m0, 0, ra);
-  fpu_load_tile<B_KMAJOR>(gB, p.ldb, n0, 0, rb);
+  const int kt_all = p.K / kFpuBK;
+  const int kt_first = split ? part * p.kt_per_part : 0;
+  const int kt_count = split ? min(kt_all, kt_first + p.kt_per_part) : kt_all;   // one past the last k-tile
+  fpu_load_tile<A_KMAJOR>(gA, p.lda, m0, kt_first * kFpuBK, ra);
+  fpu_load_tile<B_KMAJOR>(gB, p.ldb, n0, kt_first * kFpuBK, rb);
   // alpha scales A on its way in, as the reference's shared_to_regs_a transform does
   fpu_store_tile<A_KMAJOR>(As[0], ra, p.alpha);
   fpu_store_tile<B_KMAJOR>(Bs[0], rb, 1.0f);
   __syncthreads();
 
-  for (int kt = 0; kt < kt_count; ++kt) {
-    const int cur = kt & 1;
+  for (int kt = kt_first; kt < kt_count; ++kt) {
+    const int cur = (kt - kt_first) & 1;
     const bool more = kt + 1 < kt_count;
     if (more) {
       fpu_load_tile<A_KMAJOR>(gA, p.lda, m0, (kt + 1) * kFpuBK, ra);
@@ -164,6 +182,21 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
   }
 
   // epilogue: each thread owns rows m0 + {tx*4..+3, 64 + tx*4..+3} and columns n0 + {ty*4..+3, 64 + ..}
+  if (split) {
+    // raw partial sums (alpha is in them already: it scaled A on its way into shared memory)
+    float* w = p.ws + (static_cast<size_t>(t - p.split_first) * p.split_q + part) * (kFpuBM * kFpuBN);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int nl = (j >> 2) * 64 + ty * 4 + (j & 3);
+#pragma unroll
+      for (int ih = 0; ih < 2; ++ih) {
+        const int ml = ih * 64 + tx * 4;
+        *reinterpret_cast<float4*>(w + ml + nl * kFpuBM) =
+            make_float4(acc[ih * 2][j].x, acc[ih * 2][j].y, acc[ih * 2 + 1][j].x, acc[ih * 2 + 1][j].y);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int jh = 0; jh < 2; ++jh)
 #pragma unroll
@@ -191,6 +224,43 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
         *reinterpret_cast<float4*>(p.D + m + static_cast<int64_t>(n) * p.ldd) = v;
       }
     }
+}
+
+// Second pass of the tail split: one block per split tile adds its parts and applies the epilogue.
+__global__ void __launch_bounds__(256) fpu_tail_reduce_kernel(const FpuParams p) {
+  const int t = p.split_first + blockIdx.x;
+  int tm, tn;
+  {
+    const int g = p.raster_group;
+    const int band = g * p.tiles_n, band_id = t / band, first_m = band_id * g;
+    const int rows = min(g, p.tiles_m - first_m), r = t - band_id * band;
+    tm = first_m + r % rows;
+    tn = r / rows;
+  }
+  const int m0 = tm * kFpuBM, n0 = tn * kFpuBN;
+  const float* w = p.ws + static_cast<size_t>(blockIdx.x) * p.split_q * (kFpuBM * kFpuBN);
+  for (int e = threadIdx.x; e < kFpuBM * kFpuBN / 4; e += blockDim.x) {
+    const int ml = (e % (kFpuBM / 4)) * 4, nl = e / (kFpuBM / 4);
+    float4 v = *reinterpret_cast<const float4*>(w + ml + nl * kFpuBM);
+    for (int q = 1; q < p.split_q; ++q) {
+      const float4 u = *reinterpret_cast<const float4*>(w + static_cast<size_t>(q) * (kFpuBM * kFpuBN) + ml + nl * kFpuBM);
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    const int m = m0 + ml, n = n0 + nl;
+    if (p.beta != 0.0f) {
+      const float4 c = *reinterpret_cast<const float4*>(p.C + m + static_cast<int64_t>(n) * p.ldc);
+      v.x = fmaf(p.beta, c.x, v.x); v.y = fmaf(p.beta, c.y, v.y); v.z = fmaf(p.beta, c.z, v.z); v.w = fmaf(p.beta, c.w, v.w);
+    }
+    if (p.bias_axis == 1) {
+      const float4 bm = __ldg(reinterpret_cast<const float4*>(p.bias + m));
+      v.x += bm.x; v.y += bm.y; v.z += bm.z; v.w += bm.w;
+    } else if (p.bias_axis == 2) {
+      const float bn = __ldg(p.bias + n);
+      v.x += bn; v.y += bn; v.z += bn; v.w += bn;
+    }
+    v.x = fpu_act(v.x, p.act); v.y = fpu_act(v.y, p.act); v.z = fpu_act(v.z, p.act); v.w = fpu_act(v.w, p.act);
+    *reinterpret_cast<float4*>(p.D + m + static_cast<int64_t>(n) * p.ldd) = v;
+  }
 }
 
 }  // namespace gk

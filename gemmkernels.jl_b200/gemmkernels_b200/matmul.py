@@ -242,9 +242,12 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
 
 def _wants_workspace(desc) -> bool:
     """Cases in which the library can use a workspace: interleaved complex / dual operands (split into
-    planes first) and real products with few output tiles and a long K (split-K)."""
+    planes first), real tensor-core products with few output tiles and a long K (split-K), and large
+    FFMA products (the tiles of a partly filled last round are cut along K)."""
     if desc.number != L.GK_REAL:
         return desc.plane_a == 0 or desc.plane_b == 0
+    if desc.op == L.GK_OP_FPU and desc.dtype_d == L.GK_F32:
+        return desc.m * desc.n >= (1 << 22) and desc.k >= 1024      # the FFMA kernel's tail split
     return desc.m * desc.n <= (1 << 22) and desc.k >= 2048
 
 

@@ -20,7 +20,7 @@ struct GkGemmDesc
     alpha::Float64; beta::Float64
     tile_n::Int32; cta_group::Int32; stages::Int32; raster_group::Int32; max_ctas::Int32
     debug::Int32; host_chunk_mib::Int32; a_resident::Int32
-    batch::Int32                                     # (4 bytes of padding follow, as in C)
+    batch::Int32; k_blocks_per_stage::Int32
     batch_stride_a::Int64; batch_stride_b::Int64; batch_stride_c::Int64; batch_stride_d::Int64
 end
 struct GkEpilogueDesc
@@ -140,7 +140,7 @@ function matmul(conf::Config, a, b, c, d;
                       plane(a, la), plane(b, lb), plane(c, lc), plane(d, ldl),
                       layout_kind(la), layout_kind(lb), layout_kind(lc), rk, alpha, beta,
                       conf.tile_n, conf.cta_group, conf.stages, rg == 0 ? conf.raster_group : rg, 0,
-                      0, 0, 0, 0, 0, 0, 0, 0)
+                      0, 0, 0, 0, 0, 0, 0, 0, 0)
     epi = GkEpilogueDesc(sizeof(GkEpilogueDesc), has_bias ? (epilogue.axis === :row ? 1 : 2) : 0,
                          has_bias ? reinterpret(CuPtr{Float32}, epilogue.bias_pointer) : CuPtr{Float32}(0), act, (0, 0, 0))
     # Interleaved complex / dual operands need a workspace (they are split into planes first); real products

@@ -212,7 +212,9 @@ GK_API gk_status gk_load_tuning(gk_handle h, const gk_tuning_entry* entries, int
  * tensor-core products with few output tiles and a long K: given enough room, K is cut into runs over
  * the otherwise idle SMs (split-K: FP32 partial sums in the workspace, one reduction pass that
  * applies alpha, beta, bias and activation); with NULL, or with a buffer smaller than the partial
- * sums need, the same product runs unsplit.  Nothing is ever written beyond workspace_bytes. */
+ * sums need, the same product runs unsplit.  The FP32 FFMA kernel uses a workspace the same way for the
+ * tiles of a last round that would fill at most half of the GPU.  Nothing is ever written beyond
+ * workspace_bytes. */
 GK_API gk_status gk_gemm(gk_handle h, const gk_gemm_desc* desc, const void* a, const void* b,
                   const void* c, void* d, const gk_epilogue_desc* epi, void* workspace,
                   int64_t workspace_bytes, gk_stream stream);
