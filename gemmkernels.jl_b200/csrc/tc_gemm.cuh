@@ -474,7 +474,6 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       [[maybe_unused]] const int k_div = is_a ? p.a_k_div : p.b_k_div;
       const uint32_t full0_signal = (CG == 2) ? map_to_cta(bar_full, 0) : bar_full;
       const uint32_t tx_bytes = stage_bytes * CG;
-      const bool solo = (p.debug & 64) != 0;
       int s = 0;
       uint32_t ph = 0;
       uint32_t issued = 0;  // k-blocks issued so far by this CTA
@@ -501,15 +500,9 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         }
         for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) pt0 = clock64();
-          bool got;
-          if (solo) {   // one lane polls the barrier; the shuffle hands its answer (and the ordering) to the others
-            got = lane == 0 ? mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs) : true;
-            got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-          } else {
-            got = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs));
-          }
+          const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
-          if (!got) {
+          if (!__all_sync(0xffffffffu, got)) {
             if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
             ok = false;
             break;
@@ -606,12 +599,9 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const uint32_t a_k16 = p.a_kadv >> 4, b_k16 = p.b_kadv >> 4;
       const uint32_t b_sub16 = b_sub_bytes >> 4;
       const int n_terms = (p.debug & 2) ? 0 : p.n_terms;
-      // With `solo` the whole loop below is run by the elected lane alone (the other lanes go straight to the
-      // teardown): tcgen05.mma, tcgen05.commit and the barrier waits are single-thread operations, and one lane
-      // polling costs a fraction of thirty-two lanes polling and voting on the result at every stage.
-      const bool solo = (p.debug & 64) != 0;
-      const bool reporter = solo ? elected : lane == 0;
-      if (!solo || elected) {
+      // (Running this loop on the elected lane alone, and polling the producers' barriers from one lane, was
+      // measured and is slower than the converged warps: 744 against 728 us at 8192^3, 26.6 against 25.8 us at 2048^3.)
+      const bool reporter = lane == 0;
       int s = 0;
       uint32_t s16 = base16;
       uint32_t ph = 0;
@@ -627,7 +617,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         if (prof) t0 = clock64();
         const bool tgot = mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs);
         if (prof) mt += clock64() - t0;
-        if (!(solo ? tgot : __all_sync(0xffffffffu, tgot))) {
+        if (!__all_sync(0xffffffffu, tgot)) {
           if (reporter) tc_report(p.status, TC_ST_TIMEOUT_MMA);
           ok = false;
           break;
@@ -639,7 +629,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           if (prof) t0 = clock64();
           const bool fgot = mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs);
           if (prof) { t1 = clock64(); mw += t1 - t0; }
-          if (!(solo ? fgot : __all_sync(0xffffffffu, fgot))) {
+          if (!__all_sync(0xffffffffu, fgot)) {
             if (reporter) tc_report(p.status, TC_ST_TIMEOUT_MMA);
             ok = false;
             break;
@@ -693,7 +683,6 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
         }
       }
-      }   // !solo || elected
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue

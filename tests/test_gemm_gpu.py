@@ -599,6 +599,41 @@ def test_strided_batched_products(ab, op, share_b):
     assert torch.all(d_store[:, M * N:] == 0)
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (1, 1)])
+def test_fpu_tail_split_matches_the_unsplit_product(ta, tb):
+    """FFMA kernel, 360 tiles on 296 CTA slots: given a workspace, the 64 tiles of the last round are cut
+    along K in four parts that run side by side and a second pass adds them and applies beta, bias and
+    ReLU.  Same numbers as the unsplit launch (small integers: exact), nothing written past the workspace."""
+    M, N, K = 2560, 2304, 1024
+    rng = np.random.default_rng(31 + ta + 2 * tb)
+    A = rng.integers(-2, 3, (K, M) if ta else (M, K)).astype(np.float32)
+    B = rng.integers(-2, 3, (N, K) if tb else (K, N)).astype(np.float32)
+    Cm = rng.integers(-4, 5, (M, N)).astype(np.float32); bias = rng.integers(-3, 4, N).astype(np.float32)
+    a, b, c = dev(A), dev(B), dev(Cm)
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float32]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float32]
+    conf = GK.get_config(gemm_shape=(M, N, K), operator=Operator.FPUOp[8, 8, 1, 4, 8, 1, GK.Float32, GK.Float32],
+                         global_a_layout=la, global_b_layout=lb, global_c_layout=Layout.UnsafeAlignedColMajor[GK.Float32],
+                         global_d_layout=Layout.UnsafeAlignedColMajor[GK.Float32], is_a_col_major=not ta, is_b_col_major=not tb)
+    epi = Epilogue.Bias(dev(bias), axis="col")
+    kw = dict(epilogue=epi, transform_shared_to_global_d=Transform.Elementwise(Transform.ReLU()),
+              transform_shared_to_regs_a=Transform.Elementwise(Transform.Scale(2.0)))
+    plan = GK.query(conf, a, b, c, GK.cuarray(GK.Float32, M, N), **kw)
+    assert plan.kernel == 2 and plan.workspace_bytes == 64 * 4 * 128 * 128 * 4
+    want = np.maximum(2.0 * ((A.T if ta else A) @ (B.T if tb else B)) + Cm + bias[None, :], 0)
+    d_split = GK.cuarray(GK.Float32, M, N)
+    ws = torch.zeros(plan.workspace_bytes + 4096, dtype=torch.uint8, device="cuda"); ws[plan.workspace_bytes:] = 0x5A
+    GK.matmul(conf, a, b, c, d_split, workspace=ws[:plan.workspace_bytes], **kw)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert np.array_equal(GK.to_numpy(d_split), want)
+    assert torch.all(ws[plan.workspace_bytes:] == 0x5A) and ws[:plan.workspace_bytes].any()      # used, and not overrun
+    d_plain = GK.cuarray(GK.Float32, M, N)
+    small = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")                                 # too small: unsplit
+    GK.matmul(conf, a, b, c, d_plain, workspace=small, **kw)
+    torch.cuda.synchronize(); GK.poll_status()
+    assert torch.equal(d_plain, d_split)
+
+
 def test_chained_products_without_host_synchronisation():
     """Y = (A*B)*C with the first product's Float16 output feeding the second, ten chains enqueued back to back:
     the second kernel may start its set-up while the first is still running (programmatic dependent launch) but
