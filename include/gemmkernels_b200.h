@@ -127,8 +127,10 @@ typedef struct gk_gemm_desc {
                            after a broadcast from another rank) and is used in place, not uploaded */
   /* Strided-batched products: `batch` independent GEMMs of the same shape, operand x of product i at
    * x + i * batch_stride_x elements (batch_stride_a / _b = 0 shares that operand between the products).
-   * batch <= 1 is the single product.  Real number system only; tensor-core operands need batch
-   * strides that are multiples of 16 bytes.  The reference has no batched entry point. */
+   * batch <= 1 is the single product.  Real number system only.  On the tensor-core path the whole
+   * batch is one launch (batch strides that are not multiples of 16 bytes, like such leading
+   * dimensions, make its producers use ordinary loads instead of TMA); the SIMT families launch once
+   * per product.  The reference has no batched entry point. */
   int32_t batch;
   int32_t k_blocks_per_stage; /* tuning override: 128-byte k-blocks per pipeline stage, 1 or 2 (0 = choose) */
   int64_t batch_stride_a, batch_stride_b, batch_stride_c, batch_stride_d;
