@@ -82,8 +82,8 @@ struct gk_handle_s {
   std::mutex mu;                   // guards the caches below
   std::mutex host_mu;              // serialises gk_gemm_host calls (shared staging buffers)
   int max_clusters[2][4] = {};     // tc kernel [planes-1][tf32 + 2*rank5] -> co-resident CTA pairs
-  bool attr_set[2][2][4] = {};     // tc kernel [cg-1][planes-1][tf32 + 2*rank5]: smem attribute set
-  bool attr_set_generic = false;   // the same for the generic-load instance
+  bool attr_set[2][2][2][4] = {};  // tc kernel [debug instance][cg-1][planes-1][tf32 + 2*rank5]: smem attribute set
+  bool attr_set_generic[2] = {};   // the same for the generic-load instances
   // staging buffers of gk_gemm_host (grown on demand, freed by gk_destroy)
   void* stage_dev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, D, bias
   size_t stage_bytes[5] = {0, 0, 0, 0, 0};

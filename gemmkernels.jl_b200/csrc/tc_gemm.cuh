@@ -81,6 +81,8 @@ struct TcParams {
   int32_t kps;               // k-blocks per pipeline stage (1 or 2): one full/empty barrier round trip and one
                              // tcgen05.commit serve kps k-blocks, which halves the fixed cost per k-block
   int32_t stages;
+  int32_t pf;                // plain (3-D map) operands: k-blocks by which an L2 prefetch of the same box runs ahead of
+                             // its load (0: none).  Runs on into the CTA's next tile.
   int32_t a_mn_major, b_mn_major;
   int32_t a_boxes, b_boxes;  // TMA boxes per plane per CTA per k-block
   int32_t a_box_mn, b_box_mn;  // M/N elements per box of an MN-major operand (one swizzle span)
@@ -318,8 +320,12 @@ __device__ __forceinline__ void tc_fill_box_generic(uint8_t* dst, const uint16_t
   }
 }
 
-template <int CG, int PLANES, bool TF32, bool RANK5, bool GENERIC = false>
+// DBG selects the instance that honours TcParams::debug (measurement and test aids); in the production
+// instance every such branch is compiled out, which shortens the per-stage loops of the producer and
+// MMA warps (their cost per pipeline stage is instruction latency, not bandwidth).
+template <int CG, int PLANES, bool TF32, bool RANK5, bool GENERIC = false, bool DBG = false>
 __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+  const int dbg = DBG ? p.debug : 0;
   static_assert(!GENERIC || (CG == 1 && PLANES == 1 && !TF32 && !RANK5), "generic loads: one CTA, one plane, 16-bit types");
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes and the pattern is a function of the address.
@@ -351,7 +357,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   // Let the next kernel of the stream begin its own set-up as SMs free up (it waits, as this one does
   // below, before touching global memory).
   pdl_launch_dependents();
-  const uint64_t t_entry = (p.debug & 8) ? global_timer_ns() : 0;
+  const uint64_t t_entry = (dbg & 8) ? global_timer_ns() : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(bar_full + 8u * s, GENERIC ? 2 : 1);   // TMA: one arrival that also expects the bytes; generic: one per producer warp
@@ -378,7 +384,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   if constexpr (CG == 2) cluster_sync_all();  // peer barriers are initialised before any remote use
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
-  if (threadIdx.x == 0) tc_mark(p.status, p.debug, 1, 1);   // set-up done, TMEM allocated
+  if (threadIdx.x == 0) tc_mark(p.status, dbg, 1, 1);   // set-up done, TMEM allocated
 
   const int units_per_product = p.tiles_m * p.tiles_n * p.k_split;
   const int num_tiles = units_per_product * p.batch;         // work units
@@ -407,7 +413,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       uint32_t ph = 0;
       bool ok = true;
       pdl_wait();
-      for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
+      for (int t = cluster_id; t < num_tiles && ok && !(dbg & 4); t += num_clusters) {
         int tm, tn;
         const int bt = t / units_per_product;
         tc_tile_coords(p, (t - bt * units_per_product) / p.k_split, tm, tn);
@@ -478,10 +484,10 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       uint32_t ph = 0;
       uint32_t issued = 0;  // k-blocks issued so far by this CTA
       bool ok = true;
-      const bool prof = (p.debug & 8) != 0;
+      const bool prof = (dbg & 8) != 0;
       long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
       pdl_wait();           // operands may be the previous kernel's output
-      for (int t = cluster_id; t < num_tiles && ok && !(p.debug & 4); t += num_clusters) {
+      for (int t = cluster_id; t < num_tiles && ok && !(dbg & 4); t += num_clusters) {
         int tm, tn;
         const int bt = t / units_per_product;                 // which product of the batch
         tc_tile_coords(p, (t - bt * units_per_product) / p.k_split, tm, tn);
@@ -498,8 +504,31 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           const int kk0 = (kb0 + kj) * p.bk + k_add;
           k_in = kk0 % k_div; k_out = kk0 / k_div;
         }
+        // L2 prefetch: the same box `pf` k-blocks ahead, continuing into this CTA's next work unit, so that the
+        // loads proper find their lines in L2 instead of each waiting for HBM.
+        [[maybe_unused]] int mn_nx = 0, c2_nx = 0, kb0_nx = 0, kb1_nx = 0;
+        if constexpr (!RANK5) {
+          const int t2 = t + num_clusters;
+          if (p.pf > 0 && t2 < num_tiles) {
+            int tm2, tn2;
+            const int bt2 = t2 / units_per_product;
+            tc_tile_coords(p, (t2 - bt2 * units_per_product) / p.k_split, tm2, tn2);
+            kb0_nx = (t2 % p.k_split) * p.kb_per_split; kb1_nx = min(kb0_nx + p.kb_per_split, p.k_blocks);
+            c2_nx = pl + bt2 * (is_a ? p.a_batched : p.b_batched);
+            mn_nx = (is_a ? (tm2 * CG + static_cast<int>(rank)) * kTcTileM
+                          : tn2 * bn_tile + static_cast<int>(rank) * bn_cta) + mn_add;
+          }
+        }
         for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) pt0 = clock64();
+          if constexpr (!RANK5) {
+            if (p.pf > 0 && active) {
+              int kf = kb + kj + p.pf, mnf = mn, c2f = c2;
+              bool go = kf < kb1;
+              if (!go) { kf = kf - kb1 + kb0_nx; mnf = mn_nx; c2f = c2_nx; go = kf < kb1_nx; }
+              if (go) tma_prefetch_l2_3d(tmap, mn_major ? mnf : kf * p.bk, mn_major ? kf * p.bk : mnf, c2f);
+            }
+          }
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
           if (!__all_sync(0xffffffffu, got)) {
@@ -507,8 +536,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             ok = false;
             break;
           }
-          if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 1);   // about to issue first copies
-          if (p.debug & 1) {
+          if (issued == 0 && lane == 0) tc_mark(p.status, dbg, is_a ? 2 : 3, 1);   // about to issue first copies
+          if (dbg & 1) {
             if (lane == 0 && leader && is_a) mbar_arrive(bar_full + 8u * s);
           } else {
             // Bytes may be counted on the barrier before they are expected: the phase cannot
@@ -539,7 +568,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
               }
             }
           }
-          if (issued == 0 && lane == 0) tc_mark(p.status, p.debug, is_a ? 2 : 3, 2);   // first copies issued
+          if (issued == 0 && lane == 0) tc_mark(p.status, dbg, is_a ? 2 : 3, 2);   // first copies issued
           if constexpr (RANK5) {
             k_in += p.kps * p.bk;
             while (k_in >= k_div) { k_in -= k_div; ++k_out; }
@@ -598,7 +627,21 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const uint32_t stage16 = stage_bytes >> 4, kblock16 = kblock_bytes >> 4;
       const uint32_t a_k16 = p.a_kadv >> 4, b_k16 = p.b_kadv >> 4;
       const uint32_t b_sub16 = b_sub_bytes >> 4;
-      const int n_terms = (p.debug & 2) ? 0 : p.n_terms;
+      const int n_terms = (dbg & 2) ? 0 : p.n_terms;
+      // Low descriptor words relative to the k-block's base, and accumulator columns, for every MMA of a
+      // k-block: the loop then adds the base and issues.
+      uint32_t off_a[kMaxTerms][kTcMmaPerKBlock], off_b[kMaxTerms][2][kTcMmaPerKBlock], d_off[kMaxTerms][2];
+#pragma unroll
+      for (int ti = 0; ti < kMaxTerms; ++ti) {
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+          d_off[ti][nb] = nb * sub_cols + t_d[ti];
+#pragma unroll
+          for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) off_b[ti][nb][ks] = t_b[ti] + nb * b_sub16 + ks * b_k16;
+        }
+#pragma unroll
+        for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) off_a[ti][ks] = t_a[ti] + ks * a_k16;
+      }
       // (Running this loop on the elected lane alone, and polling the producers' barriers from one lane, was
       // measured and is slower than the converged warps: 744 against 728 us at 8192^3, 26.6 against 25.8 us at 2048^3.)
       const bool reporter = lane == 0;
@@ -607,7 +650,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       uint32_t ph = 0;
       uint32_t acc_it = 0;
       bool ok = true;
-      const bool prof = (p.debug & 8) != 0;
+      const bool prof = (dbg & 8) != 0;
       long long mw = 0, mi = 0, mt = 0, t0 = 0, t1 = 0;
       const long long k_start = clock64();
       const uint64_t g_start = global_timer_ns();
@@ -625,6 +668,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         tc_fence_after_sync();
         const uint32_t d_base = tmem_base + as * acc_cols;
         const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+        bool first_kb = true;   // the first k-block of a tile (or K-run) overwrites the accumulators
         for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) t0 = clock64();
           const bool fgot = mbar_wait(bar_full + 8u * s, ph, abort_flag, kTcWaitLimitNs);
@@ -635,7 +679,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
             break;
           }
           tc_fence_after_sync();
-          if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, p.debug, 4, 1);   // first stage landed
+          if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, dbg, 4, 1);   // first stage landed
           for (int kj = 0; kj < p.kps && kb + kj < kb1; ++kj) {   // the k-blocks of this stage that belong to the run
             const uint32_t k16 = s16 + kj * kblock16;
 #pragma unroll
@@ -646,18 +690,19 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
 #pragma unroll
                   for (int ti = 0; ti < kMaxTerms; ++ti) {
                     if (ti < n_terms) {
-                      const uint64_t da = smem_desc(k16 + t_a[ti] + ks * a_k16, hi_a);
-                      const uint64_t db = smem_desc(k16 + t_b[ti] + nb * b_sub16 + ks * b_k16, hi_b);
-                      const uint32_t acc = ((kb + kj - kb0) | ks) ? 1u : t_keep[ti];
-                      if (elected) umma<CG, TF32>(d_base + nb * sub_cols + t_d[ti], da, db, t_id[ti], acc);
+                      const uint64_t da = smem_desc(k16 + off_a[ti][ks], hi_a);
+                      const uint64_t db = smem_desc(k16 + off_b[ti][nb][ks], hi_b);
+                      const uint32_t acc = (ks == 0 && first_kb) ? t_keep[ti] : 1u;
+                      if (elected) umma<CG, TF32>(d_base + d_off[ti][nb], da, db, t_id[ti], acc);
                     }
                   }
                 }
               }
             }
+            first_kb = false;
           }
           if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
-          if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, p.debug, 4, 2);   // first MMAs issued
+          if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, dbg, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
           if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }
           if (prof) mi += clock64() - t1;
@@ -724,16 +769,16 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         }
       }
       // all-or-nothing per warp: the TMEM loads below are warp-collective
-      const long long e0 = (p.debug & 8) ? clock64() : 0;
+      const long long e0 = (dbg & 8) ? clock64() : 0;
       const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);
-      const long long e1 = (p.debug & 8) ? clock64() : 0;
+      const long long e1 = (dbg & 8) ? clock64() : 0;
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_EPILOGUE);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, p.debug, 5, 1);   // first accumulator complete
+      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, dbg, 5, 1);   // first accumulator complete
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * acc_cols;
       const bool m_ok = m < p.M;
       float bias_row = 0.0f;
@@ -846,8 +891,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
         if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * as);
         else mbar_arrive(bar_tempty + 8u * as);
       }
-      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, p.debug, 5, 2);   // first tile stored
-      if ((p.debug & 8) && warp == 4 && lane == 0) {
+      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, dbg, 5, 2);   // first tile stored
+      if ((dbg & 8) && warp == 4 && lane == 0) {
         p.dbg_out[blockIdx.x * 16 + 7] += e1 - e0;
         p.dbg_out[blockIdx.x * 16 + 8] += clock64() - e1;
         p.dbg_out[blockIdx.x * 16 + 15] = static_cast<long long>(global_timer_ns());   // last tile stored
@@ -863,7 +908,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, p.tmem_cols);
   }
-  if ((p.debug & 8) && threadIdx.x == 0) {   // the launch's timeline: entry and exit of this CTA
+  if ((dbg & 8) && threadIdx.x == 0) {   // the launch's timeline: entry and exit of this CTA
     p.dbg_out[blockIdx.x * 16 + 13] = static_cast<long long>(t_entry);
     p.dbg_out[blockIdx.x * 16 + 14] = static_cast<long long>(global_timer_ns());
   }

@@ -3,7 +3,8 @@
 #include "tc_gemm.cuh"
 
 namespace gk {
-const void* tc_kernel_generic() {
-  return reinterpret_cast<const void*>(&tc_gemm_kernel<1, 1, false, false, true>);
+const void* tc_kernel_generic(bool dbg) {
+  return dbg ? reinterpret_cast<const void*>(&tc_gemm_kernel<1, 1, false, false, true, true>)
+             : reinterpret_cast<const void*>(&tc_gemm_kernel<1, 1, false, false, true, false>);
 }
 }  // namespace gk

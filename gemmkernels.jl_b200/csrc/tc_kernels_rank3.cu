@@ -2,5 +2,5 @@
 #include "tc_kernels.cuh"
 
 namespace gk {
-template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32);
+template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32, bool dbg);
 }

@@ -1,4 +1,5 @@
 // Host side of the tcgen05 path: eligibility, tile choice, TMA tensor maps, launch.
+#include <cstdlib>
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -164,14 +165,15 @@ static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op,
 // The kernel instances are compiled in two translation units of their own (tc_kernels_rank3.cu,
 // tc_kernels_rank5.cu), which is what makes the build parallel.
 template <bool RANK5>
-const void* tc_kernel_select_r(int cg, int planes, bool tf32);
-extern template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32);
-extern template const void* tc_kernel_select_r<true>(int cg, int planes, bool tf32);
+const void* tc_kernel_select_r(int cg, int planes, bool tf32, bool dbg);
+extern template const void* tc_kernel_select_r<false>(int cg, int planes, bool tf32, bool dbg);
+extern template const void* tc_kernel_select_r<true>(int cg, int planes, bool tf32, bool dbg);
 
-const void* tc_kernel_generic();   // tc_kernels_generic.cu: <1, 1, false, false, GENERIC>
+const void* tc_kernel_generic(bool dbg);   // tc_kernels_generic.cu: <1, 1, false, false, GENERIC, dbg>
 
-static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5) {
-  return rank5 ? tc_kernel_select_r<true>(cg, planes, tf32) : tc_kernel_select_r<false>(cg, planes, tf32);
+// dbg: the instance that honours the descriptor's diagnostic bits (the production instance compiles them out)
+static const void* tc_kernel_select(int cg, int planes, bool tf32, bool rank5, bool dbg) {
+  return rank5 ? tc_kernel_select_r<true>(cg, planes, tf32, dbg) : tc_kernel_select_r<false>(cg, planes, tf32, dbg);
 }
 
 static constexpr int kSmemBudget = 232448;  // 227 KiB opt-in limit per CTA on sm_100
@@ -514,6 +516,10 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
            2 * boxes_per_kblock <= 32) ? 2 : 1;
   if (kps * boxes_per_kblock > 32) kps = 1;
   p.kps = kps;
+  {
+    static const int pf_env = [] { const char* e = getenv("GK_TC_PREFETCH"); return e ? atoi(e) : 0; }();
+    p.pf = pr.rank5 ? 0 : pf_env;
+  }
   const int stage_bytes = kps * kblock_bytes;
   int stages = (kSmemBudget - 1024 - kCtrlBytes) / stage_bytes;
   stages = std::min(stages, 8);
@@ -581,7 +587,8 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   // are still draining.  Asking for more than half of an SM's shared memory makes two tcgen05 CTAs on one
   // SM impossible, so two CTA pairs can never each hold one SM's tensor memory and wait for the other's.
   out->smem_bytes = std::max(out->smem_bytes, kSmemBudget / 2 + 2048);
-  out->kernel = pr.generic ? tc_kernel_generic() : tc_kernel_select(cg, planes, tf32, pr.rank5);
+  const bool dbg = pr.debug != 0;
+  out->kernel = pr.generic ? tc_kernel_generic(dbg) : tc_kernel_select(cg, planes, tf32, pr.rank5, dbg);
   if (pr.generic) {
     p.ga = pr.A.ptr; p.gb = pr.B.ptr;
     p.g_lda = pr.A.mn_major ? pr.A.k_str[0] : pr.A.mn_str[0];
@@ -596,7 +603,8 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   int slots;
   {
     std::lock_guard<std::mutex> lock(h->mu);
-    bool& set = pr.generic ? h->attr_set_generic : h->attr_set[cg - 1][planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
+    bool& set = pr.generic ? h->attr_set_generic[dbg ? 1 : 0]
+                           : h->attr_set[dbg ? 1 : 0][cg - 1][planes - 1][(tf32 ? 1 : 0) + (pr.rank5 ? 2 : 0)];
     if (!set) {
       GK_CUDA_CHECK(cudaFuncSetAttribute(out->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
       set = true;
