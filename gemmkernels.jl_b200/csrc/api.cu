@@ -93,7 +93,8 @@ static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, co
   if (d.m < kFpuBM || d.n < kFpuBN || d.k < kFpuBK) return false;
   if (d.m % kFpuBM || d.n % kFpuBN || d.k % kFpuBK) return false;
   if (d.m > INT32_MAX / 2 || d.n > INT32_MAX / 2 || d.k > INT32_MAX / 2) return false;
-  if (d.lda % 4 || d.ldb % 4 || d.ldd % 4) return false;
+  const int chunk = d.dtype_a == GK_F32 ? 4 : 8;   // elements per 16-byte copy
+  if (d.lda % chunk || d.ldb % chunk || d.ldd % 4) return false;
   auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
   if (misaligned(a) || misaligned(b) || misaligned(dd) || (has_c && misaligned(c))) return false;
   if (epi && epi->bias_axis != GK_BIAS_NONE && misaligned(epi->bias)) return false;
@@ -147,16 +148,29 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   const dim3 grid(blocks);
   const bool ak = d.trans_a != 0;   // stored K x M: K is the contiguous index of A
   const bool bk = d.trans_b == 0;   // stored K x N: K is the contiguous index of B
-  auto launch = [&](auto tag) {
-    using TIn = decltype(tag);
-    if (ak && bk) fpu_gemm_kernel<true, true, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
-    else if (ak && !bk) fpu_gemm_kernel<true, false, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
-    else if (!ak && bk) fpu_gemm_kernel<false, true, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
-    else fpu_gemm_kernel<false, false, TIn><<<grid, kFpuThreads, 0, stream>>>(p);
+  // The kernels ask for more dynamic shared memory than the default limit: raise it once per instance and device.
+  cudaError_t attr_err = cudaSuccess;
+  auto run = [&](auto kernel, int slot) {
+    bool& set = h->fpu_attr_set[slot];
+    if (!set) {
+      attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFpuSmemBytes);
+      if (attr_err != cudaSuccess) return;
+      set = true;
+    }
+    kernel<<<grid, kFpuThreads, kFpuSmemBytes, stream>>>(p);
   };
-  if (d.dtype_a == GK_F16) launch(__half{});
-  else if (d.dtype_a == GK_BF16) launch(__nv_bfloat16{});
-  else launch(float{});
+  auto launch = [&](auto tag, int type_slot) {
+    using TIn = decltype(tag);
+    const int slot = type_slot * 4 + (ak ? 2 : 0) + (bk ? 1 : 0);
+    if (ak && bk) run(fpu_gemm_kernel<true, true, TIn>, slot);
+    else if (ak && !bk) run(fpu_gemm_kernel<true, false, TIn>, slot);
+    else if (!ak && bk) run(fpu_gemm_kernel<false, true, TIn>, slot);
+    else run(fpu_gemm_kernel<false, false, TIn>, slot);
+  };
+  if (d.dtype_a == GK_F16) launch(__half{}, 1);
+  else if (d.dtype_a == GK_BF16) launch(__nv_bfloat16{}, 2);
+  else launch(float{}, 0);
+  GK_CUDA_CHECK(attr_err);
   GK_CUDA_CHECK(cudaGetLastError());
   if (p.split_q > 1) {
     const unsigned n_split = static_cast<unsigned>(p.tiles_m) * static_cast<unsigned>(p.tiles_n) - static_cast<unsigned>(p.split_first);
@@ -519,8 +533,8 @@ gk_status gk_gemm_query(gk_handle h, const gk_gemm_desc* desc, const gk_epilogue
     plan->kernel = 2;
     plan->grid = static_cast<int32_t>((desc->m / kFpuBM) * (desc->n / kFpuBN));
     plan->block = kFpuThreads; plan->cluster = 1;
-    plan->smem_bytes = 2 * 2 * kFpuBK * (kFpuBM + kFpuPad) * 4;
-    plan->tile_m = kFpuBM; plan->tile_n = kFpuBN; plan->tile_k = kFpuBK; plan->stages = 2;
+    plan->smem_bytes = kFpuSmemBytes;
+    plan->tile_m = kFpuBM; plan->tile_n = kFpuBN; plan->tile_k = kFpuBK; plan->stages = kFpuStages;
     if (desc->batch <= 1) plan->workspace_bytes = fpu_plan_split(h, *desc).bytes;   // optional: splits the last round's tiles along K
   } else {
     // same rule as launch_simt_typed: 128 x 128 tiles for 4-byte accumulators once there are 96 of them

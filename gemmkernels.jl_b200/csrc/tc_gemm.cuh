@@ -81,8 +81,6 @@ struct TcParams {
   int32_t kps;               // k-blocks per pipeline stage (1 or 2): one full/empty barrier round trip and one
                              // tcgen05.commit serve kps k-blocks, which halves the fixed cost per k-block
   int32_t stages;
-  int32_t pf;                // plain (3-D map) operands: k-blocks by which an L2 prefetch of the same box runs ahead of
-                             // its load (0: none).  Runs on into the CTA's next tile.
   int32_t a_mn_major, b_mn_major;
   int32_t a_boxes, b_boxes;  // TMA boxes per plane per CTA per k-block
   int32_t a_box_mn, b_box_mn;  // M/N elements per box of an MN-major operand (one swizzle span)
@@ -504,31 +502,8 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           const int kk0 = (kb0 + kj) * p.bk + k_add;
           k_in = kk0 % k_div; k_out = kk0 / k_div;
         }
-        // L2 prefetch: the same box `pf` k-blocks ahead, continuing into this CTA's next work unit, so that the
-        // loads proper find their lines in L2 instead of each waiting for HBM.
-        [[maybe_unused]] int mn_nx = 0, c2_nx = 0, kb0_nx = 0, kb1_nx = 0;
-        if constexpr (!RANK5) {
-          const int t2 = t + num_clusters;
-          if (p.pf > 0 && t2 < num_tiles) {
-            int tm2, tn2;
-            const int bt2 = t2 / units_per_product;
-            tc_tile_coords(p, (t2 - bt2 * units_per_product) / p.k_split, tm2, tn2);
-            kb0_nx = (t2 % p.k_split) * p.kb_per_split; kb1_nx = min(kb0_nx + p.kb_per_split, p.k_blocks);
-            c2_nx = pl + bt2 * (is_a ? p.a_batched : p.b_batched);
-            mn_nx = (is_a ? (tm2 * CG + static_cast<int>(rank)) * kTcTileM
-                          : tn2 * bn_tile + static_cast<int>(rank) * bn_cta) + mn_add;
-          }
-        }
         for (int kb = kb0; kb < kb1; kb += p.kps) {
           if (prof) pt0 = clock64();
-          if constexpr (!RANK5) {
-            if (p.pf > 0 && active) {
-              int kf = kb + kj + p.pf, mnf = mn, c2f = c2;
-              bool go = kf < kb1;
-              if (!go) { kf = kf - kb1 + kb0_nx; mnf = mn_nx; c2f = c2_nx; go = kf < kb1_nx; }
-              if (go) tma_prefetch_l2_3d(tmap, mn_major ? mnf : kf * p.bk, mn_major ? kf * p.bk : mnf, c2f);
-            }
-          }
           const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
           if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
           if (!__all_sync(0xffffffffu, got)) {

@@ -516,10 +516,6 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
            2 * boxes_per_kblock <= 32) ? 2 : 1;
   if (kps * boxes_per_kblock > 32) kps = 1;
   p.kps = kps;
-  {
-    static const int pf_env = [] { const char* e = getenv("GK_TC_PREFETCH"); return e ? atoi(e) : 0; }();
-    p.pf = pr.rank5 ? 0 : pf_env;
-  }
   const int stage_bytes = kps * kblock_bytes;
   int stages = (kSmemBudget - 1024 - kCtrlBytes) / stage_bytes;
   stages = std::min(stages, 8);
