@@ -101,8 +101,9 @@ static bool fpu_eligible(const gk_gemm_desc& d, const void* a, const void* b, co
   return true;
 }
 
-// Tail split of the FFMA kernel (fpu_gemm.cuh): how many parts the tiles of the last round are cut into
-// (1 = none), the first split tile, and the workspace the partial sums need.
+// K split of the FFMA kernel (fpu_gemm.cuh): how many parts the tiles of the last round - or, when the
+// whole grid is smaller than half a round, all tiles - are cut into (1 = none), the first split tile,
+// and the workspace the partial sums need.
 struct FpuSplit { int q = 1, first = 0; int64_t bytes = 0; };
 static FpuSplit fpu_plan_split(gk_handle h, const gk_gemm_desc& d) {
   FpuSplit sp;
@@ -110,6 +111,15 @@ static FpuSplit fpu_plan_split(gk_handle h, const gk_gemm_desc& d) {
   const int64_t slots = 2 * static_cast<int64_t>(h->sm_count);     // two CTAs per SM
   const int64_t rem = tiles % slots;
   const int64_t kt = d.k / kFpuBK;
+  if (2 * tiles <= slots) {
+    // Fewer tiles than half the slots: every tile is cut along K so that the grid fills the GPU.
+    int q = static_cast<int>(std::min<int64_t>(slots / tiles, 8));
+    while (q > 1 && kt / q < 8) --q;
+    if (q < 2) return sp;
+    sp.q = q; sp.first = 0;
+    sp.bytes = tiles * q * static_cast<int64_t>(kFpuBM) * kFpuBN * 4;
+    return sp;
+  }
   if (tiles <= slots || rem == 0 || 2 * rem > slots || kt < 64) return sp;   // one round, a full last round, or a short K
   int q = static_cast<int>(std::min<int64_t>(slots / rem, 4));
   while (q > 1 && kt / q < 16) --q;

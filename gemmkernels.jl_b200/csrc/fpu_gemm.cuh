@@ -235,18 +235,28 @@ __global__ void __launch_bounds__(kFpuThreads, 2) fpu_gemm_kernel(const FpuParam
       fpu_move_tile<A_KMAJOR, TIn>(As[cur ^ 1], ring_a + slot * kFpuStageBytes, p.alpha);
       fpu_move_tile<B_KMAJOR, TIn>(Bs[cur ^ 1], ring_b + slot * kFpuStageBytes, 1.0f);
     }
+    // Fragments of k-step k + 1 are loaded before the FMAs of k-step k are issued.
+    float4 fa[2][4], fb[2][2];
+#pragma unroll
+    for (int sm = 0; sm < 4; ++sm) fa[0][sm] = *reinterpret_cast<const float4*>(&As[cur][0][ma + 32 * sm]);
+    fb[0][0] = *reinterpret_cast<const float4*>(&Bs[cur][0][nb]);
+    fb[0][1] = *reinterpret_cast<const float4*>(&Bs[cur][0][nb + 16]);
 #pragma unroll
     for (int k = 0; k < kFpuBK; ++k) {
+      const int f = k & 1;
+      if (k + 1 < kFpuBK) {
+#pragma unroll
+        for (int sm = 0; sm < 4; ++sm) fa[f ^ 1][sm] = *reinterpret_cast<const float4*>(&As[cur][k + 1][ma + 32 * sm]);
+        fb[f ^ 1][0] = *reinterpret_cast<const float4*>(&Bs[cur][k + 1][nb]);
+        fb[f ^ 1][1] = *reinterpret_cast<const float4*>(&Bs[cur][k + 1][nb + 16]);
+      }
       float2 a[8];
 #pragma unroll
       for (int sm = 0; sm < 4; ++sm) {
-        const float4 v = *reinterpret_cast<const float4*>(&As[cur][k][ma + 32 * sm]);
-        a[2 * sm] = make_float2(v.x, v.y);
-        a[2 * sm + 1] = make_float2(v.z, v.w);
+        a[2 * sm] = make_float2(fa[f][sm].x, fa[f][sm].y);
+        a[2 * sm + 1] = make_float2(fa[f][sm].z, fa[f][sm].w);
       }
-      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[cur][k][nb]);
-      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[cur][k][nb + 16]);
-      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const float b[8] = {fb[f][0].x, fb[f][0].y, fb[f][0].z, fb[f][0].w, fb[f][1].x, fb[f][1].y, fb[f][1].z, fb[f][1].w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float2 bb = make_float2(b[j], b[j]);

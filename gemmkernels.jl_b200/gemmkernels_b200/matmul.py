@@ -242,11 +242,13 @@ def lower(conf: Config, a, b, c, d, hooks: dict, epilogue, kernel):
 
 def _wants_workspace(desc) -> bool:
     """Cases in which the library can use a workspace: interleaved complex / dual operands (split into
-    planes first), real tensor-core products with few output tiles and a long K (split-K), and large
-    FFMA products (the tiles of a partly filled last round are cut along K)."""
+    planes first), real tensor-core products with few output tiles and a long K (split-K), and FFMA
+    products (the tiles of a partly filled last round, or of a grid too small for the GPU, are cut along K)."""
     if desc.number != L.GK_REAL:
         return desc.plane_a == 0 or desc.plane_b == 0
     if desc.op == L.GK_OP_FPU and desc.dtype_d == L.GK_F32:
+        if desc.m * desc.n <= 148 * 128 * 128:                      # too few tiles to fill the GPU: all cut along K
+            return desc.k >= 256
         return desc.m * desc.n >= (1 << 22) and desc.k >= 1024      # the FFMA kernel's tail split
     return desc.m * desc.n <= (1 << 22) and desc.k >= 2048
 

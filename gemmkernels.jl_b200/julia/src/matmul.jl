@@ -145,7 +145,10 @@ function matmul(conf::Config, a, b, c, d;
                          has_bias ? reinterpret(CuPtr{Float32}, epilogue.bias_pointer) : CuPtr{Float32}(0), act, (0, 0, 0))
     # Interleaved complex / dual operands need a workspace (they are split into planes first); real products
     # with few output tiles and a long K can use one (split-K).  gk_gemm_query reports the size.
+    # The FFMA kernel cuts the tiles of a partly filled last round, or of a grid too small for the GPU, along K.
+    ffma = desc.op == 2 && desc.dtype_d == 2
     wants = Operator.number(conf.operator) != 0 ? (desc.plane_a == 0 || desc.plane_b == 0) :
+            ffma ? (desc.m * desc.n <= 148 * 128 * 128 ? desc.k >= 256 : (desc.m * desc.n >= 1 << 22 && desc.k >= 1024)) :
             (desc.m * desc.n <= 1 << 22 && desc.k >= 2048)
     if workspace === nothing && wants
         plan = Ref(GkGemmPlan(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0))

@@ -599,12 +599,15 @@ def test_strided_batched_products(ab, op, share_b):
     assert torch.all(d_store[:, M * N:] == 0)
 
 
+@pytest.mark.parametrize("shape,split_tiles,parts", [((2560, 2304, 1024), 64, 4), ((384, 512, 1056), 12, 8)])
 @pytest.mark.parametrize("ta,tb", [(0, 0), (1, 0), (1, 1)])
-def test_fpu_tail_split_matches_the_unsplit_product(ta, tb):
+def test_fpu_tail_split_matches_the_unsplit_product(ta, tb, shape, split_tiles, parts):
     """FFMA kernel, 360 tiles on 296 CTA slots: given a workspace, the 64 tiles of the last round are cut
     along K in four parts that run side by side and a second pass adds them and applies beta, bias and
-    ReLU.  Same numbers as the unsplit launch (small integers: exact), nothing written past the workspace."""
-    M, N, K = 2560, 2304, 1024
+    ReLU.  A grid of 12 tiles, too small for the GPU, has every tile cut in eight parts (66 k-tiles: the
+    last part is shorter).  Same numbers as the unsplit launch (small integers: exact), nothing written
+    past the workspace."""
+    M, N, K = shape
     rng = np.random.default_rng(31 + ta + 2 * tb)
     A = rng.integers(-2, 3, (K, M) if ta else (M, K)).astype(np.float32)
     B = rng.integers(-2, 3, (N, K) if tb else (K, N)).astype(np.float32)
@@ -619,7 +622,7 @@ def test_fpu_tail_split_matches_the_unsplit_product(ta, tb):
     kw = dict(epilogue=epi, transform_shared_to_global_d=Transform.Elementwise(Transform.ReLU()),
               transform_shared_to_regs_a=Transform.Elementwise(Transform.Scale(2.0)))
     plan = GK.query(conf, a, b, c, GK.cuarray(GK.Float32, M, N), **kw)
-    assert plan.kernel == 2 and plan.workspace_bytes == 64 * 4 * 128 * 128 * 4
+    assert plan.kernel == 2 and plan.workspace_bytes == split_tiles * parts * 128 * 128 * 4
     want = np.maximum(2.0 * ((A.T if ta else A) @ (B.T if tb else B)) + Cm + bias[None, :], 0)
     d_split = GK.cuarray(GK.Float32, M, N)
     ws = torch.zeros(plan.workspace_bytes + 4096, dtype=torch.uint8, device="cuda"); ws[plan.workspace_bytes:] = 0x5A
