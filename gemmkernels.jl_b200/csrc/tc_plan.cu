@@ -504,15 +504,16 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
 
   // Every pipeline stage costs the producer and MMA warps a fixed ≈250 ns (barrier waits, votes, loop
   // bookkeeping: measured with copies and MMAs switched off, the same for every tile shape), which a
-  // 128-column tile's four MMAs per k-block (≈130 ns) cannot cover.  Small tiles therefore put two
-  // k-blocks in a stage (1024^3: 10.7 -> 8.7 us); for tiles whose MMAs outlast the fixed cost it only
-  // makes the ring shallower (8192^3 with 256 x 256 tiles: 857 -> 898 us), so they keep one.
+  // 128-column tile's four MMAs per k-block (≈130 ns) cannot cover and a 256-column tile's (≈270 ns) only
+  // just.  Tiles up to 256 columns therefore put two k-blocks in a stage when three such stages fit
+  // (1024^3: 10.7 -> 8.7 us; 256 x 256 tiles at 8192^3: 874-906 -> 767-835 us in the tuner's sweep); a
+  // 256 x 512 tile's MMAs outlast the fixed cost and two k-blocks would leave it a ring of two stages.
   const int kblock_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
   const int boxes_per_kblock = planes * std::max(p.a_boxes * p.a_sub, n_sub * p.b_boxes * p.b_sub);
   const int mma_cycles_per_kblock = 2 * bn * n_sub * p.n_terms;
   int kps = pr.kps;
   if (kps == 0)
-    kps = (mma_cycles_per_kblock < 480 && (kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 &&
+    kps = (mma_cycles_per_kblock <= 512 && (kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 &&
            2 * boxes_per_kblock <= 32) ? 2 : 1;
   if (kps * boxes_per_kblock > 32) kps = 1;
   p.kps = kps;

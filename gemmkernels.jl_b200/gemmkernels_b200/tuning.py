@@ -350,9 +350,13 @@ def winners(results: dict, min_gain: float = 0.02) -> list[dict]:
 def emit_table(results_path, out_path) -> int:
     """Writes the winners of a results file as the initialiser list the library compiles in
     (csrc/tuned_table.inc).  Returns the number of entries."""
-    entries = winners(load_results(results_path))
+    results = load_results(results_path)
+    entries = winners(results)
+    n_ok = sum(1 for r in results.values() if r.get("category") == "success")
+    n_problems = len({pk for pk, _ in results})
     lines = ["// Generated by `python -m gemmkernels_b200.tuning --emit-table` from a sweep on B200: the fastest verified",
              "// candidate of each measured problem where it beat the planner's own choice by 2 % or more.",
+             f"// This sweep: {n_problems} problems, {n_ok} verified candidates, {len(entries)} entries.",
              "// {dtype, trans_a, trans_b, has_c, m, n, k, tile_n, cta_group, stages, raster_group, k_blocks_per_stage, 0}"]
     for e in entries:
         note = f"{e['time_us']:.1f} us" + (f" (planner {e['planner_time_us']:.1f} us)" if e["planner_time_us"] else "")
