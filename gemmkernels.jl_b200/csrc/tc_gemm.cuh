@@ -655,28 +655,34 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
           tc_fence_after_sync();
           if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, dbg, 4, 1);   // first stage landed
-          for (int kj = 0; kj < p.kps && kb + kj < kb1; ++kj) {   // the k-blocks of this stage that belong to the run
-            const uint32_t k16 = s16 + kj * kblock16;
+          // One divergent region per stage: the elected lane issues every MMA of the stage and the commit.
+          // (A branch around each MMA costs the warp ~40 cycles per site whether or not it issues anything,
+          // which is more than a 128 x 64 MMA takes to execute.)  Descriptors are sums of warp-uniform values.
+          if (elected) {
+            for (int kj = 0; kj < p.kps && kb + kj < kb1; ++kj) {   // the k-blocks of this stage that belong to the run
+              const uint32_t k16 = s16 + kj * kblock16;
 #pragma unroll
-            for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
+              for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
 #pragma unroll
-              for (int nb = 0; nb < 2; ++nb) {
-                if (nb < p.n_sub) {
+                for (int nb = 0; nb < 2; ++nb) {
+                  if (nb < p.n_sub) {
 #pragma unroll
-                  for (int ti = 0; ti < kMaxTerms; ++ti) {
-                    if (ti < n_terms) {
-                      const uint64_t da = smem_desc(k16 + off_a[ti][ks], hi_a);
-                      const uint64_t db = smem_desc(k16 + off_b[ti][nb][ks], hi_b);
-                      const uint32_t acc = (ks == 0 && first_kb) ? t_keep[ti] : 1u;
-                      if (elected) umma<CG, TF32>(d_base + d_off[ti][nb], da, db, t_id[ti], acc);
+                    for (int ti = 0; ti < kMaxTerms; ++ti) {
+                      if (ti < n_terms) {
+                        const uint64_t da = smem_desc(k16 + off_a[ti][ks], hi_a);
+                        const uint64_t db = smem_desc(k16 + off_b[ti][nb][ks], hi_b);
+                        const uint32_t acc = (ks == 0 && first_kb) ? t_keep[ti] : 1u;
+                        umma<CG, TF32>(d_base + d_off[ti][nb], da, db, t_id[ti], acc);
+                      }
                     }
                   }
                 }
               }
+              first_kb = false;
             }
-            first_kb = false;
+            umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
           }
-          if (elected) umma_commit<CG>(bar_empty + 8u * s);  // stage is free once these MMAs have read it
+          first_kb = false;
           if (kb == kb0 && acc_it == 0 && reporter) tc_mark(p.status, dbg, 4, 2);   // first MMAs issued
           ++s; s16 += stage16;
           if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }

@@ -93,38 +93,23 @@ static gk_status encode_plain(gk_handle h, CUtensorMap* tm, const TcOperand& op,
   return GK_OK;
 }
 
-// Two-mode operands (contractions) use 5-D tensor maps whose modes are listed by increasing stride
-// (the contiguous one first, unit modes and the plane last), with nested strides as the TMA unit
-// expects.  order[i] = which of (0 mn_in, 1 mn_out, 2 k_in, 3 k_out) sits at position i; *perm packs
-// the position of each of the four, 3 bits apiece.  False when the strides are not nested.
-static bool plan_modes(const TcOperand& op, int order[4], int32_t* perm) {
-  const int64_t ext[4] = {op.mn_ext[0], op.mn_ext[1], op.k_ext[0], op.k_ext[1]};
-  const int64_t str[4] = {op.mn_str[0], op.mn_str[1], op.k_str[0], op.k_str[1]};
-  const int first = op.mn_major ? 0 : 2;
-  int idx[4] = {0, 1, 2, 3};
-  std::stable_sort(idx, idx + 4, [&](int x, int y) {
-    if ((x == first) != (y == first)) return x == first;
-    const bool ux = ext[x] <= 1, uy = ext[y] <= 1;
-    if (ux != uy) return uy;
-    return str[x] < str[y];
-  });
-  int64_t covered = 1;
-  for (int i = 0; i < 4; ++i) {
-    const int m = idx[i];
-    if (i > 0 && ext[m] > 1 && str[m] < covered) return false;   // modes overlap in memory
-    if (ext[m] > 1 || i == 0) covered = str[m] * ext[m];
-    order[i] = m;
-  }
+// Two-mode operands (contractions) use 5-D tensor maps whose modes are listed in the order in which a box
+// is to lie in shared memory, not by stride (TMA adds coordinate x stride per mode; nothing asks for
+// nested or increasing strides):
+//   MN-major: mn_in (contiguous), k_in, k_out, mn_out  - spans of the contiguous mode, each with its K rows in order
+//   K-major : k_in (contiguous), mn_in, mn_out, k_out  - the tile's rows in order, 128 bytes of K each
+// and the plane last.  order[i] = which of (0 mn_in, 1 mn_out, 2 k_in, 3 k_out) sits at position i; *perm
+// packs the position of each of the four, 3 bits apiece.
+static void plan_modes(const TcOperand& op, int order[4], int32_t* perm) {
+  static const int mn_first[4] = {0, 2, 3, 1}, k_first[4] = {2, 0, 1, 3};
+  for (int i = 0; i < 4; ++i) order[i] = op.mn_major ? mn_first[i] : k_first[i];
   *perm = 0;
   for (int i = 0; i < 4; ++i) *perm |= i << (3 * order[i]);
-  return true;
 }
 
-// Each box is `box_contig` elements of the contiguous mode by `box_rows` of one other mode
-// (`row_mode`, numbered as above) and, when the outer mode of the same index follows it in memory
-// (`row_mode2`, `box_rows2` > 1), by that many steps of the outer mode too; every other mode has box 1.
-static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, int box_contig,
-                              int row_mode, int box_rows, int row_mode2, int box_rows2, CUtensorMapSwizzle swizzle) {
+// mode_box[m] = extent of a box along mode m (numbered as above); the plane has box 1.
+static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op, int planes, const int mode_box[4],
+                              CUtensorMapSwizzle swizzle) {
   const int es = dtype_size(op.dtype);
   CUtensorMapDataType tdt = op.dtype == GK_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                             : op.dtype == GK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -133,20 +118,18 @@ static gk_status encode_modes(gk_handle h, CUtensorMap* tm, const TcOperand& op,
   const int64_t str[4] = {op.mn_str[0], op.mn_str[1], op.k_str[0], op.k_str[1]};
   int order[4];
   int32_t perm;
-  if (!plan_modes(op, order, &perm))
-    return set_error(GK_ERR_INVALID_CONFIG, "tensor strides are not nested");
+  plan_modes(op, order, &perm);
   cuuint64_t dims[5], strides[4];
   cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
-  cuuint64_t covered = 0;   // bytes spanned by the modes so far: the stride given to unit modes
+  cuuint64_t covered = 16;   // bytes spanned by the modes: the stride given to unit modes (any multiple of 16 would do)
+  for (int m = 0; m < 4; ++m)
+    if (ext[m] > 1) covered = std::max<cuuint64_t>(covered, static_cast<cuuint64_t>(str[m]) * es * ext[m]);
+  covered = (covered + 15) / 16 * 16;
   for (int i = 0; i < 4; ++i) {
     const int m = order[i];
     dims[i] = static_cast<cuuint64_t>(ext[m]);
-    const cuuint64_t sbytes = (ext[m] > 1 || i == 0) ? static_cast<cuuint64_t>(str[m]) * es : covered;
-    if (i > 0) strides[i - 1] = sbytes;
-    covered = std::max<cuuint64_t>(covered, sbytes * dims[i]);
-    box[i] = i == 0 ? static_cast<cuuint32_t>(box_contig)
-                    : (m == row_mode ? static_cast<cuuint32_t>(box_rows)
-                                     : (m == row_mode2 && box_rows2 > 1 ? static_cast<cuuint32_t>(box_rows2) : 1u));
+    if (i > 0) strides[i - 1] = ext[m] > 1 ? static_cast<cuuint64_t>(str[m]) * es : covered;
+    box[i] = static_cast<cuuint32_t>(std::max(1, mode_box[m]));
   }
   dims[4] = static_cast<cuuint64_t>(planes);
   strides[3] = planes > 1 ? static_cast<cuuint64_t>(op.plane_stride) * es : covered;
@@ -422,48 +405,48 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
     p.b_boxes = 1; p.b_box_bytes = p.b_plane_bytes;
     p.b_lbo = 16; p.b_sbo = 1024; p.b_kadv = 32; p.b_swz = 2;
   }
-  if (planes * std::max(p.a_boxes, n_sub * p.b_boxes) > 32)
-    return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
   if (pr.kps < 0 || pr.kps > 2) return set_error(GK_ERR_INVALID_CONFIG, "k_blocks_per_stage must be 1 or 2 (0 = choose), got %d", pr.kps);
-  // Two-mode operands: a box covers one swizzle span of the contiguous mode and rows of ONE other
-  // mode; what a k-block (MN-major) or the tile's rows (K-major) need beyond that comes from
-  // `sub` boxes stepping through the outer mode.
-  int a_row_mode = 0, a_rows = 0, b_row_mode = 0, b_rows = 0, a_rows2 = 1, b_rows2 = 1;
+  // Two-mode operands.  The modes of a tensor map are listed in shared-memory order, so one box can walk
+  // both modes of an index: an MN-major box is one swizzle span of the contiguous mode by the k-block's rows
+  // (inner contracted mode, then steps of the outer one), and when the contiguous mode is exactly one span
+  // long the tile's spans - consecutive values of the outer M/N mode - join the same box, which then is the
+  // operand's whole k-block; a K-major box is 128 bytes of K by the tile's rows (inner M/N mode, then steps
+  // of the outer one).
+  int a_box[4] = {1, 1, 1, 1}, b_box[4] = {1, 1, 1, 1};
   p.a_sub = p.b_sub = 1;
+  p.a_sub_step = p.b_sub_step = 0; p.a_sub_bytes = p.b_sub_bytes = 0;
   if (pr.rank5) {
-    auto plan_sub = [&](const TcOperand& op, bool mn_major, int tile_rows, uint32_t row_bytes, int32_t* sub,
-                        int32_t* step, int32_t* sub_bytes, int* row_mode, int* rows, int* rows2) -> bool {
-      const int need = mn_major ? p.bk : tile_rows;       // rows of one chunk
+    auto plan_box = [&](const TcOperand& op, bool mn_major, int tile_rows, int box_mn, int32_t* boxes, int mode_box[4]) -> bool {
+      const int need = mn_major ? p.bk : tile_rows;       // rows of one box
       const int64_t* e = mn_major ? op.k_ext : op.mn_ext;
-      *row_mode = mn_major ? 2 : 0;
-      if (e[1] <= 1 || e[0] % need == 0) { *rows = need; *sub = 1; }
-      else if (need % e[0] == 0) { *rows = static_cast<int>(e[0]); *sub = need / *rows; }
+      int rows, rows2 = 1;
+      if (e[1] <= 1 || e[0] % need == 0) rows = need;
+      else if (need % e[0] == 0) { rows = static_cast<int>(e[0]); rows2 = need / rows; }
       else return false;
-      *step = *rows;
-      *sub_bytes = static_cast<int32_t>(*rows * row_bytes);
-      // The sub-boxes step through the outer mode of the same index.  When that mode also lies further
-      // out in memory, TMA writes a box that spans both modes in exactly the order the sub-boxes would
-      // have been placed in: one copy instead of `sub`.
-      const int64_t* st = mn_major ? op.k_str : op.mn_str;
-      *rows2 = 1;
-      if (*sub > 1 && *sub <= 256 && st[0] < st[1]) { *rows2 = *sub; *sub = 1; }
-      // K-major operands need whole 128-byte runs of their inner contracted mode
-      if (!mn_major && op.k_ext[1] > 1 && op.k_ext[0] % p.bk != 0) return false;
-      // MN-major operands: the chunk must be cut from the inner mode
-      if (mn_major && op.mn_ext[1] > 1 && op.mn_ext[0] % (mn_major ? (&op == &pr.A ? p.a_box_mn : p.b_box_mn) : 1) != 0) return false;
+      if (rows > 256 || rows2 > 256) return false;
+      if (mn_major) {
+        // the span must be cut from the inner mode
+        if (op.mn_ext[1] > 1 && op.mn_ext[0] % box_mn != 0) return false;
+        int spans = 1;
+        if (op.mn_ext[1] > 1 && op.mn_ext[0] == box_mn) { spans = *boxes; *boxes = 1; }
+        mode_box[0] = box_mn; mode_box[1] = spans; mode_box[2] = rows; mode_box[3] = rows2;
+      } else {
+        // K-major operands need whole 128-byte runs of their inner contracted mode
+        if (op.k_ext[1] > 1 && op.k_ext[0] % p.bk != 0) return false;
+        mode_box[0] = rows; mode_box[1] = rows2; mode_box[2] = p.bk; mode_box[3] = 1;
+      }
       return true;
     };
-    const uint32_t a_row_bytes = p.a_mn_major ? static_cast<uint32_t>(p.a_box_bytes / p.bk) : kTcKBytes;
-    const uint32_t b_row_bytes = p.b_mn_major ? static_cast<uint32_t>(p.b_box_bytes / p.bk) : kTcKBytes;
     int order[4];
-    const bool ok =
-        plan_sub(pr.A, p.a_mn_major != 0, kTcTileM, a_row_bytes, &p.a_sub, &p.a_sub_step, &p.a_sub_bytes, &a_row_mode, &a_rows, &a_rows2) &&
-        plan_sub(pr.B, p.b_mn_major != 0, bn_cta, b_row_bytes, &p.b_sub, &p.b_sub_step, &p.b_sub_bytes, &b_row_mode, &b_rows, &b_rows2) &&
-        plan_modes(pr.A, order, &p.a_perm) && plan_modes(pr.B, order, &p.b_perm) &&
-        planes * p.a_boxes * p.a_sub <= 32 && planes * p.b_boxes * p.b_sub <= 32;
+    const bool ok = plan_box(pr.A, p.a_mn_major != 0, kTcTileM, p.a_box_mn, &p.a_boxes, a_box) &&
+                    plan_box(pr.B, p.b_mn_major != 0, bn_cta, p.b_box_mn, &p.b_boxes, b_box);
     if (!ok)
       return set_error(GK_ERR_INVALID_CONFIG, "tensor modes do not tile into TMA boxes (extents or strides)");
+    plan_modes(pr.A, order, &p.a_perm);
+    plan_modes(pr.B, order, &p.b_perm);
   }
+  if (planes * std::max(p.a_boxes, n_sub * p.b_boxes) > 32)
+    return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
   p.a_mn_div = clamp_div(pr.A.mn_ext[0], pr.A.mn_ext[1]);
   p.a_k_div = clamp_div(pr.A.k_ext[0], pr.A.k_ext[1]);
   p.b_mn_div = clamp_div(pr.B.mn_ext[0], pr.B.mn_ext[1]);
@@ -633,9 +616,9 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   if (encode && !pr.generic) {
     gk_status s;
     if (pr.rank5) {
-      s = encode_modes(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, a_row_mode, a_rows, a_row_mode + 1, a_rows2, a_tma);
+      s = encode_modes(h, &p.tm_a, pr.A, planes, a_box, a_tma);
       if (s != GK_OK) return s;
-      s = encode_modes(h, &p.tm_b, pr.B, planes, p.b_mn_major ? p.b_box_mn : p.bk, b_row_mode, b_rows, b_row_mode + 1, b_rows2, b_tma);
+      s = encode_modes(h, &p.tm_b, pr.B, planes, b_box, b_tma);
     } else {
       s = encode_plain(h, &p.tm_a, pr.A, planes, p.a_mn_major ? p.a_box_mn : p.bk, p.a_mn_major ? p.bk : kTcTileM, a_tma,
                        pr.batch, pr.batch_a);
