@@ -318,6 +318,28 @@ __device__ __forceinline__ void tc_fill_box_generic(uint8_t* dst, const uint16_t
   }
 }
 
+// All MMAs of one k-block as straight-line code: NSUB column blocks x NTERMS terms x the K steps of a
+// k-block, no branch between them (a single warp pays 10-20 cycles for every branch it resolves, taken or
+// not, and eight of them per k-block were more than the MMAs of a small tile).  `lo` is the k-block's base
+// in descriptor units; the tables hold the offsets of each operand slice relative to it.
+template <int CG, bool TF32, int KMAX, int NSUB, int NTERMS>
+__device__ __forceinline__ void tc_issue_kblock(uint32_t lo, bool first, uint32_t d_base, uint32_t hi_a, uint32_t hi_b,
+                                                const uint32_t (&off_a)[KMAX][kTcMmaPerKBlock],
+                                                const uint32_t (&off_b)[KMAX][2][kTcMmaPerKBlock],
+                                                const uint32_t (&d_off)[KMAX][2], const uint32_t (&t_id)[KMAX],
+                                                const uint32_t (&t_keep)[KMAX]) {
+#pragma unroll
+  for (int ks = 0; ks < kTcMmaPerKBlock; ++ks)
+#pragma unroll
+    for (int nb = 0; nb < NSUB; ++nb)
+#pragma unroll
+      for (int ti = 0; ti < NTERMS; ++ti) {
+        const uint32_t acc = (ks == 0 && first) ? t_keep[ti] : 1u;
+        umma<CG, TF32>(d_base + d_off[ti][nb], smem_desc(lo + off_a[ti][ks], hi_a), smem_desc(lo + off_b[ti][nb][ks], hi_b),
+                       t_id[ti], acc);
+      }
+}
+
 // DBG selects the instance that honours TcParams::debug (measurement and test aids); in the production
 // instance every such branch is compiled out, which shortens the per-stage loops of the producer and
 // MMA warps (their cost per pipeline stage is instruction latency, not bandwidth).
@@ -661,22 +683,15 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           if (elected) {
             for (int kj = 0; kj < p.kps && kb + kj < kb1; ++kj) {   // the k-blocks of this stage that belong to the run
               const uint32_t k16 = s16 + kj * kblock16;
-#pragma unroll
-              for (int ks = 0; ks < kTcMmaPerKBlock; ++ks) {
-#pragma unroll
-                for (int nb = 0; nb < 2; ++nb) {
-                  if (nb < p.n_sub) {
-#pragma unroll
-                    for (int ti = 0; ti < kMaxTerms; ++ti) {
-                      if (ti < n_terms) {
-                        const uint64_t da = smem_desc(k16 + off_a[ti][ks], hi_a);
-                        const uint64_t db = smem_desc(k16 + off_b[ti][nb][ks], hi_b);
-                        const uint32_t acc = (ks == 0 && first_kb) ? t_keep[ti] : 1u;
-                        umma<CG, TF32>(d_base + d_off[ti][nb], da, db, t_id[ti], acc);
-                      }
-                    }
-                  }
+              if constexpr (PLANES == 1) {
+                if (n_terms != 0) {
+                  if (p.n_sub == 2) tc_issue_kblock<CG, TF32, kMaxTerms, 2, 1>(k16, first_kb, d_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+                  else tc_issue_kblock<CG, TF32, kMaxTerms, 1, 1>(k16, first_kb, d_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
                 }
+              } else {
+                // two planes: one column block; four terms (complex) or three (dual)
+                if (n_terms == 4) tc_issue_kblock<CG, TF32, kMaxTerms, 1, 4>(k16, first_kb, d_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+                else if (n_terms == 3) tc_issue_kblock<CG, TF32, kMaxTerms, 1, 3>(k16, first_kb, d_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
               }
               first_kb = false;
             }
