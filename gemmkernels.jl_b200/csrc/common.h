@@ -85,6 +85,7 @@ struct gk_handle_s {
   bool attr_set[2][2][2][4] = {};  // tc kernel [debug instance][cg-1][planes-1][tf32 + 2*rank5]: smem attribute set
   bool attr_set_generic[2] = {};   // the same for the generic-load instances
   bool fpu_attr_set[12] = {};      // FFMA kernel instances (3 operand types x 4 transposes): shared-memory limit raised
+  bool f64_attr_set[4] = {};       // FP64 kernel instances (4 transposes): shared-memory limit raised
   // staging buffers of gk_gemm_host (grown on demand, freed by gk_destroy)
   void* stage_dev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, D, bias
   size_t stage_bytes[5] = {0, 0, 0, 0, 0};

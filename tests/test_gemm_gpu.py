@@ -637,6 +637,39 @@ def test_fpu_tail_split_matches_the_unsplit_product(ta, tb, shape, split_tiles, 
     assert torch.equal(d_plain, d_split)
 
 
+@pytest.mark.parametrize("ta,tb", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_fp64_fast_path_matches_float64_numpy(ta, tb):
+    """Float64 FPU operator on tile-multiple, aligned shapes: the FP64 kernel (family 2 in the plan), all four
+    transposes, alpha, beta, per-column bias and ReLU fused.  Small integers make the sums exact; a second
+    product with random operands is held to 1e-12 normwise against numpy's float64 product."""
+    M, N, K = 1536, 1280, 224          # 120 tiles: the fast path wants three quarters of a round
+    rng = np.random.default_rng(41 + ta + 2 * tb)
+    la = (Layout.UnsafeAlignedRowMajor if ta else Layout.UnsafeAlignedColMajor)[GK.Float64]
+    lb = (Layout.UnsafeAlignedRowMajor if tb else Layout.UnsafeAlignedColMajor)[GK.Float64]
+    op = Operator.FPUOp[8, 8, 1, 4, 8, 1, GK.Float64, GK.Float64]
+    for exact in (True, False):
+        if exact:
+            A = rng.integers(-3, 4, (K, M) if ta else (M, K)).astype(np.float64)
+            B = rng.integers(-3, 4, (N, K) if tb else (K, N)).astype(np.float64)
+            Cm = rng.integers(-5, 6, (M, N)).astype(np.float64); bias = rng.integers(-3, 4, N).astype(np.float32)
+        else:
+            A = rng.standard_normal((K, M) if ta else (M, K)); B = rng.standard_normal((N, K) if tb else (K, N))
+            Cm = rng.standard_normal((M, N)); bias = rng.standard_normal(N).astype(np.float32)
+        a, b, c, d = dev(A), dev(B), dev(Cm), GK.cuarray(GK.Float64, M, N)
+        conf = run_matmul(a, b, c, d, M=M, N=N, K=K, op=op, la=la, lb=lb, lc=Layout.UnsafeAlignedColMajor[GK.Float64],
+                          ld=Layout.UnsafeAlignedColMajor[GK.Float64], alpha=2.0, beta=3.0,
+                          epilogue=Epilogue.Bias(dev(bias), axis="col"), act=Transform.ReLU(), block_shape=(128, 128, 32))
+        plan = GK.query(conf, a, b, c, d, epilogue=Epilogue.Bias(dev(bias), axis="col"),
+                        transform_shared_to_global_d=Transform.Elementwise(Transform.ReLU()))
+        assert plan.kernel == 2 and plan.tile_m == 128 and plan.block == 256
+        want = np.maximum(2.0 * ((A.T if ta else A) @ (B.T if tb else B)) + 3.0 * Cm + bias[None, :].astype(np.float64), 0)
+        got = GK.to_numpy(d)
+        if exact:
+            assert np.array_equal(got, want)
+        else:
+            assert O.normwise_error(got, want) <= 1e-12
+
+
 def test_chained_products_without_host_synchronisation():
     """Y = (A*B)*C with the first product's Float16 output feeding the second, ten chains enqueued back to back:
     the second kernel may start its set-up while the first is still running (programmatic dependent launch) but
