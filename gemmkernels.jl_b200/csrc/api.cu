@@ -142,6 +142,7 @@ static gk_status launch_f64(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   const bool bk = d.trans_b == 0;   // stored K x N: K is the contiguous index of B
   cudaError_t attr_err = cudaSuccess;
   auto run = [&](auto kernel, int slot) {
+    std::lock_guard<std::mutex> lock(h->mu);
     bool& set = h->f64_attr_set[slot];
     if (!set) {
       attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF64SmemBytes);
@@ -219,6 +220,7 @@ static gk_status launch_fpu(gk_handle h, const gk_gemm_desc& d, const gk_epilogu
   // The kernels ask for more dynamic shared memory than the default limit: raise it once per instance and device.
   cudaError_t attr_err = cudaSuccess;
   auto run = [&](auto kernel, int slot) {
+    std::lock_guard<std::mutex> lock(h->mu);
     bool& set = h->fpu_attr_set[slot];
     if (!set) {
       attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFpuSmemBytes);
