@@ -491,18 +491,19 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   p.idesc = idesc;
   p.idesc_neg = idesc | (1u << 13);                   // negate A
 
-  // Every pipeline stage costs the producer and MMA warps a fixed ≈250 ns (barrier waits, votes, loop
-  // bookkeeping: measured with copies and MMAs switched off, the same for every tile shape), which a
-  // 128-column tile's four MMAs per k-block (≈130 ns) cannot cover and a 256-column tile's (≈270 ns) only
-  // just.  Tiles up to 256 columns therefore put two k-blocks in a stage when three such stages fit
-  // (1024^3: 10.7 -> 8.7 us; 256 x 256 tiles at 8192^3: 874-906 -> 767-835 us in the tuner's sweep); a
-  // 256 x 512 tile's MMAs outlast the fixed cost and two k-blocks would leave it a ring of two stages.
+  // Every pipeline stage costs the producer and MMA warps a fixed amount of barrier waits, votes and loop
+  // bookkeeping (a few hundred cycles), which the MMAs of a narrow tile's k-block do not cover: a 128-column
+  // tile's four take ≈130 ns.  Tiles up to 128 columns therefore put two k-blocks in a stage (1024^3: 10.7 ->
+  // 8.7 us).  For 256-column tiles it was worth 8-12 % while the MMA warp still branched around every MMA;
+  // since that loop became straight-line code the deeper ring of single k-blocks is 1-2 % ahead again
+  // (2048^3: 17.2 against 17.5 us, 8192 x 4096 x 8192: 369 against 375 us), and a 256 x 512 tile's MMAs
+  // outlast the fixed cost by far.
   const int kblock_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
   const int boxes_per_kblock = planes * std::max(p.a_boxes * p.a_sub, n_sub * p.b_boxes * p.b_sub);
   const int mma_cycles_per_kblock = 2 * bn * n_sub * p.n_terms;
   int kps = pr.kps;
   if (kps == 0)
-    kps = (mma_cycles_per_kblock <= 512 && (kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 &&
+    kps = (mma_cycles_per_kblock < 512 && (kSmemBudget - 1024 - kCtrlBytes) / (2 * kblock_bytes) >= 3 && p.k_blocks >= 8 &&
            2 * boxes_per_kblock <= 32) ? 2 : 1;
   if (kps * boxes_per_kblock > 32) kps = 1;
   p.kps = kps;

@@ -393,6 +393,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Sweep the tcgen05 GEMM's tile parameters on this GPU.")
     ap.add_argument("--out", default="tuning_results.jsonl")
     ap.add_argument("--sizes", type=int, nargs="*", default=[2048, 4096, 8192])
+    ap.add_argument("--shapes", nargs="*", default=[], metavar="MxNxK",
+                    help="rectangular problems on top of --sizes, e.g. 8192x1024x8192 (a rank's column block)")
     ap.add_argument("--dtype", default="Float16", choices=sorted(_ELTYPES))
     ap.add_argument("--layouts", nargs="*", default=["NN", "NT", "TN", "TT"])
     ap.add_argument("--with-c", action="store_true", help="tune D = A*B + C instead of D = A*B")
@@ -402,7 +404,10 @@ def main(argv=None) -> int:
     if args.emit_table:
         print(f"{emit_table(args.out, args.emit_table)} entries written to {args.emit_table}")
         return 0
-    probs = [Problem(n, n, n, l[0] == "T", l[1] == "T", args.dtype, args.with_c) for n in args.sizes for l in args.layouts]
+    shapes = [(n, n, n) for n in args.sizes] + [tuple(int(x) for x in t.lower().split("x")) for t in args.shapes]
+    if any(len(t) != 3 or min(t) < 1 for t in shapes):
+        ap.error("--shapes wants MxNxK with positive extents")
+    probs = [Problem(m, n, k, l[0] == "T", l[1] == "T", args.dtype, args.with_c) for m, n, k in shapes for l in args.layouts]
     fn = (lambda p: candidates(p, tile_n=(64, 128, 256, 512), stages=(0,), raster_group=(0,))) if args.quick else candidates
     tune(probs, args.out, candidate_fn=fn)
     return 0
