@@ -187,7 +187,7 @@ static void choose_tile(const TcProblem& pr, int sm_count, int planes, int* cg_o
   if (pr.rank5 && pr.B.mn_major && pr.B.mn_ext[1] > 1 && pr.B.mn_ext[0] < n_unit) n_unit = static_cast<int>(pr.B.mn_ext[0]);
   struct Cand { int cg, bn, n_sub; double eff; };
   static const Cand cands[] = {{2, 256, 2, kWideEff}, {2, 256, 1, 1.00}, {1, 256, 1, 0.92}, {2, 128, 1, 0.80},
-                               {1, 128, 1, 0.74},     {1, 64, 1, 0.50},  {1, 32, 1, 0.30}};
+                               {1, 128, 1, 0.74},     {1, 64, 1, 0.50},  {1, 32, 1, 0.24}};   // 32 columns: only when it saves a round (512x512x2048: 11.9 us against 9.5 with 64)
   double best = 1e300;
   int bcg = 1, bbn = 128, bns = 1;
   for (const Cand& c : cands) {
@@ -679,6 +679,15 @@ gk_status tc_launch(const TcLaunch& L, cudaStream_t stream) {
 // (small tiles were chosen to fill the SMs in one round, which a long K makes slow: every tile then
 // streams all of K with little operand reuse).  Returns the number of runs (1 = no split) and may
 // replace *pr's tile choice.
+// Does cutting K pay?  Measured with bound launches (512^2, 1024^2, 256^2, 2048 x 1024 outputs, K = 2048 .. 16384):
+// an unsplit product of few tiles costs ≈0.18 us per k-block; split, ≈40 % of that, plus a second kernel and the
+// partial planes' trip through memory: ≈6 us + 0.19 us per MB of partial sums.
+static bool split_pays(const TcProblem& pr, int k_blocks, int splits, int planes) {
+  const double saved_us = 0.11 * k_blocks;
+  const double cost_us = 6.0 + 0.19 * (static_cast<double>(splits) * planes * pr.M * pr.N * 4.0 / 1.0e6);
+  return saved_us > cost_us;
+}
+
 static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
   if (pr->tile_n == 0 && pr->cta_group == 0) {
     TcProblem alt = *pr;
@@ -688,12 +697,14 @@ static int plan_k_split(gk_handle h, TcProblem* pr, const TcLaunch& L) {
       // worth it only for a long K (32 k-blocks or more): below that the second pass costs more than the
       // large tiles save (measured: the 1024^3 contraction took 25 us this way against 13 us unsplit)
       const int splits = La.params.k_blocks >= 32 ? tc_choose_k_split(alt, La, h->sm_count) : 1;
-      if (splits > 1) { pr->tile_n = alt.tile_n; pr->cta_group = 2; return splits; }
+      if (splits > 1 && split_pays(*pr, La.params.k_blocks, splits, La.planes)) { pr->tile_n = alt.tile_n; pr->cta_group = 2; return splits; }
+      if (splits > 1) return 1;
     } else {
       clear_error();
     }
   }
-  return tc_choose_k_split(*pr, L, h->sm_count);
+  const int splits = tc_choose_k_split(*pr, L, h->sm_count);
+  return splits > 1 && split_pays(*pr, L.params.k_blocks, splits, L.planes) ? splits : 1;
 }
 
 int64_t tc_split_workspace_bytes(gk_handle h, const TcProblem& pr, const TcLaunch& L) {
