@@ -467,21 +467,31 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   }
   if (!GENERIC && (warp == 0 || warp == 3)) {
     // ------------------------------------------------------------------ TMA producers
-    // Warp 0 loads A, warp 3 loads B: issuing a copy costs its thread on the order of 100
-    // cycles, and splitting the operands keeps each producer loop well under one k-block of MMA.
-    // One lane per TMA box: every lane runs the same short instruction stream with its own
-    // destination and coordinates, so the cost per k-block does not grow with the box count.
-    // (Measured on B200: issuing from one elected lane of a converged warp with warp-uniform
-    // operands cost ~3x more cycles per copy than this form.)
+    // Both warps load both operands, for alternate pipeline stages (warp 0 the even ones, warp 3 the odd
+    // ones).  Filling a stage costs its warp a few hundred cycles whatever the stage holds - the wait for
+    // the slot, the vote, the divergent region that issues the copies - so two warps on alternate stages
+    // have twice the time per stage that one warp per operand had (worth 1 % on 256 x 256 tiles at 8192^3,
+    // whose main loop is otherwise bound by the L2 -> shared memory rate: with the MMAs switched off it
+    // still takes 606 us).  One lane per TMA box, A's boxes on the first lanes and B's behind them: every
+    // lane runs the same short instruction stream with its own destination and coordinates, so the cost
+    // per stage does not grow with the box count.  (Measured on B200: issuing from one elected lane of a
+    // converged warp with warp-uniform operands cost ~3x more cycles per copy.)
     {
-      const bool is_a = warp == 0;
-      const int subs = RANK5 ? (is_a ? p.a_sub : p.b_sub) : 1;
+      const uint32_t which = warp == 0 ? 0u : 1u;
+      const int a_subs = RANK5 ? p.a_sub : 1, b_subs = RANK5 ? p.b_sub : 1;
+      const int a_per_block = p.a_planes * p.a_boxes * a_subs;             // A boxes of one k-block
+      const int b_per_block = p.b_planes * p.b_boxes * b_subs;             // B boxes of one column block and k-block
+      const int a_pieces = a_per_block * p.kps;                            // A boxes of one stage
+      const int b_pieces = p.n_sub * b_per_block * p.kps;
+      const bool is_a = lane < a_pieces;
+      const bool active = lane < a_pieces + b_pieces;
+      const int piece = active ? (is_a ? lane : lane - a_pieces) : 0;
+      const int subs = is_a ? a_subs : b_subs;
       const int per_plane = (is_a ? p.a_boxes : p.b_boxes) * subs;
-      const int per_block = (is_a ? p.a_planes : p.b_planes) * per_plane;   // boxes of one column block
+      const int per_block = is_a ? a_per_block : b_per_block;
       const int n_boxes = (is_a ? 1 : p.n_sub) * per_block;    // boxes of one k-block
-      const bool active = lane < n_boxes * p.kps;
-      const int kj = active ? lane / n_boxes : 0;              // which k-block of the stage
-      const int bl = active ? lane % n_boxes : 0;              // which box of that k-block
+      const int kj = piece / n_boxes;                          // which k-block of the stage
+      const int bl = piece % n_boxes;                          // which box of that k-block
       const int nb = bl / per_block;                           // which column block (B only)
       const int pl = (bl % per_block) / per_plane;
       const int bx = (bl % per_plane) / subs;                  // which swizzle-span chunk
@@ -502,7 +512,9 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const uint32_t tx_bytes = stage_bytes * CG;
       int s = 0;
       uint32_t ph = 0;
-      uint32_t issued = 0;  // k-blocks issued so far by this CTA
+      uint32_t it = 0;        // pipeline stages passed so far (both warps count all of them)
+      uint32_t armed = 0;     // stages this warp has armed
+      uint32_t last_it = 0;   // the last of them
       bool ok = true;
       const bool prof = (dbg & 8) != 0;
       long long pw = 0, pi = 0, pt0 = 0, pt1 = 0;
@@ -524,24 +536,23 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           const int kk0 = (kb0 + kj) * p.bk + k_add;
           k_in = kk0 % k_div; k_out = kk0 / k_div;
         }
-        for (int kb = kb0; kb < kb1; kb += p.kps) {
-          if (prof) pt0 = clock64();
-          const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
-          if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
-          if (!__all_sync(0xffffffffu, got)) {
-            if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
-            ok = false;
-            break;
-          }
-          if (issued == 0 && lane == 0) tc_mark(p.status, dbg, is_a ? 2 : 3, 1);   // about to issue first copies
-          if (dbg & 1) {
-            if (lane == 0 && leader && is_a) mbar_arrive(bar_full + 8u * s);
-          } else {
-            // Bytes may be counted on the barrier before they are expected: the phase cannot
-            // complete until the A producer's arrival below.
-            if (lane == 0 && leader && is_a) mbar_arrive_expect_tx(bar_full + 8u * s, tx_bytes);
-            __syncwarp();
-            if (active) {
+        for (int kb = kb0; kb < kb1; kb += p.kps, ++it) {
+          if ((it & 1u) == which) {
+            if (prof) pt0 = clock64();
+            const bool got = mbar_wait(bar_empty + 8u * s, ph ^ 1u, abort_flag, kTcWaitLimitNs);
+            if (prof) { pt1 = clock64(); pw += pt1 - pt0; }
+            if (!__all_sync(0xffffffffu, got)) {
+              if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_PRODUCER);
+              ok = false;
+              break;
+            }
+            if (armed == 0 && lane == 0) tc_mark(p.status, dbg, 2 + which, 1);   // about to issue first copies
+            if (dbg & 1) {
+              if (lane == 0 && leader) mbar_arrive(bar_full + 8u * s);
+            } else if (active) {
+              // Bytes may be counted on the barrier before they are expected: the phase cannot
+              // complete until the arrival that announces them.
+              if (lane == 0 && leader) mbar_arrive_expect_tx(bar_full + 8u * s, tx_bytes);
               const int k0 = (kb + kj) * p.bk;     // a k-block past the end of K (or of this K-run) is loaded too:
                                                    // zeros, or operands the MMA issuer does not use
               const uint32_t dst = smem_base + s * stage_bytes + dst_off;
@@ -564,28 +575,27 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
                 else tma_load_3d(dst, tmap, full0_signal + 8u * s, c0, c1, c2);
               }
             }
+            if (armed == 0 && lane == 0) tc_mark(p.status, dbg, 2 + which, 2);   // first copies issued
+            ++armed; last_it = it;
+            if (prof) pi += clock64() - pt1;
           }
-          if (issued == 0 && lane == 0) tc_mark(p.status, dbg, is_a ? 2 : 3, 2);   // first copies issued
           if constexpr (RANK5) {
             k_in += p.kps * p.bk;
             while (k_in >= k_div) { k_in -= k_div; ++k_out; }
           }
-          ++issued;
           if (++s == p.stages) { s = 0; ph ^= 1u; }
-          if (prof) pi += clock64() - pt1;
         }
       }
       if (prof && lane == 0) {
-        p.dbg_out[blockIdx.x * 16 + (is_a ? 0 : 9)] = pw;
-        p.dbg_out[blockIdx.x * 16 + (is_a ? 1 : 10)] = pi;
+        p.dbg_out[blockIdx.x * 16 + (which == 0 ? 0 : 9)] = pw;
+        p.dbg_out[blockIdx.x * 16 + (which == 0 ? 1 : 10)] = pi;
       }
       if (!ok && lane == 0) {
         if (leader) {
           // Let this CTA's copies in flight land before shared memory is given back: the full
-          // barrier of every stage that was armed completes when its bytes arrive.
-          const uint32_t n_back = issued < static_cast<uint32_t>(p.stages) ? issued : p.stages;
-          for (uint32_t b = 0; b < n_back; ++b) {
-            const uint32_t idx = issued - 1 - b;
+          // barrier of every stage this warp armed completes when its bytes arrive.
+          uint32_t idx = last_it;
+          for (uint32_t b = 0; b < armed && 2 * b < static_cast<uint32_t>(p.stages) + 1; ++b, idx -= 2) {
             const uint32_t st = idx % p.stages;
             const uint32_t par = (idx / p.stages) & 1u;
             const uint64_t t0 = global_timer_ns();

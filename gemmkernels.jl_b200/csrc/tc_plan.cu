@@ -451,7 +451,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
     plan_modes(pr.A, order, &p.a_perm);
     plan_modes(pr.B, order, &p.b_perm);
   }
-  if (planes * std::max(p.a_boxes, n_sub * p.b_boxes) > 32)
+  if (planes * (p.a_boxes * p.a_sub + n_sub * p.b_boxes * p.b_sub) > 32)
     return set_error(GK_ERR_INVALID_CONFIG, "too many TMA boxes per k-block for one producer warp");
   p.a_mn_div = clamp_div(pr.A.mn_ext[0], pr.A.mn_ext[1]);
   p.a_k_div = clamp_div(pr.A.k_ext[0], pr.A.k_ext[1]);
@@ -499,7 +499,7 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   // (2048^3: 17.2 against 17.5 us, 8192 x 4096 x 8192: 369 against 375 us), and a 256 x 512 tile's MMAs
   // outlast the fixed cost by far.
   const int kblock_bytes = stage_bytes_for(cg, bn, n_sub, planes, planes);
-  const int boxes_per_kblock = planes * std::max(p.a_boxes * p.a_sub, n_sub * p.b_boxes * p.b_sub);
+  const int boxes_per_kblock = planes * (p.a_boxes * p.a_sub + n_sub * p.b_boxes * p.b_sub);   // one lane each in a producer warp
   const int mma_cycles_per_kblock = 2 * bn * n_sub * p.n_terms;
   int kps = pr.kps;
   if (kps == 0)
