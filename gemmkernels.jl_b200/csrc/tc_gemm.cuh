@@ -77,6 +77,9 @@ struct TcParams {
   int32_t bn;                // columns per MMA (multiple of 32; per-CTA B rows = bn/CG)
   int32_t n_sub;             // a cluster tile is n_sub (1 or 2) such column blocks that share A
   int32_t acc_stages;        // accumulator stages in TMEM: 2, or 1 when one tile fills all 512 columns
+  int32_t skew;              // 1: a 512-column tile's two column blocks finish (and start) half a ring apart, each
+                             // with its own full / empty barrier, so the epilogue of block 0 overlaps the last
+                             // MMAs of block 1 and the first MMAs of the next tile overlap the epilogue of block 1
   int32_t bk;                // K elements per k-block (128 bytes)
   int32_t kps;               // k-blocks per pipeline stage (1 or 2): one full/empty barrier round trip and one
                              // tcgen05.commit serve kps k-blocks, which halves the fixed cost per k-block
@@ -321,8 +324,9 @@ __device__ __forceinline__ void tc_fill_box_generic(uint8_t* dst, const uint16_t
 // All MMAs of one k-block as straight-line code: NSUB column blocks x NTERMS terms x the K steps of a
 // k-block, no branch between them (a single warp pays 10-20 cycles for every branch it resolves, taken or
 // not, and eight of them per k-block were more than the MMAs of a small tile).  `lo` is the k-block's base
-// in descriptor units; the tables hold the offsets of each operand slice relative to it.
-template <int CG, bool TF32, int KMAX, int NSUB, int NTERMS>
+// in descriptor units; the tables hold the offsets of each operand slice relative to it.  NB0 is the first
+// column block (the skewed schedule of 512-column tiles issues the two blocks of a k-block apart).
+template <int CG, bool TF32, int KMAX, int NSUB, int NTERMS, int NB0 = 0>
 __device__ __forceinline__ void tc_issue_kblock(uint32_t lo, bool first, uint32_t d_base, uint32_t hi_a, uint32_t hi_b,
                                                 const uint32_t (&off_a)[KMAX][kTcMmaPerKBlock],
                                                 const uint32_t (&off_b)[KMAX][2][kTcMmaPerKBlock],
@@ -331,7 +335,7 @@ __device__ __forceinline__ void tc_issue_kblock(uint32_t lo, bool first, uint32_
 #pragma unroll
   for (int ks = 0; ks < kTcMmaPerKBlock; ++ks)
 #pragma unroll
-    for (int nb = 0; nb < NSUB; ++nb)
+    for (int nb = NB0; nb < NB0 + NSUB; ++nb)
 #pragma unroll
       for (int ti = 0; ti < NTERMS; ++ti) {
         const uint32_t acc = (ks == 0 && first) ? t_keep[ti] : 1u;
@@ -415,6 +419,7 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
   const uint32_t sub_cols = PLANES * p.bn;  // TMEM columns per column block
   const uint32_t acc_cols = p.n_sub * sub_cols;  // TMEM columns per accumulator stage
   const bool two_acc = p.acc_stages == 2;
+  const bool skew = !DBG && !GENERIC && PLANES == 1 && p.skew != 0;   // the diagnostic instance keeps the plain schedule
 
   if constexpr (GENERIC) {
     if (warp == 0 || warp == 3) {
@@ -664,6 +669,72 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++acc_it) {
         const uint32_t as = two_acc ? (acc_it & 1u) : 0u;
         const uint32_t aph = (two_acc ? (acc_it >> 1) : acc_it) & 1u;
+        if constexpr (PLANES == 1 && !GENERIC && !DBG) {
+          if (skew) {
+            // 512-column tile, one accumulator stage, barrier slot h for column block h.  Head: the first F
+            // k-blocks (F = the ring's depth) go into block 0 as soon as the epilogue has drained it, then -
+            // once block 1 is drained too - into block 1, which is what releases their stages.  Tail: the last
+            // F k-blocks go into block 0 first, its accumulator is handed to the epilogue, then into block 1.
+            const int kb0 = (t % p.k_split) * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
+            const int nkb = kb1 - kb0, F = p.stages;
+            auto await = [&](uint32_t bar, uint32_t par) -> bool {
+              const bool g = mbar_wait(bar, par, abort_flag, kTcWaitLimitNs);
+              if (!__all_sync(0xffffffffu, g)) {
+                if (reporter) tc_report(p.status, TC_ST_TIMEOUT_MMA);
+                return false;
+              }
+              tc_fence_after_sync();
+              return true;
+            };
+            auto advance = [&]() {
+              ++s; s16 += stage16;
+              if (s == p.stages) { s = 0; s16 = base16; ph ^= 1u; }
+            };
+            ok = await(bar_tempty, aph ^ 1u);
+            int s_sv = s; uint32_t s16_sv = s16, ph_sv = ph;
+            for (int i = 0; i < F && ok; ++i) {
+              ok = await(bar_full + 8u * s, ph);
+              if (ok && elected) tc_issue_kblock<CG, TF32, kMaxTerms, 1, 1, 0>(s16, i == 0, tmem_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+              advance();
+            }
+            if (ok) ok = await(bar_tempty + 8u, aph ^ 1u);
+            if (!ok) break;
+            s = s_sv; s16 = s16_sv; ph = ph_sv;
+            for (int i = 0; i < F; ++i) {
+              if (elected) {
+                tc_issue_kblock<CG, TF32, kMaxTerms, 1, 1, 1>(s16, i == 0, tmem_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+                umma_commit<CG>(bar_empty + 8u * s);
+              }
+              advance();
+            }
+            for (int i = F; i < nkb - F && ok; ++i) {
+              ok = await(bar_full + 8u * s, ph);
+              if (ok && elected) {
+                tc_issue_kblock<CG, TF32, kMaxTerms, 2, 1, 0>(s16, false, tmem_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+                umma_commit<CG>(bar_empty + 8u * s);
+              }
+              advance();
+            }
+            s_sv = s; s16_sv = s16; ph_sv = ph;
+            for (int i = 0; i < F && ok; ++i) {
+              ok = await(bar_full + 8u * s, ph);
+              if (ok && elected) tc_issue_kblock<CG, TF32, kMaxTerms, 1, 1, 0>(s16, false, tmem_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+              advance();
+            }
+            if (!ok) break;
+            if (elected) umma_commit<CG>(bar_tfull);            // column block 0 complete
+            s = s_sv; s16 = s16_sv; ph = ph_sv;
+            for (int i = 0; i < F; ++i) {
+              if (elected) {
+                tc_issue_kblock<CG, TF32, kMaxTerms, 1, 1, 1>(s16, false, tmem_base, hi_a, hi_b, off_a, off_b, d_off, t_id, t_keep);
+                umma_commit<CG>(bar_empty + 8u * s);
+              }
+              advance();
+            }
+            if (elected) umma_commit<CG>(bar_tfull + 8u);       // column block 1 complete
+            continue;
+          }
+        }
         if (prof) t0 = clock64();
         const bool tgot = mbar_wait(bar_tempty + 8u * as, aph ^ 1u, abort_flag, kTcWaitLimitNs);
         if (prof) mt += clock64() - t0;
@@ -774,17 +845,6 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
         }
       }
-      // all-or-nothing per warp: the TMEM loads below are warp-collective
-      const long long e0 = (dbg & 8) ? clock64() : 0;
-      const bool got = mbar_wait(bar_tfull + 8u * as, aph, abort_flag, kTcWaitLimitNs);
-      const long long e1 = (dbg & 8) ? clock64() : 0;
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_EPILOGUE);
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, dbg, 5, 1);   // first accumulator complete
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * acc_cols;
       const bool m_ok = m < p.M;
       float bias_row = 0.0f;
@@ -792,7 +852,24 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
       const int m_in = m % p.m_div, m_out = m / p.m_div;
       const int64_t d_row = m_in * p.d_sm0 + m_out * p.d_sm1 + bt * p.d_batch + split_off;
       const int64_t c_row = m_in * p.c_sm0 + m_out * p.c_sm1 + bt * p.c_batch;
-      for (int c = chunk_first; c < bn_tile; c += chunk_step) {
+      // One pass over the accumulator stage - or, with the skewed schedule of 512-column tiles, one pass per
+      // column block, each behind its own barrier (slot = block).
+      long long e0 = 0, e1 = 0;
+      for (int half = 0; half < (skew ? 2 : 1); ++half) {
+      const uint32_t hb = skew ? static_cast<uint32_t>(half) : as;
+      // all-or-nothing per warp: the TMEM loads below are warp-collective
+      e0 = (dbg & 8) ? clock64() : 0;
+      const bool got = mbar_wait(bar_tfull + 8u * hb, aph, abort_flag, kTcWaitLimitNs);
+      e1 = (dbg & 8) ? clock64() : 0;
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) tc_report(p.status, TC_ST_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      if (acc_it == 0 && half == 0 && warp == 4 && lane == 0) tc_mark(p.status, dbg, 5, 1);   // first accumulator complete
+      const int c_lo = chunk_first + (skew ? half * p.bn : 0), c_hi = skew ? (half + 1) * p.bn : bn_tile;
+      for (int c = c_lo; c < c_hi; c += chunk_step) {
         uint32_t v[PLANES][32];
         // column c of the tile is column c % bn of block c / bn (bn is a multiple of 32)
         const uint32_t t_col = t_row + (c >= p.bn ? sub_cols + (c - p.bn) : c);
@@ -890,13 +967,15 @@ __global__ void __launch_bounds__(tc_threads(PLANES), 1) tc_gemm_kernel(const __
           }
         }
       }
-      // Accumulator stage can be overwritten once every warp of the pair has read it.
+      // Accumulator stage (or column block) can be overwritten once every warp of the pair has read it.
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * as);
-        else mbar_arrive(bar_tempty + 8u * as);
+        if constexpr (CG == 2) mbar_arrive_cluster(tempty_leader + 8u * hb);
+        else mbar_arrive(bar_tempty + 8u * hb);
       }
+      }
+      if (!ok) break;
       if (acc_it == 0 && warp == 4 && lane == 0) tc_mark(p.status, dbg, 5, 2);   // first tile stored
       if ((dbg & 8) && warp == 4 && lane == 0) {
         p.dbg_out[blockIdx.x * 16 + 7] += e1 - e0;

@@ -515,6 +515,9 @@ gk_status tc_plan(gk_handle h, const TcProblem& pr_in, bool encode, TcLaunch* ou
   if (stages < 2)
     return set_error(GK_ERR_INVALID_CONFIG, "Requested too much shared memory: one pipeline stage needs %d bytes", stage_bytes);
   p.stages = stages;
+  // Skewed schedule of 512-column tiles (tc_gemm.cuh): every work unit must hold at least two rings of k-blocks.
+  p.skew = (n_sub == 2 && acc_stages == 1 && planes == 1 && kps == 1 && !pr.generic && pr.k_split <= 1 &&
+            p.k_blocks >= 2 * stages && !(pr.debug & 32)) ? 1 : 0;
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(acc_stages * n_sub * planes * bn)) cols <<= 1;
   p.tmem_cols = cols;

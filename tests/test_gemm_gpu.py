@@ -307,6 +307,31 @@ def test_tile_shapes_and_transposes_exact(ta, tb, cg, bn):
     assert np.array_equal(GK.to_numpy(d), O.gemm(A, B, trans_a=bool(ta), trans_b=bool(tb)))
 
 
+@pytest.mark.parametrize("ta,tb,K", [(0, 0, 512), (1, 0, 640), (0, 1, 1088), (1, 1, 576)])
+def test_wide_tiles_skewed_schedule_exact(ta, tb, K):
+    """256 x 512 tiles with K of at least two pipeline rings run the skewed schedule: the two 256-column blocks
+    of a tile start and finish half a ring apart, each behind its own accumulator barrier.  190 tiles on 74
+    CTA pairs (two or three tiles per pair, so the barriers change phase), a ragged last tile column, small
+    integers: any slip in the order of MMAs, commits or epilogue passes is a hard mismatch.  Twice, on the
+    same operands, to catch state left behind by the first launch."""
+    M, N = 2560, 9504
+    rng = np.random.default_rng(K + ta * 2 + tb)
+    A = rng.integers(-2, 3, (K, M) if ta else (M, K)).astype(np.float16)
+    B = rng.integers(-2, 3, (N, K) if tb else (K, N)).astype(np.float16)
+    la = (Layout.RowMajor if ta else Layout.ColMajor)[GK.Float16]
+    lb = (Layout.RowMajor if tb else Layout.ColMajor)[GK.Float16]
+    want = O.gemm(A, B, trans_a=bool(ta), trans_b=bool(tb))
+    a, b = dev(A), dev(B)
+    for _ in range(2):
+        d = GK.cuarray(GK.Float32, M, N); d.fill_(-7.0)
+        conf = run_matmul(a, b, None, d, M=M, N=N, K=K, op=Operator.TCGen05Operator[GK.Float16, GK.Float32],
+                          la=la, lb=lb, lc=Layout.Zero[GK.Float32], ld=Layout.ColMajor[GK.Float32],
+                          block_shape=(128, 128, 64), cta_group=2, tile_n=512)
+        plan = GK.query(conf, a, b, None, d)
+        assert plan.tile_n == 512 and plan.tmem_columns == 512 and K // 64 >= 2 * plan.stages
+        assert np.array_equal(GK.to_numpy(d), want)
+
+
 @pytest.mark.parametrize("swizzle", [CTASwizzle.Identity(), CTASwizzle.HorizontallyTiled[2], CTASwizzle.HorizontallyTiled[8],
                                      CTASwizzle.VerticallyTiled[3], CTASwizzle.LebesgueCurve()])
 @pytest.mark.parametrize("M,N", [(2048, 2048), (1024, 4096), (1400, 900)])
