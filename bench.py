@@ -41,7 +41,7 @@ METRIC = "GEMM TFLOP/s (FP16->FP32, 8192^3)"
 N_DIM = 8192
 FLOPS_PER_GEMM = 2.0 * N_DIM ** 3
 # DRAM traffic of one launch, from the ncu capture summarised in profiles/ (dram read + write).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.190e9   # dram__bytes.sum.per_second (1.706 TB/s) x gpu__time_duration (697.5 us)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.107e9   # dram__bytes.sum.per_second (1.619 TB/s) x gpu__time_duration (683.9 us)
 
 
 def measured_peaks():
