@@ -695,6 +695,32 @@ def test_fp64_fast_path_matches_float64_numpy(ta, tb):
             assert O.normwise_error(got, want) <= 1e-12
 
 
+@pytest.mark.parametrize("axis,act,beta", [("row", Transform.GELU(), 1.0), ("row", None, 0.0), (None, Transform.ReLU(), 0.5)])
+def test_fp64_fast_path_epilogue_variants(axis, act, beta):
+    """The FP64 kernel's other epilogue paths: per-row bias, GELU, no bias, beta = 0 (C not read) — against float64
+    numpy (erf from math), 1e-12 normwise."""
+    import math
+    M, N, K = 1536, 1280, 96
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((K, M)); B = rng.standard_normal((K, N)); Cm = rng.standard_normal((M, N))
+    bias = rng.standard_normal(M).astype(np.float32)
+    a, b, c, d = dev(A), dev(B), dev(Cm), GK.cuarray(GK.Float64, M, N)
+    epi = Epilogue.Bias(dev(bias), axis=axis) if axis else None
+    run_matmul(a, b, c if beta != 0.0 else None, d, M=M, N=N, K=K, op=Operator.FPUOp[8, 8, 1, 4, 8, 1, GK.Float64, GK.Float64],
+               la=Layout.UnsafeAlignedRowMajor[GK.Float64], lb=Layout.UnsafeAlignedColMajor[GK.Float64],
+               lc=(Layout.UnsafeAlignedColMajor if beta != 0.0 else Layout.Zero)[GK.Float64],
+               ld=Layout.UnsafeAlignedColMajor[GK.Float64], alpha=1.5, beta=beta if beta != 0.0 else 1.0,
+               epilogue=epi, act=act, block_shape=(128, 128, 32))
+    want = 1.5 * (A.T @ B) + (beta * Cm if beta != 0.0 else 0.0)
+    if axis:
+        want = want + bias[:, None].astype(np.float64)
+    if isinstance(act, Transform.ReLU):
+        want = np.maximum(want, 0)
+    elif isinstance(act, Transform.GELU):
+        want = 0.5 * want * (1.0 + np.vectorize(math.erf)(want / math.sqrt(2.0)))
+    assert O.normwise_error(GK.to_numpy(d), want) <= 1e-12
+
+
 def test_chained_products_without_host_synchronisation():
     """Y = (A*B)*C with the first product's Float16 output feeding the second, ten chains enqueued back to back:
     the second kernel may start its set-up while the first is still running (programmatic dependent launch) but
